@@ -1,0 +1,112 @@
+/* C ABI of the B200 (sm_100a) DeepSeek-sparse-attention kernels.
+ *
+ * Conventions (every entry point):
+ *   - plain pointers and sizes; all data pointers are DEVICE pointers on the current CUDA device;
+ *   - tensors are contiguous row-major in the layouts stated per function;
+ *   - returns 0 on success, non-zero on error with a message available from dsa_get_last_error();
+ *   - launches asynchronously on `stream` (a cudaStream_t passed as void*; NULL = default stream),
+ *     never synchronises, and allocates nothing except one 4-byte status word per device on the
+ *     first call on that device; workspaces are passed in by the caller;
+ *   - dtype: 0 = bfloat16, 1 = float16.
+ *
+ * These replace, for this path, the `extern "C" void call(uint8_t* arg0, ..., int64_t dyn0, ...,
+ * aclrtStream stream)` launcher that the reference's code generator emits per kernel
+ * (src/target/codegen_ascend.cc:1141-1226) and that its adapter binds
+ * (tilelang/jit/adapter/cython/cython_wrapper.pyx:75-203).  The `int` status + message convention is
+ * the one of the reference's CUDA wrapper, `init / get_last_error / call`
+ * (tilelang/jit/adapter/wrapper.py:30-50).
+ */
+#ifndef DSA_B200_H_
+#define DSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSA_DTYPE_BF16 0
+#define DSA_DTYPE_FP16 1
+
+/* Kernel choice for dsa_sparse_mla_fwd: the tensor-core kernel needs D = 576 and DV = 512. */
+#define DSA_IMPL_AUTO 0
+#define DSA_IMPL_GENERIC 1
+#define DSA_IMPL_TENSOR_CORE 2
+
+/* Prepares the current device (allocates and clears its status word).  Optional: every entry point
+ * does this on first use.  Mirrors `init()` of tilelang/jit/adapter/wrapper.py:30-50. */
+int dsa_init(void);
+
+/* Message of the last failed call on this thread (empty string if none).
+ * Mirrors `get_last_error()` of tilelang/jit/adapter/wrapper.py:30-50. */
+const char* dsa_get_last_error(void);
+
+/* Synchronises the current device, reads the device status word into *status (0 = every kernel ran
+ * to completion, 1 = a bounded in-kernel wait gave up) and clears it.  No reference counterpart: the
+ * reference launcher returns void and faults surface at the next synchronisation. */
+int dsa_kernel_status(int* status);
+
+/* Row-wise top-k.  scores [rows, row_stride] fp32 (n <= row_stride entries per row are looked at);
+ * limits [rows] int32 or NULL: number of leading entries of each row that are candidates;
+ * out_idx [rows, top_k] int32; out_val [rows, top_k] fp32 or NULL.
+ * Order: descending score, equal scores by ascending index; candidates need score > -1e30; unused
+ * slots hold -1 / -inf.  Replaces the kernel of simple_topk_selector
+ * (examples/topk_selector/example_topk_selector.py:10-54) and the sort/merge phase of the
+ * production indexer (examples/deepseek_v4/lightning_indexer.py:945-1081). */
+int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits,
+                    int32_t top_k, int32_t* out_idx, float* out_val, void* stream);
+
+/* Lightning-indexer scores: scores[b,s1,s2] = sum_h w[b,s1,h] * relu(q[b,s1,h,:] . k[b,s2,0,:]).
+ * q [B,S1,N1,D], k [B,S2,1,D] (dtype), w [B,S1,N1] fp32, scores [B,S1,S2] fp32.
+ * sparse_mode 3 = causal (key s2 is a candidate iff s2 < ak - aq + s1 + 1), 0 = all ak keys.
+ * q_len_b / k_len_b: per-batch actual lengths [B] int32 or NULL.  limits_out [B,S1] int32 or NULL
+ * receives the candidate count per row.  fill_masked != 0 writes -inf into every non-candidate entry
+ * (needed when `scores` is read as a full matrix; dsa_topk_select with limits does not need it).
+ * Replaces the cube + vector phases of make_lightning_indexer_kernel
+ * (examples/deepseek_v4/lightning_indexer.py:661-940) and the `indexer` kernel
+ * (examples/lightning_indexer/example_lightning_indexer.py:19-125). */
+int dsa_indexer_scores(const void* q, const void* k, const float* w, float* scores, int32_t B, int32_t S1, int32_t S2,
+                       int32_t N1, int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b,
+                       const int32_t* k_len_b, int32_t* limits_out, int32_t fill_masked, void* stream);
+
+/* Bytes of workspace dsa_lightning_indexer needs (fp32 score matrix + per-row limits). */
+size_t dsa_lightning_indexer_workspace_bytes(int32_t B, int32_t S1, int32_t S2);
+
+/* Fused front door of the production indexer: scores + causal limits + top-k in one call.
+ * out_idx [B,S1,1,top_k] int32, out_val [B,S1,1,top_k] fp32 or NULL, workspace as sized above.
+ * Replaces the kernel launched by lightning_indexer(...)
+ * (examples/deepseek_v4/lightning_indexer.py:1202-1370). */
+int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1,
+                          int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b,
+                          int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+/* Sparse MLA forward.  q [B,S,H,D], kv [B,S_kv,1,D] (or [num_blocks,block_size,1,D] with a block
+ * table), indices [B,S,1,topk] int32, out [B,S,H,DV] (dtype), lse [B,S,H] fp32 or NULL.
+ * An index takes part iff 0 <= idx < kv_len and (not causal or idx <= q_start + t); -1 and S_kv are
+ * therefore both padding.  Indices of one query must be distinct.  q_start_b / kv_len_b / q_len_b:
+ * per-batch [B] int32 overrides or NULL.  sm_scale multiplies q.k before the softmax; lse is
+ * natural-log.  Replaces the kernels of sparse_attention_fwd
+ * (examples/sparse_flash_attention/example_sparse_flash_attn.py:18-243, _mask_pa.py:13-333) and of
+ * sparse_attn_tilelang (bench_sfa/sparse_flash_attn_pa_no_cv_pipeline.py:27-419). */
+int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B,
+                       int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale,
+                       int32_t q_start, int32_t causal, int32_t dtype, const int32_t* q_start_b,
+                       const int32_t* kv_len_b, const int32_t* q_len_b, const int32_t* block_table, int32_t block_size,
+                       int32_t max_blocks, int32_t impl, void* stream);
+
+/* Sparse MLA backward.  Inputs as the forward plus out / lse of the forward and d_out [B,S,H,DV];
+ * outputs d_q [B,S,H,D] (dtype) and d_kv (fp32, same shape as kv, ACCUMULATED INTO: zero it first).
+ * The reference has no counterpart kernel; the decomposition follows its dense backward
+ * (examples_experiment/example_gqa_bwd/example_gqa_bwd.py:189-556). */
+int dsa_sparse_mla_bwd(const void* q, const void* kv, const int32_t* indices, const void* out, const float* lse,
+                       const void* d_out, void* d_q, float* d_kv, int32_t B, int32_t S, int32_t S_kv, int32_t H,
+                       int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start, int32_t causal,
+                       int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                       const int32_t* block_table, int32_t block_size, int32_t max_blocks, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_B200_H_ */

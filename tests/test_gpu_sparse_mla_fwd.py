@@ -1,0 +1,166 @@
+"""Sparse MLA forward on the GPU against the reference fixtures and the fp32 oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import from_bits
+from gpu_util import assert_close_fp, check_status
+from oracle import dsa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+IMPL_GENERIC, IMPL_TC = 1, 2
+
+
+def _fwd(q, kv, idx, impl, q_start=None, **kw):
+    import tilelang_ascend_b200 as dsa
+    S, S_kv, D = q.shape[1], kv.shape[1], q.shape[-1]
+    qs = S_kv - S if q_start is None else q_start
+    out, lse = dsa.sparse_mla_fwd_raw(q.cuda(), kv.cuda(), idx.cuda(), sm_scale=D ** -0.5, q_start=qs, causal=True, dv=512,
+                                      impl=impl, **kw)
+    check_status()
+    return out.cpu(), lse.cpu()
+
+
+@pytest.mark.parametrize("impl", [IMPL_TC, IMPL_GENERIC])
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_reference_golden_fixture(golden, tag, impl):
+    g = golden(f"sparse_mla_fwd_{tag}.npz")
+    q, kv, idx = from_bits(g["q"]), from_bits(g["kv"]), torch.from_numpy(g["indices"])
+    out, lse = _fwd(q, kv, idx, impl, q_start=int(g["q_start"]))
+    assert_close_fp(out, from_bits(g["out"]), f"out vs reference golden ({tag})")  # the reference's own bar is rtol=atol=1e-2
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx, q_start_index_s=int(g["q_start"]))
+    assert_close_fp(out, ref_o, "out vs oracle")
+    assert_close_fp(lse, ref_l, "lse vs oracle")
+
+
+@pytest.mark.parametrize("impl", [IMPL_TC, IMPL_GENERIC])
+def test_cpu_runnable_config(impl):
+    # B=1, S_q=128, S_kv=1024, H=16, topk=256, seed 0
+    q, kv, idx = orc.make_sparse_mla_inputs(1, 128, 1024, 16, 256, seed=0)
+    out, lse = _fwd(q, kv, idx, impl)
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(out, ref_o, "out")
+    assert_close_fp(lse, ref_l, "lse")
+
+
+def test_reference_factory_signature_and_lse_keyword():
+    import tilelang_ascend_b200 as dsa
+    q, kv, idx = orc.make_sparse_mla_inputs(1, 16, 512, 128, 128, seed=2)
+    kernel = dsa.sparse_attention_fwd(heads=128, dim=512, tail_dim=64, topk=128, kv_stride=1)
+    out = kernel(q.cuda(), kv.cuda(), idx.cuda())
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16 and tuple(out.shape) == (1, 16, 128, 512)
+    out2, lse = dsa.sparse_attention_fwd(128, 512, 64, 128, 1, return_softmax_lse=True)(q.cuda(), kv.cuda(), idx.cuda())
+    check_status()
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert torch.equal(out, out2)
+    assert_close_fp(out.cpu(), ref_o, "out")
+    assert_close_fp(lse.cpu(), ref_l, "lse")
+    assert dsa.sparse_attention_fwd(128, 512, 64, 128, 1) is kernel  # cached per argument tuple
+
+
+def test_fp16_inputs():
+    q, kv, idx = orc.make_sparse_mla_inputs(2, 8, 300, 128, 96, seed=3, dtype=torch.float16)
+    for impl in (IMPL_TC, IMPL_GENERIC):
+        out, lse = _fwd(q, kv, idx, impl)
+        ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+        assert out.dtype == torch.float16
+        assert_close_fp(out, ref_o, "out fp16")
+        assert_close_fp(lse, ref_l, "lse fp16")
+
+
+@pytest.mark.parametrize("impl", [IMPL_TC, IMPL_GENERIC])
+def test_padding_sentinels_masked_and_empty_rows(impl):
+    B, S, S_kv, H, topk = 2, 6, 200, 32, 64
+    q, kv, idx = orc.make_sparse_mla_inputs(B, S, S_kv, H, topk, seed=4)
+    idx[0, 0, 0, :] = -1                       # a query with no key at all
+    idx[0, 1, 0, ::2] = S_kv                   # the torch golden's sentinel
+    idx[0, 2, 0, 5:] = -1                      # -1 terminated list
+    idx[1, 0, 0, :32] = -1                     # a whole first tile empty, keys only later
+    idx[1, 1, 0, 3] = S_kv - 1                 # beyond the causal limit of query 1
+    idx[1, 2, 0, 7] = 10 ** 6                  # out of range
+    out, lse = _fwd(q, kv, idx, impl)
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(out, ref_o, "out")
+    assert_close_fp(lse, ref_l, "lse")
+    assert torch.all(out[0, 0] == 0) and torch.all(torch.isinf(lse[0, 0]))
+
+
+def test_ragged_topk_and_head_counts():
+    for H, topk in ((1, 40), (17, 8), (64, 72), (128, 200), (130, 33)):
+        q, kv, idx = orc.make_sparse_mla_inputs(1, 5, 400, H, topk, seed=H)
+        ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+        for impl in (IMPL_TC, IMPL_GENERIC):
+            out, lse = _fwd(q, kv, idx, impl)
+            assert_close_fp(out, ref_o, f"out H={H} topk={topk}")
+            assert_close_fp(lse, ref_l, f"lse H={H} topk={topk}")
+
+
+def test_large_scores_need_rescaling():
+    # a growing maximum across tiles exercises the accumulator rescale path
+    q, kv, idx = orc.make_sparse_mla_inputs(1, 4, 600, 128, 512, seed=6)
+    kv = (kv.float() * torch.linspace(0.2, 3.0, 600).view(1, -1, 1, 1)).to(torch.bfloat16)
+    idx = torch.sort(idx, dim=-1).values  # ascending positions -> growing score magnitude
+    out, lse = _fwd(q, kv, idx, IMPL_TC)
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(out, ref_o, "out")
+    assert_close_fp(lse, ref_l, "lse")
+
+
+def test_decode_shape_small():
+    # decode: one query per sequence, non-causal sampling over the whole cache
+    B, S_kv, H, topk = 4, 4096, 128, 512
+    q, kv, idx = orc.make_sparse_mla_inputs(B, 1, S_kv, H, topk, seed=7, causal=False)
+    out, lse = _fwd(q, kv, idx, IMPL_TC)
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(out, ref_o, "out")
+    assert_close_fp(lse, ref_l, "lse")
+
+
+def test_paged_front_end_matches_numpy_golden(golden):
+    import tilelang_ascend_b200 as dsa
+    g = golden("sfa_numpy_golden.npz")
+    q, kv = from_bits(g["q"]), from_bits(g["kv"])
+    idx = torch.from_numpy(g["indices"])
+    act_q, act_kv = torch.from_numpy(g["act_q"]), torch.from_numpy(g["act_kv"])
+    # BSND
+    out = dsa.sparse_attn_tilelang(q[..., :512].cuda(), kv[..., :512].cuda(), None, idx.cuda(), 576 ** -0.5, 1, act_q, act_kv,
+                                   query_rope=q[..., 512:].cuda(), key_rope=kv[..., 512:].cuda())
+    check_status()
+    for b in range(q.shape[0]):
+        aq = int(act_q[b])
+        assert_close_fp(out[b, :aq].cpu(), torch.from_numpy(g["out"][b, :aq]), "BSND vs NumPy golden")
+    # paged: scatter the same keys into shuffled 16-token blocks
+    bs, B, S_kv = 16, kv.shape[0], kv.shape[1]
+    nblk = S_kv // bs
+    perm = torch.randperm(B * nblk, generator=torch.Generator().manual_seed(0))
+    table = perm.view(B, nblk).to(torch.int32)
+    paged = torch.zeros((B * nblk, bs, 1, 576), dtype=kv.dtype)
+    for b in range(B):
+        for j in range(nblk):
+            paged[table[b, j]] = kv[b, j * bs:(j + 1) * bs]
+    out_p = dsa.sparse_attn_tilelang(q[..., :512].cuda(), paged[..., :512].cuda(), None, idx.cuda(), 576 ** -0.5, 1, act_q, act_kv,
+                                     query_rope=q[..., 512:].cuda(), key_rope=paged[..., 512:].cuda(), layout_kv="PA_BSND",
+                                     block_table=table.cuda())
+    check_status()
+    for b in range(B):
+        aq = int(act_q[b])
+        assert torch.equal(out_p[b, :aq], out[b, :aq])
+
+
+def test_rejects_bad_inputs():
+    import tilelang_ascend_b200 as dsa
+    q, kv, idx = orc.make_sparse_mla_inputs(1, 4, 64, 16, 64, seed=0)
+    k = dsa.sparse_attention_fwd(16, 512, 64, 64, 1)
+    with pytest.raises(ValueError):
+        k(q.cuda().transpose(1, 2), kv.cuda(), idx.cuda())          # not contiguous
+    with pytest.raises(ValueError):
+        k(q.cuda().half(), kv.cuda(), idx.cuda())                    # dtype
+    with pytest.raises(ValueError):
+        k(q.cuda(), kv, idx.cuda())                                  # device
+    with pytest.raises(ValueError):
+        k(q.cuda(), kv.cuda(), idx.cuda().long())                    # index dtype
+    with pytest.raises(AssertionError):
+        dsa.sparse_attention_fwd(16, 512, 64, 100, 1)                # topk % block_I
+    with pytest.raises(AssertionError):
+        dsa.sparse_attention_fwd(16, 512, 64, 64, 1, is_causal=False)

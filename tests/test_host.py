@@ -1,0 +1,79 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol, host logic, sharding."""
+import os
+import re
+
+import pytest
+import torch
+
+import tilelang_ascend_b200 as dsa
+from tilelang_ascend_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    with open(os.path.join(ROOT, "include", "dsa_b200.h")) as fh:
+        header = fh.read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(dsa_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def test_error_reporting_without_compute():
+    lib = _lib.load()
+    # argument validation happens before any CUDA call
+    rc = lib.dsa_topk_select(None, 1, 1, 1, None, 1, None, None, None)
+    assert rc != 0 and b"null" in lib.dsa_get_last_error()
+    rc = lib.dsa_sparse_mla_fwd(None, None, None, None, None, 1, 1, 1, 1, 576, 512, 1, 1.0, 0, 1, 0, None, None, None, None, 0, 0, 0, None)
+    assert rc != 0
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    x = torch.randn(4, 64)
+    with pytest.raises(ValueError, match="no CPU path"):
+        dsa.simple_topk_selector(4, 64, 8, 2)(x)
+    q = torch.randn(1, 2, 16, 576).bfloat16()
+    kv = torch.randn(1, 8, 1, 576).bfloat16()
+    idx = torch.zeros(1, 2, 1, 64, dtype=torch.int32)
+    with pytest.raises(ValueError, match="no CPU path"):
+        dsa.sparse_attention_fwd(16, 512, 64, 64, 1)(q, kv, idx)
+
+
+def test_factory_argument_rules():
+    with pytest.raises(AssertionError):
+        dsa.sparse_attention_fwd(16, 500, 64, 64, 1)
+    with pytest.raises(ValueError):
+        dsa.sparse_attention_fwd(16, 512, 64, 64, 4)
+    with pytest.raises(ValueError):
+        dsa.simple_topk_selector(4, 64, 128, 2)
+    with pytest.raises(ValueError):
+        dsa.mla_decode(1, 16, 2, 128, 512, 64)
+
+
+def test_shard_range_covers_everything_once():
+    for n in (0, 1, 7, 64, 4096, 4097):
+        for world in (1, 2, 3, 4, 8):
+            spans = [dsa.shard_range(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+            sizes = [e - s for s, e in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        dsa.shard_range(4, 2, 2)
+
+
+def test_shard_queries_keeps_causal_positions():
+    q = torch.zeros(1, 10, 2, 8)
+    idx = torch.zeros(1, 10, 1, 4, dtype=torch.int32)
+    starts = []
+    for r in range(4):
+        qs, ix, q_start = dsa.shard_queries(q, idx, r, 4, s_kv=32)
+        assert qs.shape[1] == ix.shape[1]
+        starts.append((q_start, qs.shape[1]))
+    assert starts[0][0] == 22
+    for (a, n), (b, _) in zip(starts, starts[1:]):
+        assert a + n == b

@@ -1,0 +1,18 @@
+"""B200 (sm_100a) kernels for the DeepSeek-sparse-attention hot path, behind the entry signatures of
+the TileLang-Ascend examples: lightning indexer -> top-k selector -> sparse MLA forward (+ decode,
+backward).  Python / PyTorch host code over a C-ABI CUDA library; there is no CPU fallback."""
+from . import _lib
+from .deepseek_mla import mla_decode
+from .lightning_indexer import indexer, indexer_scores_raw, lightning_indexer, lightning_indexer_raw
+from .sharding import shard_batch, shard_queries, shard_range
+from .sparse_flash_attention import (sparse_attention_fwd, sparse_attn_tilelang, sparse_mla, sparse_mla_bwd_raw,
+                                     sparse_mla_fwd_raw)
+from .topk_selector import simple_topk_selector, topk_select_raw
+
+kernel_status = _lib.kernel_status
+
+__all__ = [
+    "indexer", "lightning_indexer", "simple_topk_selector", "sparse_attention_fwd", "sparse_attn_tilelang", "mla_decode",
+    "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
+    "topk_select_raw", "shard_range", "shard_queries", "shard_batch", "kernel_status",
+]

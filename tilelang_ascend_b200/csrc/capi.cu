@@ -1,0 +1,208 @@
+// C ABI of the library: argument validation, parameter blocks, kernel launches.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "../../include/dsa_b200.h"
+#include "params.h"
+
+namespace dsa {
+// launchers defined in the kernel translation units
+bool sparse_mla_fwd_tc_supported(const FwdParams& p);
+int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream);
+int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t stream);
+size_t topk_smem_bytes(int n, int top_k, int* kpow2_out);
+int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
+                       int32_t* out_idx, float* out_val, cudaStream_t stream);
+bool indexer_tc_supported(const IndexerParams& p);
+int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream);
+int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream);
+int launch_sparse_mla_bwd(const BwdParams& bp, bool bf16, cudaStream_t stream);
+}  // namespace dsa
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(const std::string& msg) {
+  g_last_error = msg;
+  return 1;
+}
+int fail_cuda(const char* what, int err) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(static_cast<cudaError_t>(err));
+  return 1;
+}
+
+constexpr int kMaxDevices = 64;
+int* g_status[kMaxDevices] = {nullptr};
+std::mutex g_status_mutex;
+
+// Device status word of the current device (allocated and cleared on first use).
+int get_status_word(int** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status[dev]) {
+    int* ptr = nullptr;
+    e = cudaMalloc(&ptr, sizeof(int));
+    if (e != cudaSuccess) return fail_cuda("cudaMalloc(status word)", e);
+    e = cudaMemset(ptr, 0, sizeof(int));
+    if (e != cudaSuccess) return fail_cuda("cudaMemset(status word)", e);
+    g_status[dev] = ptr;
+  }
+  *out = g_status[dev];
+  return 0;
+}
+
+bool dtype_ok(int dtype) { return dtype == DSA_DTYPE_BF16 || dtype == DSA_DTYPE_FP16; }
+
+int fill_fwd_params(dsa::FwdParams* p, const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B,
+                    int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start,
+                    int32_t causal, int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                    const int32_t* block_table, int32_t block_size, int32_t max_blocks) {
+  if (!q || !kv || !indices || !out) return fail("null tensor pointer");
+  if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
+  if (B <= 0 || S <= 0 || S_kv <= 0 || H <= 0 || topk <= 0) return fail("B, S, S_kv, H and topk must be positive");
+  if (D <= 0 || D % 8 != 0 || D > 640) return fail("D must be a positive multiple of 8, at most 640");
+  if (DV <= 0 || DV > D || DV > 512) return fail("DV must be in [1, min(D, 512)]");
+  if (static_cast<int64_t>(B) * S > 0x7fffffffLL / 2) return fail("B * S too large");
+  if (block_table && (block_size <= 0 || max_blocks <= 0)) return fail("block_size and max_blocks must be positive with a block table");
+  if (!(sm_scale > 0.f) || !std::isfinite(sm_scale)) return fail("sm_scale must be positive and finite");
+  p->q = q; p->kv = kv; p->indices = indices; p->out = out; p->lse = lse;
+  p->B = B; p->S = S; p->S_kv = S_kv; p->H = H; p->topk = topk; p->D = D; p->DV = DV;
+  p->q_start = q_start; p->causal = causal ? 1 : 0;
+  p->q_start_b = q_start_b; p->kv_len_b = kv_len_b; p->q_len_b = q_len_b;
+  p->block_table = block_table; p->block_size = block_size; p->max_blocks = max_blocks;
+  p->scale_log2 = sm_scale * 1.4426950408889634f;
+  return get_status_word(&p->status);
+}
+
+}  // namespace
+
+extern "C" {
+
+int dsa_init(void) {
+  int* s = nullptr;
+  return get_status_word(&s);
+}
+
+const char* dsa_get_last_error(void) { return g_last_error.c_str(); }
+
+int dsa_kernel_status(int* status) {
+  int* s = nullptr;
+  if (get_status_word(&s)) return 1;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda("cudaDeviceSynchronize", e);
+  int host = 0;
+  e = cudaMemcpy(&host, s, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda("cudaMemcpy(status word)", e);
+  if (host != 0) {
+    e = cudaMemset(s, 0, sizeof(int));
+    if (e != cudaSuccess) return fail_cuda("cudaMemset(status word)", e);
+  }
+  if (status) *status = host;
+  return 0;
+}
+
+int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
+                    int32_t* out_idx, float* out_val, void* stream) {
+  if (!scores || !out_idx) return fail("null tensor pointer");
+  if (rows < 0 || n <= 0 || top_k <= 0 || row_stride < n) return fail("need rows >= 0, n > 0, top_k > 0, row_stride >= n");
+  if (rows == 0) return 0;
+  if (rows > 0x7fffffffLL) return fail("too many rows");
+  if (top_k > 8192) return fail("top_k must be at most 8192");
+  if (dsa::topk_smem_bytes(static_cast<int>(n), top_k, nullptr) > 220 * 1024)
+    return fail("row too long for the shared-memory selector (n * 4 + pow2(top_k) * 8 must fit 220 KB)");
+  int err = dsa::launch_topk_select(scores, rows, static_cast<int>(n), row_stride, limits, top_k, out_idx, out_val,
+                                    static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("topk_select launch", err) : 0;
+}
+
+static int indexer_scores_impl(const void* q, const void* k, const float* w, float* scores, int32_t B, int32_t S1, int32_t S2,
+                               int32_t N1, int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b,
+                               const int32_t* k_len_b, int32_t* limits_out, int32_t fill_masked, void* stream) {
+  if (!q || !k || !w || !scores) return fail("null tensor pointer");
+  if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
+  if (B <= 0 || S1 <= 0 || S2 <= 0 || N1 <= 0 || D <= 0) return fail("B, S1, S2, N1 and D must be positive");
+  if (sparse_mode != 0 && sparse_mode != 3) return fail("sparse_mode must be 0 or 3");
+  if (D % 8 != 0) return fail("D must be a multiple of 8");
+  dsa::IndexerParams p;
+  p.q = q; p.k = k; p.w = w; p.scores = scores;
+  p.B = B; p.S1 = S1; p.S2 = S2; p.N1 = N1; p.D = D;
+  p.sparse_mode = sparse_mode; p.q_len_b = q_len_b; p.k_len_b = k_len_b; p.limits = limits_out;
+  p.fill_masked = fill_masked ? 1 : 0;
+  if (get_status_word(&p.status)) return 1;
+  int err;
+  if (dsa::indexer_tc_supported(p)) {
+    err = dsa::launch_indexer_scores_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  } else {
+    if ((static_cast<size_t>(N1) * D + N1) * 4 > 200 * 1024) return fail("N1 * D too large for the generic indexer kernel");
+    err = dsa::launch_indexer_scores_generic(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  }
+  return err ? fail_cuda("indexer_scores launch", err) : 0;
+}
+
+int dsa_indexer_scores(const void* q, const void* k, const float* w, float* scores, int32_t B, int32_t S1, int32_t S2, int32_t N1,
+                       int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b,
+                       int32_t* limits_out, int32_t fill_masked, void* stream) {
+  return indexer_scores_impl(q, k, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits_out, fill_masked,
+                             stream);
+}
+
+size_t dsa_lightning_indexer_workspace_bytes(int32_t B, int32_t S1, int32_t S2) {
+  const size_t rows = static_cast<size_t>(B) * S1;
+  const size_t scores = (rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255);
+  return scores + rows * sizeof(int32_t);
+}
+
+int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
+                          int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, int32_t top_k,
+                          int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < dsa_lightning_indexer_workspace_bytes(B, S1, S2)) return fail("workspace missing or too small");
+  if (!out_idx) return fail("null tensor pointer");
+  const size_t rows = static_cast<size_t>(B) * S1;
+  float* scores = static_cast<float*>(workspace);
+  int32_t* limits = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ((rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255)));
+  int rc = indexer_scores_impl(q, k, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream);
+  if (rc) return rc;
+  return dsa_topk_select(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream);
+}
+
+int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B, int32_t S,
+                       int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start, int32_t causal,
+                       int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                       const int32_t* block_table, int32_t block_size, int32_t max_blocks, int32_t impl, void* stream) {
+  dsa::FwdParams p;
+  if (fill_fwd_params(&p, q, kv, indices, out, lse, B, S, S_kv, H, D, DV, topk, sm_scale, q_start, causal, dtype, q_start_b,
+                      kv_len_b, q_len_b, block_table, block_size, max_blocks))
+    return 1;
+  const bool tc_ok = dsa::sparse_mla_fwd_tc_supported(p);
+  if (impl == DSA_IMPL_TENSOR_CORE && !tc_ok) return fail("the tensor-core kernel needs D = 576, DV = 512 and topk <= 8192");
+  if (impl != DSA_IMPL_AUTO && impl != DSA_IMPL_GENERIC && impl != DSA_IMPL_TENSOR_CORE) return fail("unknown impl");
+  const bool use_tc = impl == DSA_IMPL_TENSOR_CORE || (impl == DSA_IMPL_AUTO && tc_ok);
+  int err = use_tc ? dsa::launch_sparse_mla_fwd_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream))
+                   : dsa::launch_sparse_mla_fwd_generic(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sparse_mla_fwd launch", err) : 0;
+}
+
+int dsa_sparse_mla_bwd(const void* q, const void* kv, const int32_t* indices, const void* out, const float* lse, const void* d_out,
+                       void* d_q, float* d_kv, int32_t B, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk,
+                       float sm_scale, int32_t q_start, int32_t causal, int32_t dtype, const int32_t* q_start_b,
+                       const int32_t* kv_len_b, const int32_t* q_len_b, const int32_t* block_table, int32_t block_size,
+                       int32_t max_blocks, void* stream) {
+  if (!lse || !d_out || !d_q || !d_kv) return fail("null tensor pointer");
+  dsa::BwdParams bp;
+  if (fill_fwd_params(&bp.f, q, kv, indices, const_cast<void*>(out), const_cast<float*>(lse), B, S, S_kv, H, D, DV, topk, sm_scale,
+                      q_start, causal, dtype, q_start_b, kv_len_b, q_len_b, block_table, block_size, max_blocks))
+    return 1;
+  bp.d_out = d_out; bp.d_q = d_q; bp.d_kv = d_kv; bp.sm_scale = sm_scale;
+  int err = dsa::launch_sparse_mla_bwd(bp, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sparse_mla_bwd launch", err) : 0;
+}
+
+}  // extern "C"

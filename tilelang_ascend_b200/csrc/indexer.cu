@@ -1,0 +1,306 @@
+// Lightning-indexer score kernel for sm_100a.
+//
+//   score[b, s1, s2] = sum_h w[b, s1, h] * relu( q[b, s1, h, :] . k[b, s2, 0, :] )        (fp32)
+//
+// with keys at or beyond the row's limit set to -inf (causal rule of sparse_mode 3).  Semantics
+// follow cpu_lightning_indexer, examples/deepseek_v4/lightning_indexer.py:303-314.
+//
+// Tensor-core kernel (D = 128): the MMA is issued transposed -- A = a tile of 128 keys x 128 dims
+// (UMMA M = keys), B = (QB queries x N1 heads = 256 rows) x 128 dims -- so the TMEM accumulator has
+// one key per lane and all heads of a query in consecutive columns.  The ReLU, the per-head weight
+// and the sum over heads are then a per-thread reduction over columns, and a warp writes 32
+// consecutive keys of one query row (coalesced).  Two accumulators (2 x 256 TMEM columns) let the
+// reduction of tile i overlap the MMAs of tile i+1.
+//
+// Generic kernel (any D, any N1): CUDA-core fp32.
+#include <type_traits>
+
+#include "params.h"
+#include "ptx.cuh"
+
+namespace dsa {
+
+__device__ __forceinline__ int indexer_limit(const IndexerParams& p, int b, int s1, int* ak_out) {
+  const int aq = p.q_len_b ? p.q_len_b[b] : p.S1;
+  const int ak = p.k_len_b ? p.k_len_b[b] : p.S2;
+  *ak_out = ak;
+  if (s1 >= aq || ak <= 0) return 0;
+  if (p.sparse_mode == 3) {
+    const int cl = ak - aq + s1 + 1;
+    return cl > 0 ? (cl < ak ? cl : ak) : ak;
+  }
+  return ak;
+}
+
+namespace itc {
+constexpr int kD = 128;
+constexpr int kKeys = 128;                         // keys per tile = UMMA M
+constexpr int kN = 256;                            // (queries x heads) per CTA = UMMA N
+constexpr int kStages = 3;
+constexpr uint32_t kQBytes = 2 * kN * 128;         // 65536: 2 chunks of [256 rows x 128 B]
+constexpr uint32_t kKStageBytes = 2 * kKeys * 128; // 32768
+constexpr uint32_t kOffK = kQBytes;
+constexpr uint32_t kOffW = kOffK + kStages * kKStageBytes;  // 163840
+constexpr uint32_t kOffBar = kOffW + kN * 4;
+constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kThreads = 288;
+constexpr uint32_t kTmemCols = 512;
+}  // namespace itc
+
+template <bool kBF16, int N1>
+__global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(const IndexerParams p) {
+  using namespace itc;
+  constexpr int QB = kN / N1;  // queries per CTA
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + kOffK;
+  float* sW = reinterpret_cast<float*>(smem + kOffW);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+  uint64_t* k_full = bars;          // [3] count 128
+  uint64_t* k_empty = bars + 3;     // [3] count 1 (commit)
+  uint64_t* acc_full = bars + 6;    // [2] count 1 (commit)
+  uint64_t* acc_empty = bars + 8;   // [2] count 128
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  int* start_status = reinterpret_cast<int*>(bars + 11);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nqb = (p.S1 + QB - 1) / QB;
+  const int b = blockIdx.x / nqb;
+  const int qb = nqb - 1 - (blockIdx.x - b * nqb);  // late (long) query blocks first
+  const int q0 = qb * QB;
+
+  if (tid == 0) *start_status = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (*start_status != kStatusOk) return;
+
+  // key range this CTA has to score: up to the largest limit among its queries
+  int ak = 0, max_lim = 0;
+  for (int i = 0; i < QB; ++i) {
+    const int s1 = q0 + i;
+    if (s1 < p.S1) { const int l = indexer_limit(p, b, s1, &ak); max_lim = l > max_lim ? l : max_lim; }
+  }
+  const int ntiles_mma = (max_lim + kKeys - 1) / kKeys;
+  const int ntiles_all = p.fill_masked ? (p.S2 + kKeys - 1) / kKeys : ntiles_mma;
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) { mbar_init(&k_full[i], 128); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    mbar_init_fence();
+  }
+  if (warp == 4) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  {  // Q rows (query, head) -> B operand rows; weights
+    const T* qbase = reinterpret_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.S1 + q0) * N1 * kD;
+    for (int u = tid; u < kN * 16; u += kThreads) {
+      const int r = u >> 4, unit = u & 15;
+      const bool ok = q0 + r / N1 < p.S1;
+      const T* src = ok ? qbase + static_cast<int64_t>(r) * kD + unit * 8 : reinterpret_cast<const T*>(p.q);
+      cp_async16(sQ + (unit >> 3) * (kN * 128) + sw128_offset(r, unit & 7), src, ok ? 16u : 0u);
+    }
+    cp_async_commit();
+    for (int r = tid; r < kN; r += kThreads)
+      sW[r] = (q0 + r / N1 < p.S1) ? p.w[(static_cast<int64_t>(b) * p.S1 + q0) * N1 + r] : 0.f;
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+  }
+  if (p.limits && tid < QB && q0 + tid < p.S1) {
+    int dummy;
+    p.limits[static_cast<int64_t>(b) * p.S1 + q0 + tid] = indexer_limit(p, b, q0 + tid, &dummy);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp >= 5) {
+    // ================================ key-tile producers ============================================
+    const int pt = tid - 160;
+    const T* kbase = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(b) * p.S2 * kD;
+    for (int it = 0; it < ntiles_mma; ++it) {
+      const int s = it % kStages;
+      if (it >= kStages && !mbar_wait(&k_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
+      const uint32_t stage = sK + s * kKStageBytes;
+#pragma unroll 4
+      for (int j = 0; j < 16; ++j) {
+        const int u = pt + 128 * j;
+        const int r = u >> 4, unit = u & 15;
+        const int key = it * kKeys + r;
+        const bool v = key < ak;
+        const T* src = v ? kbase + static_cast<int64_t>(key) * kD + unit * 8 : kbase;
+        cp_async16(stage + (unit >> 3) * (kKeys * 128) + sw128_offset(r, unit & 7), src, v ? 16u : 0u);
+      }
+      cp_async_commit();
+      if (it >= 1) {
+        cp_async_wait<1>();
+        fence_proxy_async_smem();
+        mbar_arrive(&k_full[(it - 1) % kStages]);
+      }
+    }
+    cp_async_wait<0>();
+    if (ok && ntiles_mma > 0) {
+      fence_proxy_async_smem();
+      mbar_arrive(&k_full[(ntiles_mma - 1) % kStages]);
+    }
+  } else if (warp == 4) {
+    // ================================ MMA issuer ====================================================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBF16, kKeys, kN, 0, 0);
+      for (int it = 0; it < ntiles_mma; ++it) {
+        const int s = it % kStages, a = it & 1;
+        if (!mbar_wait(&k_full[s], (it / kStages) & 1, p.status)) { ok = false; break; }
+        if (it >= 2 && !mbar_wait(&acc_empty[a], ((it >> 1) + 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t stage = sK + s * kKStageBytes;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_smem_desc(stage + c * (kKeys * 128) + k * 32, 16, 1024, kSwizzle128B);
+            const uint64_t db = make_smem_desc(sQ + c * (kN * 128) + k * 32, 16, 1024, kSwizzle128B);
+            umma_ss(tmem_base + a * kN, da, db, idesc, (c | k) != 0);
+          }
+        }
+        umma_commit(&k_empty[s]);
+        umma_commit(&acc_full[a]);
+      }
+    }
+  } else {
+    // ================================ reduce over heads + store ====================================
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    int lim[QB];
+#pragma unroll
+    for (int i = 0; i < QB; ++i) {
+      int dummy;
+      lim[i] = (q0 + i < p.S1) ? indexer_limit(p, b, q0 + i, &dummy) : 0;
+    }
+    float* out = p.scores + (static_cast<int64_t>(b) * p.S1 + q0) * p.S2;
+    for (int it = 0; it < ntiles_all; ++it) {
+      const int key = it * kKeys + tid;
+      if (it < ntiles_mma) {
+        const int a = it & 1;
+        if (!mbar_wait(&acc_full[a], (it >> 1) & 1, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + a * kN + lane_base;
+        if constexpr (N1 >= 32) {
+#pragma unroll
+          for (int i = 0; i < QB; ++i) {
+            float sum = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < N1 / 32; ++cc) {
+              uint32_t v[32];
+              tmem_ld32(tacc + i * N1 + cc * 32, v);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) sum = fmaf(sW[i * N1 + cc * 32 + j], fmaxf(__uint_as_float(v[j]), 0.f), sum);
+            }
+            if (q0 + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? sum : -INFINITY;
+          }
+        } else {
+          constexpr int QPC = 32 / N1;  // queries per 32-column chunk
+#pragma unroll
+          for (int cc = 0; cc < kN / 32; ++cc) {
+            uint32_t v[32];
+            tmem_ld32(tacc + cc * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int qq = 0; qq < QPC; ++qq) {
+              float sum = 0.f;
+#pragma unroll
+              for (int j = 0; j < N1; ++j)
+                sum = fmaf(sW[cc * 32 + qq * N1 + j], fmaxf(__uint_as_float(v[qq * N1 + j]), 0.f), sum);
+              const int i = cc * QPC + qq;
+              if (q0 + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? sum : -INFINITY;
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[a]);
+      } else if (key < p.S2) {  // tile entirely beyond every limit of this CTA
+#pragma unroll
+        for (int i = 0; i < QB; ++i)
+          if (q0 + i < p.S1) out[static_cast<int64_t>(i) * p.S2 + key] = -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// -------------------------------------------------------------------------------------------------
+// generic CUDA-core kernel: one CTA per (batch, query), one thread per key (strided)
+// -------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) indexer_scores_generic_kernel(const IndexerParams p) {
+  extern __shared__ float sq[];  // [N1 * D] query heads in fp32, then [N1] weights
+  float* sw = sq + p.N1 * p.D;
+  const int b = blockIdx.y, s1 = blockIdx.x;
+  const T* qrow = reinterpret_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.S1 + s1) * p.N1 * p.D;
+  for (int i = threadIdx.x; i < p.N1 * p.D; i += blockDim.x) sq[i] = static_cast<float>(qrow[i]);
+  for (int i = threadIdx.x; i < p.N1; i += blockDim.x) sw[i] = p.w[(static_cast<int64_t>(b) * p.S1 + s1) * p.N1 + i];
+  __syncthreads();
+  int ak;
+  const int lim = indexer_limit(p, b, s1, &ak);
+  if (p.limits && threadIdx.x == 0) p.limits[static_cast<int64_t>(b) * p.S1 + s1] = lim;
+  float* out = p.scores + (static_cast<int64_t>(b) * p.S1 + s1) * p.S2;
+  const int kend = p.fill_masked ? p.S2 : lim;
+  for (int key = threadIdx.x; key < kend; key += blockDim.x) {
+    float score = -INFINITY;
+    if (key < lim) {
+      const T* krow = reinterpret_cast<const T*>(p.k) + (static_cast<int64_t>(b) * p.S2 + key) * p.D;
+      score = 0.f;
+      for (int h = 0; h < p.N1; ++h) {
+        float dot = 0.f;
+        for (int d = 0; d < p.D; ++d) dot = fmaf(sq[h * p.D + d], static_cast<float>(krow[d]), dot);
+        score = fmaf(sw[h], fmaxf(dot, 0.f), score);
+      }
+    }
+    out[key] = score;
+  }
+}
+
+bool indexer_tc_supported(const IndexerParams& p) {
+  return p.D == itc::kD && (p.N1 == 64 || p.N1 == 32 || p.N1 == 16 || p.N1 == 8);
+}
+
+template <bool kBF16, int N1>
+static int launch_indexer_tc_n1(const IndexerParams& p, cudaStream_t stream) {
+  auto kern = indexer_scores_tc_kernel<kBF16, N1>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(itc::kSmemBytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  constexpr int QB = itc::kN / N1;
+  const int nqb = (p.S1 + QB - 1) / QB;
+  kern<<<p.B * nqb, itc::kThreads, itc::kSmemBytes, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream) {
+  switch (p.N1) {
+    case 64: return bf16 ? launch_indexer_tc_n1<true, 64>(p, stream) : launch_indexer_tc_n1<false, 64>(p, stream);
+    case 32: return bf16 ? launch_indexer_tc_n1<true, 32>(p, stream) : launch_indexer_tc_n1<false, 32>(p, stream);
+    case 16: return bf16 ? launch_indexer_tc_n1<true, 16>(p, stream) : launch_indexer_tc_n1<false, 16>(p, stream);
+    case 8: return bf16 ? launch_indexer_tc_n1<true, 8>(p, stream) : launch_indexer_tc_n1<false, 8>(p, stream);
+    default: return static_cast<int>(cudaErrorInvalidValue);
+  }
+}
+
+int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream) {
+  const size_t smem = (static_cast<size_t>(p.N1) * p.D + p.N1) * sizeof(float);
+  dim3 grid(p.S1, p.B);
+  cudaError_t e;
+  if (bf16) {
+    e = cudaFuncSetAttribute(indexer_scores_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    indexer_scores_generic_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(indexer_scores_generic_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    indexer_scores_generic_kernel<__half><<<grid, 256, smem, stream>>>(p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dsa

@@ -1,0 +1,59 @@
+// Plain-old-data parameter blocks passed by value to the kernels.
+#pragma once
+#include <stdint.h>
+
+namespace dsa {
+
+// Sparse MLA forward.  All tensors contiguous row-major.
+//   q        [B, S, H, D]            bf16 / fp16
+//   kv       [B, S_kv, 1, D]         (or [num_blocks, block_size, 1, D] when block_table != null)
+//   indices  [B, S, 1, topk] int32   (-1, >= kv_len, or beyond the causal limit = not taking part)
+//   out      [B, S, H, DV]           same dtype as q
+//   lse      [B, S, H] fp32          (nullable)
+struct FwdParams {
+  const void* q;
+  const void* kv;
+  const int32_t* indices;
+  void* out;
+  float* lse;
+  int B, S, S_kv, H, topk, D, DV;
+  int q_start;                 // absolute position of query 0 (used when q_start_b == null)
+  int causal;                  // 1: key idx takes part only if idx <= q_start + t
+  const int32_t* q_start_b;    // [B] per-sequence start position (act_kv - act_q), nullable
+  const int32_t* kv_len_b;     // [B] per-sequence key count, nullable (default S_kv)
+  const int32_t* q_len_b;      // [B] per-sequence query count, nullable (default S)
+  const int32_t* block_table;  // [B, max_blocks] paged KV, nullable
+  int block_size, max_blocks;
+  float scale_log2;            // sm_scale * log2(e)
+  int* status;                 // device status word (0 = ok)
+};
+
+// Sparse MLA backward: the forward's fields (out / lse hold the forward results) plus gradients.
+struct BwdParams {
+  FwdParams f;
+  const void* d_out;  // [B, S, H, DV]
+  void* d_q;          // [B, S, H, D]
+  float* d_kv;        // fp32, same shape as kv, accumulated into
+  float sm_scale;
+};
+
+// Lightning-indexer scores.  All tensors contiguous row-major.
+//   q       [B, S1, N1, D]  bf16 / fp16
+//   k       [B, S2, 1, D]
+//   w       [B, S1, N1]     fp32
+//   scores  [B, S1, S2]     fp32; entries at or beyond the row's limit are -inf
+struct IndexerParams {
+  const void* q;
+  const void* k;
+  const float* w;
+  float* scores;
+  int B, S1, S2, N1, D;
+  int sparse_mode;            // 3: causal limit k < ak - aq + s1 + 1 (all keys if that is <= 0); 0: k < ak
+  const int32_t* q_len_b;     // [B] actual query counts (nullable: S1)
+  const int32_t* k_len_b;     // [B] actual key counts (nullable: S2)
+  int32_t* limits;            // [B, S1] out, nullable: number of leading keys that are candidates per row
+  int fill_masked;            // 1: also write -inf into tiles that lie entirely beyond the limit
+  int* status;
+};
+
+}  // namespace dsa

@@ -1,0 +1,207 @@
+// Row-wise top-k selector: radix select + bitonic sort of the survivors.
+//
+// For each fp32 row the kernel emits the indices of the `top_k` largest candidates in descending
+// score order, equal scores in ascending index order (the stable-sort rule of
+// cpu_lightning_indexer, examples/deepseek_v4/lightning_indexer.py:316-325); candidates are the first
+// `limit[row]` entries whose score is > -1e30; slots left over hold -1 (value -inf).  For rows of
+// distinct values this is also torch.topk's answer (examples/topk_selector/example_topk_selector.py:57-58).
+//
+// One CTA per row.  The row is converted to order-preserving 32-bit keys in shared memory, four
+// 8-bit most-significant-digit-first histogram passes find the k-th largest key, one ordered
+// compaction pass takes everything above it plus the lowest-index ties, and a bitonic sort of the
+// <= k survivors on (key, ~index) fixes the output order.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace dsa {
+
+namespace topk {
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+}  // namespace topk
+
+__device__ __forceinline__ uint32_t float_to_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  if (u == 0x80000000u) u = 0u;  // -0.0 ties with +0.0, as in a floating-point comparison
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+// scores [rows, row_stride]; limits [rows] or null; out_idx [rows, top_k]; out_val [rows, top_k] or null.
+// Dynamic shared memory: n * 4 (keys) + kpow2 * 8 (sort buffer).
+__global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
+                                                                     const int32_t* __restrict__ limits, int top_k, int kpow2,
+                                                                     int32_t* __restrict__ out_idx, float* __restrict__ out_val) {
+  using namespace topk;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  unsigned long long* sortbuf = reinterpret_cast<unsigned long long*>(smem_raw);            // [kpow2]
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(kpow2) * 8);  // [n]
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t warp_sums[kWarps];
+  __shared__ uint32_t s_prefix, s_remaining, s_nvalid, s_count, s_tie_base;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;
+  const float* x = scores + static_cast<int64_t>(row) * row_stride;
+  int lim = limits ? limits[row] : n;
+  lim = lim < 0 ? 0 : (lim > n ? n : lim);
+
+  if (tid == 0) { s_nvalid = 0; s_count = 0; s_tie_base = 0; }
+  if (tid < 256) hist[tid] = 0;
+  __syncthreads();
+
+  // ---- load, convert, count candidates, first-digit histogram ---------------------------------------
+  uint32_t my_valid = 0;
+  for (int base = 0; base < n; base += kThreads) {  // whole warps iterate together (full-mask match below)
+    const int i = base + tid;
+    uint32_t k = 0;
+    if (i < lim) {
+      const float f = x[i];
+      if (f > -1e30f) { k = float_to_key(f); ++my_valid; }
+    }
+    if (i < n) keys[i] = k;  // 0 marks "not a candidate" (a real key is never 0 for a score > -1e30)
+    const uint32_t d = k ? (k >> 24) : 256u;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    if (k && lane == __ffs(peers) - 1) atomicAdd(&hist[d], __popc(peers));
+  }
+  for (int o = 16; o > 0; o >>= 1) my_valid += __shfl_xor_sync(0xffffffffu, my_valid, o);
+  if (lane == 0 && my_valid) atomicAdd(&s_nvalid, my_valid);
+  __syncthreads();
+  const uint32_t nvalid = s_nvalid;
+  const uint32_t kk = nvalid < static_cast<uint32_t>(top_k) ? nvalid : static_cast<uint32_t>(top_k);
+
+  // ---- radix select: threshold key T = kk-th largest candidate key -----------------------------------
+  uint32_t thresh = 0;     // everything is taken when nvalid <= top_k
+  uint32_t need_ties = 0;  // how many keys equal to T are taken (lowest indices first)
+  if (nvalid > static_cast<uint32_t>(top_k)) {
+    if (tid == 0) { s_prefix = 0; s_remaining = kk; }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (pass > 0) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const uint32_t pmask = 0xffffffffu << (shift + 8);
+        for (int base = 0; base < n; base += kThreads) {
+          const int i = base + tid;
+          const uint32_t k = i < n ? keys[i] : 0u;
+          const bool in = k && (k & pmask) == prefix;
+          const uint32_t d = in ? ((k >> shift) & 0xffu) : 256u;
+          const uint32_t peers = __match_any_sync(0xffffffffu, d);
+          if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[d], __popc(peers));
+        }
+        __syncthreads();
+      }
+      // warp 0 walks the 256 bins from the top: find digit dsel with  sum(bins > dsel) < remaining <= sum(bins >= dsel)
+      if (warp == 0) {
+        const uint32_t remaining = s_remaining;
+        uint32_t c[8], tot = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { c[j] = hist[255 - (lane * 8 + j)]; tot += c[j]; }  // lane 0 holds the top 8 bins
+        uint32_t incl = tot;
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        uint32_t above = incl - tot;  // candidates in bins above this lane's 8 bins
+        const bool mine = above < remaining && remaining <= incl;
+        if (mine) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (above < remaining && remaining <= above + c[j]) {
+              s_prefix = s_prefix | ((255u - (lane * 8 + j)) << shift);
+              s_remaining = remaining - above;
+            }
+            above += c[j];
+          }
+        }
+      }
+      __syncthreads();
+    }
+    thresh = s_prefix;
+    need_ties = s_remaining;
+  }
+
+  // ---- ordered compaction: keys > T in any order, keys == T by ascending index until need_ties ----------
+  for (int i = tid; i < kpow2; i += kThreads) sortbuf[i] = 0ull;
+  __syncthreads();
+  const bool take_all = nvalid <= static_cast<uint32_t>(top_k);
+  for (int base = 0; base < n; base += kThreads) {
+    const int i = base + tid;
+    const uint32_t k = i < n ? keys[i] : 0u;
+    const bool gt = k != 0 && (take_all || k > thresh);
+    const bool eq = !take_all && k != 0 && k == thresh;
+    // rank of this tie among the ties seen so far (index order): block-wide exclusive scan of eq
+    const uint32_t bal = __ballot_sync(0xffffffffu, eq);
+    const uint32_t in_warp = __popc(bal & ((1u << lane) - 1u));
+    if (lane == 0) warp_sums[warp] = __popc(bal);
+    __syncthreads();
+    uint32_t before = s_tie_base;
+    for (int w = 0; w < warp; ++w) before += warp_sums[w];
+    const bool take_tie = eq && (before + in_warp) < need_ties;
+    if (gt || take_tie) {
+      const uint32_t pos = atomicAdd(&s_count, 1u);
+      sortbuf[pos] = (static_cast<unsigned long long>(k) << 32) | static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(i));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t t = 0;
+      for (int w = 0; w < kWarps; ++w) t += warp_sums[w];
+      s_tie_base += t;
+    }
+    __syncthreads();
+  }
+
+  // ---- bitonic sort, descending on (key, ~index): larger score first, then lower index ---------------------
+  for (int size = 2; size <= kpow2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
+        const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
+        const int hi = lo | stride;
+        const bool desc = (lo & size) == 0;
+        const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
+        if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---- output ---------------------------------------------------------------------------------------------
+  int32_t* oi = out_idx + static_cast<int64_t>(row) * top_k;
+  float* ov = out_val ? out_val + static_cast<int64_t>(row) * top_k : nullptr;
+  for (int i = tid; i < top_k; i += kThreads) {
+    if (static_cast<uint32_t>(i) < kk) {
+      const unsigned long long e = sortbuf[i];
+      oi[i] = static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(e & 0xffffffffull));
+      if (ov) ov[i] = key_to_float(static_cast<uint32_t>(e >> 32));
+    } else {
+      oi[i] = -1;
+      if (ov) ov[i] = -INFINITY;
+    }
+  }
+}
+
+size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
+  int kp = 2;
+  while (kp < top_k) kp <<= 1;
+  if (kpow2_out) *kpow2_out = kp;
+  return static_cast<size_t>(n) * 4 + static_cast<size_t>(kp) * 8;
+}
+
+int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
+                       int32_t* out_idx, float* out_val, cudaStream_t stream) {
+  int kp = 0;
+  const size_t smem = topk_smem_bytes(n, top_k, &kp);
+  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  topk_select_kernel<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx,
+                                                                                   out_val);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace dsa

@@ -1,0 +1,191 @@
+"""Sparse MLA forward / backward behind the reference's entry signatures.
+
+``sparse_attention_fwd(...)`` keeps the factory signature of
+examples/sparse_flash_attention/example_sparse_flash_attn.py:18-28 and returns a kernel called as
+``kernel(q, kv, indices)``; ``sparse_attn_tilelang(...)`` keeps the paged / decode wrapper signature of
+examples/sparse_flash_attention/bench_sfa/sparse_flash_attn_pa_no_cv_pipeline.py:384-400.  The LSE
+output follows the reference's own keyword ``return_softmax_lse``
+(examples/deepseek_v4/sparse_flash_mla/sparse_flash_mla_api.py:114,251-253).
+"""
+from __future__ import annotations
+
+import functools
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .adapter import check_inputs, current_stream, dtype_code, ptr, torch_dtype
+
+
+def _next_pow2(x: int) -> int:
+    return 1 << (max(int(x), 1) - 1).bit_length()
+
+
+def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal: bool, dv: int, out=None,
+                       return_lse: bool = True, q_start_b=None, kv_len_b=None, q_len_b=None, block_table=None,
+                       block_size: int = 0, impl: int = _lib.IMPL_AUTO):
+    """One launch of the forward through the C ABI.  q [B,S,H,D], kv [B,S_kv,1,D] (or paged blocks),
+    indices [B,S,1,topk] int32.  Returns (out, lse-or-None)."""
+    opt = [t for t in (q_start_b, kv_len_b, q_len_b, block_table) if t is not None]
+    dev = check_inputs([q, kv, indices] + opt, [None, q.dtype, torch.int32] + [torch.int32] * len(opt),
+                       ["q", "kv", "indices"] + ["int32 side input"] * len(opt))
+    code = dtype_code(q.dtype)
+    if q.dim() != 4 or kv.dim() != 4 or indices.dim() != 4:
+        raise ValueError("q, kv and indices must be 4-dimensional ([B,S,H,D], [B,S_kv,1,D], [B,S,1,topk])")
+    B, S, H, D = q.shape
+    if kv.shape[2] != 1 or kv.shape[3] != D or indices.shape[:3] != (B, S, 1):
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, kv {tuple(kv.shape)}, indices {tuple(indices.shape)}")
+    if block_table is None:
+        if kv.shape[0] != B:
+            raise ValueError("kv batch size differs from q")
+        S_kv, max_blocks = kv.shape[1], 0
+    else:
+        block_size = int(block_size) if block_size else kv.shape[1]
+        max_blocks = block_table.shape[1]
+        S_kv = max_blocks * block_size
+    topk = indices.shape[3]
+    if out is None:
+        out = torch.empty((B, S, H, dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, S, H), dtype=torch.float32, device=dev) if return_lse else None
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().dsa_sparse_mla_fwd(
+            ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
+            1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
+            int(max_blocks), int(impl), current_stream(dev)))
+    return out, lse
+
+
+def sparse_mla_bwd_raw(q, kv, indices, out, lse, d_out, *, sm_scale: float, q_start: int, causal: bool):
+    """dQ (input dtype) and dKV (fp32) of the forward; no reference counterpart (see the C header)."""
+    dev = check_inputs([q, kv, indices, out, lse, d_out], [None, q.dtype, torch.int32, q.dtype, torch.float32, q.dtype],
+                       ["q", "kv", "indices", "out", "lse", "d_out"])
+    B, S, H, D = q.shape
+    S_kv, dv, topk = kv.shape[1], out.shape[3], indices.shape[3]
+    d_q = torch.empty_like(q)
+    d_kv = torch.zeros(kv.shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().dsa_sparse_mla_bwd(
+            ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), ptr(d_out), ptr(d_q), ptr(d_kv), B, S, S_kv, H, D, dv, topk,
+            float(sm_scale), int(q_start), 1 if causal else 0, dtype_code(q.dtype), None, None, None, None, 0, 0,
+            current_stream(dev)))
+    return d_q, d_kv
+
+
+class SparseAttentionFwdKernel:
+    """Callable returned by :func:`sparse_attention_fwd`; ``kernel(q, kv, indices) -> out`` (or
+    ``(out, lse)`` with ``return_softmax_lse=True``).  Only inputs are passed; outputs are allocated
+    on the device of ``q`` and the launch goes to the current stream without synchronising."""
+
+    def __init__(self, heads, dim, tail_dim, topk, sm_scale, dtype, return_softmax_lse, impl):
+        self.heads, self.dim, self.tail_dim, self.topk = heads, dim, tail_dim, topk
+        self.sm_scale, self.dtype, self.return_softmax_lse, self.impl = sm_scale, dtype, return_softmax_lse, impl
+
+    def __call__(self, q, kv, indices, q_start_index_s: Optional[int] = None):
+        if q.dtype != self.dtype:
+            raise ValueError(f"Input tensor q has dtype {q.dtype}, expected {self.dtype}")
+        if q.dim() != 4 or q.shape[2] != self.heads or q.shape[3] != self.dim + self.tail_dim:
+            raise ValueError(f"q must be [B, S, {self.heads}, {self.dim + self.tail_dim}], got {tuple(q.shape)}")
+        if indices.dim() != 4 or indices.shape[3] != self.topk:
+            raise ValueError(f"indices must be [B, S, 1, {self.topk}], got {tuple(indices.shape)}")
+        S, S_kv = q.shape[1], kv.shape[1]
+        q_start = S_kv - S if q_start_index_s is None else int(q_start_index_s)
+        out, lse = sparse_mla_fwd_raw(q, kv, indices, sm_scale=self.sm_scale, q_start=q_start, causal=True, dv=self.dim,
+                                      return_lse=self.return_softmax_lse, impl=self.impl)
+        return (out, lse) if self.return_softmax_lse else out
+
+
+@functools.lru_cache(maxsize=None)
+def _sparse_attention_fwd_cached(heads, dim, tail_dim, topk, kv_stride, kv_group, sm_scale, is_causal, block_I, dtype,
+                                 return_softmax_lse, impl):
+    # argument rules of the reference factory (example_sparse_flash_attn.py:30-36)
+    assert dim == _next_pow2(dim), f"haven't check padding correctness yet, dim={dim}"
+    assert tail_dim == _next_pow2(tail_dim), f"haven't check padding correctness yet, dim={tail_dim}"
+    assert is_causal, "non-casual is not supported"
+    assert topk % block_I == 0, "otherwise will load some index=0 thus causing wrong kv to be loaded"
+    if kv_group != 1:
+        raise ValueError("kv_group must be 1 (one latent KV head shared by all query heads)")
+    if kv_stride != 1:
+        raise ValueError("kv_stride must be 1")
+    scale = (1.0 / (dim + tail_dim)) ** 0.5 if sm_scale is None else float(sm_scale)
+    return SparseAttentionFwdKernel(heads, dim, tail_dim, topk, scale, torch_dtype(dtype), return_softmax_lse, impl)
+
+
+def sparse_attention_fwd(heads, dim, tail_dim, topk, kv_stride, kv_group=1, sm_scale=None, is_causal=True, block_I=64,
+                         dtype="bfloat16", return_softmax_lse=False, impl=_lib.IMPL_AUTO):
+    """Factory with the reference's signature; cached per argument tuple like the reference's
+    ``@tilelang.jit`` (tilelang/jit/__init__.py:216-255).  ``block_I`` is a tiling hint of the
+    reference kernel: it is validated and otherwise ignored."""
+    return _sparse_attention_fwd_cached(heads, dim, tail_dim, topk, kv_stride, kv_group, sm_scale, is_causal, block_I,
+                                        str(dtype).replace("torch.", ""), bool(return_softmax_lse), int(impl))
+
+
+def sparse_attn_tilelang(query, key, value, sparse_indices, scale_value, sparse_block_size, actual_seq_lengths_query,
+                         actual_seq_lengths_kv, query_rope=None, key_rope=None, layout_query="BSND", layout_kv="BSND",
+                         sparse_mode=3, block_table=None, attention_mode=None, return_softmax_lse=False):
+    """Paged / variable-length front end (decode and chunked prefill).
+
+    query [B,S,H,512] + query_rope [B,S,H,64]; key / key_rope either BSND ([B,S_kv,1,*]) or paged
+    PA_BSND ([num_blocks, block_size, 1, *]) with ``block_table`` [B, max_blocks]; ``value`` is the
+    latent itself and is not read; sparse_indices [B,S,1,topk] int32, -1 terminated; per-batch actual
+    lengths give the causal rule idx <= act_kv - act_q + s.  Mirrors sparse_attn_tilelang
+    (bench_sfa/sparse_flash_attn_pa_no_cv_pipeline.py:384-419) and the NumPy golden
+    cpu_sparse_flash_attention (examples/sparse_flash_attention/sfa_golden.py:117-199).  The reference
+    wrapper takes a single un-batched [S,H,*] query as well; that form is accepted too.
+    """
+    if layout_query != "BSND":
+        raise ValueError("only layout_query='BSND' is supported")
+    if layout_kv not in ("BSND", "PA_BSND"):
+        raise ValueError(f"unsupported layout_kv {layout_kv}")
+    if sparse_block_size != 1:
+        raise ValueError("sparse_block_size must be 1 (token-level indices)")
+    if sparse_mode not in (0, 3):
+        raise ValueError("sparse_mode must be 0 or 3")
+    squeeze = query.dim() == 3
+    if squeeze:
+        query, query_rope, sparse_indices = query.unsqueeze(0), query_rope.unsqueeze(0), sparse_indices.unsqueeze(0)
+    q = torch.cat((query, query_rope), dim=-1).contiguous()
+    kv = torch.cat((key, key_rope), dim=-1).contiguous()
+    dev = q.device
+    B, S = q.shape[0], q.shape[1]
+    act_q = torch.as_tensor(actual_seq_lengths_query, dtype=torch.int32).to(dev).contiguous()
+    act_kv = torch.as_tensor(actual_seq_lengths_kv, dtype=torch.int32).to(dev).contiguous()
+    q_start_b = (act_kv - act_q).contiguous()
+    bt = None
+    if layout_kv == "PA_BSND":
+        if block_table is None:
+            raise ValueError("block_table is required for PA_BSND")
+        bt = block_table.to(device=dev, dtype=torch.int32).contiguous()
+    out, lse = sparse_mla_fwd_raw(q, kv, sparse_indices.to(torch.int32).contiguous(), sm_scale=float(scale_value), q_start=0,
+                                  causal=(sparse_mode == 3), dv=query.shape[-1], return_lse=return_softmax_lse,
+                                  q_start_b=q_start_b, kv_len_b=act_kv, q_len_b=act_q, block_table=bt,
+                                  block_size=kv.shape[1] if bt is not None else 0)
+    if squeeze:
+        out = out.squeeze(0)
+        lse = lse.squeeze(0) if lse is not None else None
+    return (out, lse) if return_softmax_lse else out
+
+
+class SparseMLAFunction(torch.autograd.Function):
+    """Autograd node over the forward / backward kernels (causal, BSND)."""
+
+    @staticmethod
+    def forward(ctx, q, kv, indices, sm_scale, q_start, dv):
+        out, lse = sparse_mla_fwd_raw(q, kv, indices, sm_scale=sm_scale, q_start=q_start, causal=True, dv=dv)
+        ctx.save_for_backward(q, kv, indices, out, lse)
+        ctx.sm_scale, ctx.q_start = sm_scale, q_start
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, d_out, _d_lse):
+        q, kv, indices, out, lse = ctx.saved_tensors
+        d_q, d_kv = sparse_mla_bwd_raw(q, kv, indices, out, lse, d_out.contiguous(), sm_scale=ctx.sm_scale,
+                                       q_start=ctx.q_start, causal=True)
+        return d_q, d_kv.to(kv.dtype), None, None, None, None
+
+
+def sparse_mla(q, kv, indices, sm_scale=None, q_start_index_s=None, dv=512):
+    """Differentiable sparse MLA: returns (out, lse)."""
+    scale = q.shape[-1] ** -0.5 if sm_scale is None else float(sm_scale)
+    q_start = kv.shape[1] - q.shape[1] if q_start_index_s is None else int(q_start_index_s)
+    return SparseMLAFunction.apply(q, kv, indices, scale, q_start, dv)
