@@ -8,10 +8,9 @@
 // of the paged variant (example_sparse_flash_attn_mask_pa.py:221-238).
 //
 // Two kernels:
-//  * sparse_mla_fwd_tc_kernel  -- D = 576, DV = 512: tcgen05 tensor-core MMAs with TMEM accumulators.
-//    One CTA per (query, half of the DV columns, block of 128 heads).  TMEM cannot hold a
-//    128 x 512 fp32 output tile and a score tile at once, so the output columns are split across
-//    two CTAs; each computes the full score tile.
+//  * sparse_mla_fwd_tc_kernel  -- D = 576, DV = 512: tcgen05 tensor-core MMAs with TMEM accumulators,
+//    one 2-CTA cluster per (query, block of 128 heads); the two CTAs split the contraction dims of
+//    Q K^T and the output columns of P V and exchange partial scores through distributed shared memory.
 //  * sparse_mla_fwd_generic_kernel -- any D <= 640 / DV <= 512 (e.g. the GQA example with dim 128):
 //    CUDA-core fp32, one warp per head.
 #include <type_traits>
@@ -69,72 +68,85 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // -------------------------------------------------------------------------------------------------
-// tcgen05 kernel
+// tcgen05 kernel: one 2-CTA cluster per (query, block of 128 heads)
 // -------------------------------------------------------------------------------------------------
+// TMEM (512 columns x 128 lanes) cannot hold a 128 x 512 fp32 output tile plus a score tile, so the
+// two CTAs of a cluster split the work of one query without duplicating any of it:
+//   CTA r owns latent dims [256 r, 256 r + 256) and rope dims [512 + 32 r, 544 + 32 r):
+//     * it gathers only those 576 bytes of every selected KV row,
+//     * computes the PARTIAL scores S_r = Q[:, its dims] . K[:, its dims]^T (contraction split),
+//     * sends S_r to its peer through distributed shared memory and adds the peer's S_(1-r),
+//     * runs the (identical) online softmax, and
+//     * accumulates O[:, 256 r : 256 r + 256] = P . V[:, its latent dims]   (output columns split).
+// Per CTA: Q latent dims live in TMEM as the A operand (no shared-memory re-read per MMA), the Q rope
+// dims and P in shared memory, KV tiles of 64 keys in a 3-stage cp.async ring, two score buffers in
+// TMEM so the QK^T of tile i+1 overlaps the softmax of tile i.
 namespace tc {
-constexpr int kD = 576, kDV = 512, kChunks = 9;     // 9 chunks of 64 dims (128 B of bf16)
-constexpr int kM = 128;                             // heads per CTA = UMMA M
-constexpr int kBK = 32;                             // keys per tile
-constexpr int kStages = 2;
-constexpr int kHalfDV = 256;                        // output columns per CTA
-constexpr int kMaxTiles = 256;                      // topk <= 8192
-constexpr uint32_t kQBytes = kChunks * kM * 128;    // 147456
-constexpr uint32_t kKVChunkBytes = kBK * 128;       // 4096
-constexpr uint32_t kKVStageBytes = kChunks * kKVChunkBytes;  // 36864
-constexpr uint32_t kPBytes = kM * kBK * 2;          // 8192
-constexpr uint32_t kOffKV = kQBytes;
-constexpr uint32_t kOffP = kOffKV + kStages * kKVStageBytes;  // 221184
-constexpr uint32_t kOffBar = kOffP + kPBytes;                 // 229376
-constexpr uint32_t kOffMask = kOffBar + 128;
-constexpr uint32_t kOffList = kOffMask + kMaxTiles * 4;
+constexpr int kD = 576, kDV = 512;
+constexpr int kM = 128;                               // heads per cluster = UMMA M
+constexpr int kBK = 64;                               // keys per tile
+constexpr int kStages = 3;
+constexpr int kHalfDV = 256;                          // output columns (and latent dims) per CTA
+constexpr int kMaxTiles = 128;                        // topk <= 8192
+constexpr uint32_t kChunkBytes = kBK * 128;           // 8192: 64 keys x 64 dims, 128-byte swizzle
+constexpr uint32_t kStageBytes = 5 * kChunkBytes;     // 4 latent chunks + the rope chunk (half of each row in use)
+constexpr uint32_t kQRopeBytes = kM * 128;            // Q rope dims, same half-used row layout
+constexpr uint32_t kPBytes = kM * 128;                // P [128 x 64] bf16
+constexpr uint32_t kXBytes = kM * kBK * 4;            // peer's partial scores [128 x 64] fp32
+constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
+constexpr uint32_t kOffP = kOffQRope + kQRopeBytes;               // 139264
+constexpr uint32_t kOffX = kOffP + kPBytes;                       // 155648
+constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 221184
+constexpr uint32_t kOffMask = kOffBar + 256;
+constexpr uint32_t kOffList = kOffMask + kMaxTiles * 8;
 constexpr uint32_t kSmemBytes = kOffList + kMaxTiles * 2 + 1024;  // + slack to align the base to 1024 B
-constexpr int kThreads = 288;                       // 4 softmax warps, 1 MMA warp, 4 gather warps
+constexpr int kThreads = 288;                         // 4 softmax warps, 1 MMA warp, 4 gather warps
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS = 256;
-constexpr float kRescaleThreshold = 8.0f;           // log2 units: P stays below 2^8
+constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
+constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
 }  // namespace tc
 
 template <bool kBF16>
-__global__ void __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(const FwdParams p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(const FwdParams p) {
   using namespace tc;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t sQ = smem_u32(smem);
-  const uint32_t sKV = sQ + kOffKV;
-  const uint32_t sP = sQ + kOffP;
+  const uint32_t sBase = smem_u32(smem);
+  const uint32_t sQRope = sBase + kOffQRope, sP = sBase + kOffP, sX = sBase + kOffX;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
-  uint64_t* kv_full = bars;        // [2] count 128: gather threads
-  uint64_t* kv_empty = bars + 2;   // [2] count 1: tcgen05.commit after the PV MMAs of the stage
-  uint64_t* s_full = bars + 4;     // count 1: commit after the QK MMAs
-  uint64_t* p_full = bars + 5;     // count 128: softmax threads wrote P
-  uint64_t* o_full = bars + 6;     // count 1: commit after the last PV
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-  int* n_valid_tiles = reinterpret_cast<int*>(bars + 9);
-  int* start_status = reinterpret_cast<int*>(bars + 10);
-  uint32_t* masks = reinterpret_cast<uint32_t*>(smem + kOffMask);
+  uint64_t* kv_full = bars;         // [3] count 128: cp.async completion of the gather threads
+  uint64_t* kv_empty = bars + 3;    // [3] count 1: commit after the PV MMAs of the stage
+  uint64_t* s_full = bars + 6;      // [2] count 1: commit after the QK MMAs
+  uint64_t* s_empty = bars + 8;     // [2] count 128: softmax threads read the partial scores
+  uint64_t* p_full = bars + 10;     // count 128: softmax threads wrote P
+  uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
+  uint64_t* x_full = bars + 12;     // [2] count 128: the peer's partial scores arrived here
+  uint64_t* x_empty = bars + 14;    // [2] count 128: the peer consumed what this CTA sent
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  int* n_valid_tiles = reinterpret_cast<int*>(bars + 17);
+  int* start_status = reinterpret_cast<int*>(bars + 18);
+  unsigned long long* masks = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint16_t* tile_list = reinterpret_cast<uint16_t*>(smem + kOffList);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int half = blockIdx.x;           // which 256 output columns
-  const int bt = blockIdx.y;             // flat (batch, query)
-  const int h0 = blockIdx.z * kM;        // first head of this CTA
+  const uint32_t rank = cluster_ctarank();   // which half of the dims / output columns
+  const uint32_t peer = rank ^ 1u;
+  const int bt = blockIdx.y;                 // flat (batch, query)
+  const int h0 = blockIdx.z * kM;            // first head of this cluster
   const RowCtx ctx = make_row_ctx(p, bt);
   const int ntiles = (p.topk + kBK - 1) / kBK;
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
 
-  if (tid == 0) *start_status = *reinterpret_cast<volatile int*>(p.status);
-  __syncthreads();
-  if (*start_status != kStatusOk || !ctx.active) return;  // an earlier CTA failed, or padding row
-
-  // ---- setup: barriers, TMEM, per-tile validity masks, Q -----------------------------------------
+  // ---- setup ------------------------------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(&kv_full[0], 128);
-    mbar_init(&kv_full[1], 128);
-    mbar_init(&kv_empty[0], 1);
-    mbar_init(&kv_empty[1], 1);
-    mbar_init(s_full, 1);
+    *start_status = *reinterpret_cast<volatile int*>(p.status);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+      mbar_init(&x_full[i], 128); mbar_init(&x_empty[i], 128);
+    }
     mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    mbar_init(pv_done, 1);
     mbar_init_fence();
   }
   if (warp == 4) {
@@ -142,18 +154,26 @@ __global__ void __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(cons
     tmem_relinquish();
   }
   for (int tile = warp; tile < ntiles; tile += kThreads / 32) {
-    const int slot = tile * kBK + lane;
-    const int idx = slot < p.topk ? ctx.idx_row[slot] : -1;
-    const uint32_t m = __ballot_sync(0xffffffffu, index_valid(ctx, idx));
-    if (lane == 0) masks[tile] = m;
+    const int s0 = tile * kBK + lane, s1 = s0 + 32;
+    const int i0 = s0 < p.topk ? ctx.idx_row[s0] : -1;
+    const int i1 = s1 < p.topk ? ctx.idx_row[s1] : -1;
+    const uint32_t lo = __ballot_sync(0xffffffffu, index_valid(ctx, i0));
+    const uint32_t hi = __ballot_sync(0xffffffffu, index_valid(ctx, i1));
+    if (lane == 0) masks[tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
   }
-  {  // Q tile: rows = heads, 9 chunks of [128 x 128 B], 128-byte swizzle; missing heads are zero
-    const T* qrow = reinterpret_cast<const T*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0) * kD;
-    for (int u = tid; u < kM * (kD / 8); u += kThreads) {
-      const int r = u / (kD / 8), unit = u - r * (kD / 8);
+  {  // Q: this CTA's 256 latent dims go to a staging area (later the KV ring), its 32 rope dims to sQRope
+    const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0) * (kD * 2);
+    for (int u = tid; u < kM * 32; u += kThreads) {
+      const int r = u >> 5, unit = u & 31;
       const bool ok = h0 + r < p.H;
-      const T* src = ok ? qrow + static_cast<int64_t>(r) * kD + unit * 8 : reinterpret_cast<const T*>(p.q);
-      cp_async16(sQ + (unit >> 3) * (kM * 128) + sw128_offset(r, unit & 7), src, ok ? 16u : 0u);
+      const uint8_t* src = ok ? qrow + static_cast<int64_t>(r) * (kD * 2) + rank * 512 + unit * 16 : reinterpret_cast<const uint8_t*>(p.q);
+      cp_async16(sBase + r * 512 + ((unit ^ (r & 31)) << 4), src, ok ? 16u : 0u);
+    }
+    for (int u = tid; u < kM * 4; u += kThreads) {
+      const int r = u >> 2, unit = 4 * rank + (u & 3);
+      const bool ok = h0 + r < p.H;
+      const uint8_t* src = ok ? qrow + static_cast<int64_t>(r) * (kD * 2) + 1024 + unit * 16 : reinterpret_cast<const uint8_t*>(p.q);
+      cp_async16(sQRope + sw128_offset(r, unit), src, ok ? 16u : 0u);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -162,108 +182,160 @@ __global__ void __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tO = tmem_base + kColO, tS = tmem_base + kColS, tQ = tmem_base + kColQ;
   if (tid == 0) {  // compact list of tiles with at least one key taking part
     int n = 0;
     for (int tile = 0; tile < ntiles; ++tile)
-      if (masks[tile] != 0) tile_list[n++] = static_cast<uint16_t>(tile);
+      if (masks[tile] != 0ull) tile_list[n++] = static_cast<uint16_t>(tile);
     *n_valid_tiles = n;
   }
+  if (warp < 4) {  // staging -> TMEM: lane = head row, column c holds dims (2c, 2c+1) of the CTA's latent slice
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+#pragma unroll 1
+    for (int cc = 0; cc < 4; ++cc) {
+      uint32_t w[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(smem + tid * 512 + (((cc * 8 + j) ^ (tid & 31)) << 4));
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      tmem_st32(tQ + lane_base + cc * 32, w);
+    }
+    tmem_wait_st();
+  }
+  tc_fence_before();
   __syncthreads();
-  const int nvt = *n_valid_tiles;
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tO = tmem_base + kColO, tS = tmem_base + kColS;
+  tc_fence_after();
+  // both CTAs must have their barriers initialised before any remote arrive; every thread takes part
+  cluster_sync_all();
+  const bool run = *start_status == kStatusOk && ctx.active;
+  const int nvt = run ? *n_valid_tiles : 0;
   bool ok = true;
 
   if (warp >= 5) {
     // ================================ gather producers =============================================
-    const int pt = tid - 160;  // 0..127
+    const int pw = warp - 5;  // keys [16 pw, 16 pw + 16) of every tile
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
     for (int it = 0; it < nvt; ++it) {
-      const int tile = tile_list[it], s = it & 1;
-      if (it >= kStages && !mbar_wait(&kv_empty[s], ((it >> 1) + 1) & 1, p.status)) { ok = false; break; }
-      const uint32_t stage = sKV + s * kKVStageBytes;
-#pragma unroll 6
-      for (int j = 0; j < (kBK * 72) / 128; ++j) {
-        const int u = pt + 128 * j;
-        const int key = u / 72, unit = u - key * 72;
-        const int slot = tile * kBK + key;
-        const int idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
-        const bool v = index_valid(ctx, idx);
-        const uint8_t* src = v ? kv_bytes + kv_row(p, ctx.b, idx) * (kD * 2) + unit * 16 : kv_bytes;
-        cp_async16(stage + (unit >> 3) * kKVChunkBytes + sw128_offset(key, unit & 7), src, v ? 16u : 0u);
+      const int tile = tile_list[it], s = it % kStages;
+      if (it >= kStages && !mbar_wait(&kv_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
+      const uint32_t stage = sBase + s * kStageBytes;
+      const int slot = tile * kBK + pw * 16 + (lane & 15);
+      const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
+      const bool my_valid = index_valid(ctx, my_idx);
+      const long long my_row = my_valid ? kv_row(p, ctx.b, my_idx) : -1ll;
+#pragma unroll 4
+      for (int kk = 0; kk < 16; ++kk) {
+        const long long row = __shfl_sync(0xffffffffu, my_row, kk);
+        const bool v = row >= 0;
+        const int key = pw * 16 + kk;
+        const uint8_t* base = kv_bytes + (v ? row : 0) * (kD * 2);
+        cp_async16(stage + (lane >> 3) * kChunkBytes + sw128_offset(key, lane & 7), base + rank * 512 + lane * 16, v ? 16u : 0u);
+        if (lane < 4)
+          cp_async16(stage + 4 * kChunkBytes + sw128_offset(key, 4 * rank + lane), base + 1024 + (4 * rank + lane) * 16, v ? 16u : 0u);
       }
-      cp_async_commit();
-      if (it >= 1) {
-        cp_async_wait<1>();
-        fence_proxy_async_smem();
-        mbar_arrive(&kv_full[(it - 1) & 1]);
-      }
+      cp_async_arrive_noinc(&kv_full[s]);
     }
     cp_async_wait<0>();
-    if (ok && nvt > 0) {
-      fence_proxy_async_smem();
-      mbar_arrive(&kv_full[(nvt - 1) & 1]);
-    }
   } else if (warp == 4) {
     // ================================ MMA issuer ====================================================
-    if (lane == 0) {
+    if (lane == 0 && nvt > 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, kHalfDV, 0, 1);
-      for (int it = 0; it < nvt; ++it) {
-        const int s = it & 1;
-        const uint32_t stage = sKV + s * kKVStageBytes;
-        if (!mbar_wait(&kv_full[s], (it >> 1) & 1, p.status)) { ok = false; break; }
+      // S_r[128 x 64] = Q[:, dims of this CTA] . K^T : 16 steps with A in TMEM + 2 rope steps with A in smem
+      auto issue_qk = [&](int it) -> bool {
+        const int s = it % kStages, sb = it & 1;
+        const uint32_t stage = sBase + s * kStageBytes;
+        if (!mbar_wait(&kv_full[s], (it / kStages) & 1, p.status)) return false;
+        if (it >= 2 && !mbar_wait(&s_empty[sb], ((it >> 1) + 1) & 1, p.status)) return false;
+        fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
-        // S[128 x 32] = Q[128 x 576] . K^T : both operands K-major, 36 steps of 16 dims
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_smem_desc(sQ + c * (kM * 128) + k * 32, 16, 1024, kSwizzle128B);
-            const uint64_t db = make_smem_desc(stage + c * kKVChunkBytes + k * 32, 16, 1024, kSwizzle128B);
-            umma_ss(tS, da, db, idesc_qk, (c | k) != 0);
+            const uint64_t db = make_smem_desc(stage + c * kChunkBytes + k * 32, 16, 1024, kSwizzle128B);
+            umma_ts(tS + sb * kBK, tQ + (c * 4 + k) * 8, db, idesc_qk, (c | k) != 0);
           }
         }
-        umma_commit(s_full);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t off = (2 * rank + k) * 32;
+          const uint64_t da = make_smem_desc(sQRope + off, 16, 1024, kSwizzle128B);
+          const uint64_t db = make_smem_desc(stage + 4 * kChunkBytes + off, 16, 1024, kSwizzle128B);
+          umma_ss(tS + sb * kBK, da, db, idesc_qk, 1);
+        }
+        umma_commit(&s_full[sb]);
+        return true;
+      };
+      ok = issue_qk(0);
+      for (int it = 0; ok && it < nvt; ++it) {
+        if (it + 1 < nvt && !issue_qk(it + 1)) { ok = false; break; }
         if (!mbar_wait(p_full, it & 1, p.status)) { ok = false; break; }
         tc_fence_after();
-        // O[128 x 256] += P[128 x 32] . V[32 x 256] : P K-major (no swizzle), V MN-major (dims contiguous)
+        // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P K-major, V MN-major (this CTA's latent dims)
+        const uint32_t stage = sBase + (it % kStages) * kStageBytes;
 #pragma unroll
         for (int ks = 0; ks < kBK / 16; ++ks) {
-          const uint64_t da = make_smem_desc(sP + ks * 256, 128, 512, kSwizzleNone);
-          const uint64_t db = make_smem_desc(stage + (4 * half) * kKVChunkBytes + ks * 2048, kKVChunkBytes, 1024, kSwizzle128B);
+          const uint64_t da = make_smem_desc(sP + ks * 32, 16, 1024, kSwizzle128B);
+          const uint64_t db = make_smem_desc(stage + ks * 2048, kChunkBytes, 1024, kSwizzle128B);
           umma_ss(tO, da, db, idesc_pv, (it | ks) != 0);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&kv_empty[it % kStages]);
+        umma_commit(pv_done);
       }
-      if (ok) umma_commit(o_full);
     }
   } else {
     // ================================ softmax + epilogue ============================================
     const int r = tid;  // TMEM lane = head row
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t peer_x = map_to_cta(sX, peer);
+    const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
+    const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
     float m_used = -INFINITY, l = 0.f;
-    uint32_t v[32];
     for (int it = 0; it < nvt; ++it) {
-      const uint32_t mask = masks[tile_list[it]];
-      if (!mbar_wait(s_full, it & 1, p.status)) { ok = false; break; }
+      const unsigned long long mask = masks[tile_list[it]];
+      const int sb = it & 1;
+      uint32_t v[64];
+      if (!mbar_wait(&s_full[sb], (it >> 1) & 1, p.status)) { ok = false; break; }
       tc_fence_after();
-      tmem_ld32(tS + lane_base, v);
+      tmem_ld32(tS + sb * kBK + lane_base, v);
+      tmem_ld32(tS + sb * kBK + lane_base + 32, v + 32);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_empty[sb]);
+      // ---- exchange partial scores with the peer CTA (row r, 16 units of 4 floats; unit-major layout) ----
+      if (it >= 2 && !mbar_wait_cluster(&x_empty[sb], ((it >> 1) + 1) & 1, p.status)) { ok = false; break; }
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        st_cluster_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      mbar_arrive_cluster(peer_x_full + sb * 8);
+      if (!mbar_wait_cluster(&x_full[sb], (it >> 1) & 1, p.status)) { ok = false; break; }
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float x = __uint_as_float(v[j]) * p.scale_log2;
-        v[j] = __float_as_uint(x);
-        if ((mask >> j) & 1u) mx = fmaxf(mx, x);
+      for (int j = 0; j < 16; ++j) {
+        const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + j * (kM * 16) + r * 16);
+        const float x0 = (__uint_as_float(v[4 * j]) + o.x) * p.scale_log2, x1 = (__uint_as_float(v[4 * j + 1]) + o.y) * p.scale_log2;
+        const float x2 = (__uint_as_float(v[4 * j + 2]) + o.z) * p.scale_log2, x3 = (__uint_as_float(v[4 * j + 3]) + o.w) * p.scale_log2;
+        v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
+        if ((mask >> (4 * j)) & 1ull) mx = fmaxf(mx, x0);
+        if ((mask >> (4 * j + 1)) & 1ull) mx = fmaxf(mx, x1);
+        if ((mask >> (4 * j + 2)) & 1ull) mx = fmaxf(mx, x2);
+        if ((mask >> (4 * j + 3)) & 1ull) mx = fmaxf(mx, x3);
       }
-      // lazy rescale: keep the old reference maximum unless the new one is far above it
+      mbar_arrive_cluster(peer_x_empty + sb * 8);
+      // ---- online softmax with a lazily updated reference maximum ----
       float factor = 1.f;
       if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
         factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
         m_used = mx;
       }
+      // P buffer free and O quiescent once the PV MMAs of the previous tile are done
+      if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, p.status)) { ok = false; break; }
       if (it > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+        tc_fence_after();
         uint32_t o[32];
 #pragma unroll 1
         for (int cc = 0; cc < kHalfDV / 32; ++cc) {
@@ -277,35 +349,37 @@ __global__ void __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(cons
       }
       l *= factor;
       float sum = 0.f;
-      uint32_t pk[16];
+      uint8_t* prow = smem + kOffP;
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float p0 = ((mask >> j) & 1u) ? exp2f(__uint_as_float(v[j]) - m_used) : 0.f;
-        const float p1 = ((mask >> (j + 1)) & 1u) ? exp2f(__uint_as_float(v[j + 1]) - m_used) : 0.f;
-        sum += p0 + p1;
-        pk[j >> 1] = pack2<kBF16>(p0, p1);
+      for (int g = 0; g < 8; ++g) {  // 8 keys -> one 16-byte unit of row r
+        uint32_t pk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = 8 * g + 2 * j;
+          const float p0 = ((mask >> c) & 1ull) ? exp2f(__uint_as_float(v[c]) - m_used) : 0.f;
+          const float p1 = ((mask >> (c + 1)) & 1ull) ? exp2f(__uint_as_float(v[c + 1]) - m_used) : 0.f;
+          sum += p0 + p1;
+          pk[j] = pack2<kBF16>(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(prow + sw128_offset(r, g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l += sum;
-      // P[128 x 32], K-major without swizzle: 8x16-byte core matrices, 128 B apart along K, 512 B apart along M
-      uint8_t* prow = smem + kOffP + (r >> 3) * 512 + (r & 7) * 16;
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        *reinterpret_cast<uint4*>(prow + g * 128) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
     }
     // ---- epilogue ----
     const int h = h0 + r;
-    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + half * kHalfDV;
-    if (nvt == 0) {
+    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
+    if (run && nvt == 0) {
       if (h < p.H) {
         for (int j = 0; j < kHalfDV / 8; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
-        if (half == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+        if (rank == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
       }
-    } else if (ok && mbar_wait(o_full, 0, p.status)) {
+    } else if (run && ok && mbar_wait(pv_done, (nvt - 1) & 1, p.status)) {
       tc_fence_after();
       const float inv_l = 1.f / l;
+      uint32_t v[32];
 #pragma unroll 1
       for (int cc = 0; cc < kHalfDV / 32; ++cc) {
         tmem_ld32(tO + lane_base + cc * 32, v);
@@ -322,15 +396,16 @@ __global__ void __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(cons
           }
         }
       }
-      if (half == 0 && p.lse && h < p.H)
+      if (rank == 0 && p.lse && h < p.H)
         p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
     }
   }
 
-  // ---- teardown: every role comes here, also after a failed wait ------------------------------------
+  // ---- teardown: every thread of both CTAs comes here, also after a failed wait -----------------------
   tc_fence_before();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+  cluster_sync_all();  // no CTA leaves while its peer may still write into its shared memory
 }
 
 // -------------------------------------------------------------------------------------------------
