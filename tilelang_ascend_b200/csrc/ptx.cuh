@@ -110,6 +110,26 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, fl
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same without memory ordering: enough for a "buffer consumed" credit, whose only requirement is that this
+// thread's earlier loads have completed (their values are already in registers when the arrive issues).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Asynchronous 16-byte store into another CTA's shared memory; on landing it subtracts 16 from the
+// transaction count of the mbarrier at `cluster_mbar` (same CTA as the data).  No fence is needed.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t cluster_mbar, float a, float b, float c, float d) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(cluster_mbar)
+               : "memory");
+}
+// Local arrive (count 1) that also adds `tx_bytes` to the barrier's expected transaction count.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t tx_bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(tx_bytes) : "memory");
+}
+// Named barrier over `nthreads` threads of the CTA (id 1..15; id 0 is __syncthreads).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 // Barrier over all threads of all CTAs of the cluster (every thread must execute it).
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

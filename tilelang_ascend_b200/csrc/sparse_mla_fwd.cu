@@ -97,14 +97,31 @@ constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
 constexpr uint32_t kOffP = kOffQRope + kQRopeBytes;               // 139264
 constexpr uint32_t kOffX = kOffP + kPBytes;                       // 155648
 constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 221184
-constexpr uint32_t kOffMask = kOffBar + 256;
+constexpr uint32_t kOffPair = kOffBar + 512;                      // row maxima exchanged between the two column halves
+constexpr uint32_t kOffMask = kOffPair + 2 * 256 * 4;
 constexpr uint32_t kOffList = kOffMask + kMaxTiles * 8;
 constexpr uint32_t kSmemBytes = kOffList + kMaxTiles * 2 + 1024;  // + slack to align the base to 1024 B
-constexpr int kThreads = 288;                         // 4 softmax warps, 1 MMA warp, 4 gather warps
+constexpr int kSoftmaxWarps = 8;                      // warp w: rows 32 (w & 3) .. +31, score columns 32 (w >> 2) .. +31
+constexpr int kMmaWarp = 8;
+constexpr int kFirstGatherWarp = 9;
+constexpr int kThreads = 416;                         // 8 softmax warps, 1 MMA warp, 4 gather warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
 }  // namespace tc
+
+// Optional timeline of one cluster (compile with -DDSA_TRACE): clock64 at the hand-over points of the three
+// roles, [role][event][tile] in a buffer set through dsa_debug_set_trace.  Not part of normal builds.
+#ifdef DSA_TRACE
+__device__ long long* g_trace = nullptr;
+#define DSA_TRACE_AT(role, ev, it)                                                                      \
+  do {                                                                                                  \
+    if (g_trace && blockIdx.y == gridDim.y - 1 && blockIdx.z == 0 && rank == 0 && (it) < 64)           \
+      g_trace[((role) * 8 + (ev)) * 64 + (it)] = clock64();                                             \
+  } while (0)
+#else
+#define DSA_TRACE_AT(role, ev, it) do {} while (0)
+#endif
 
 template <bool kBF16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(const FwdParams p) {
@@ -117,14 +134,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   uint64_t* kv_full = bars;         // [3] count 128: cp.async completion of the gather threads
   uint64_t* kv_empty = bars + 3;    // [3] count 1: commit after the PV MMAs of the stage
   uint64_t* s_full = bars + 6;      // [2] count 1: commit after the QK MMAs
-  uint64_t* s_empty = bars + 8;     // [2] count 128: softmax threads read the partial scores
-  uint64_t* p_full = bars + 10;     // count 128: softmax threads wrote P
+  uint64_t* s_empty = bars + 8;     // [2] count 8: one elected lane per softmax warp, scores read
+  uint64_t* p_full = bars + 10;     // count 8: softmax warps wrote P
   uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
-  uint64_t* x_full = bars + 12;     // [2] count 128: the peer's partial scores arrived here
-  uint64_t* x_empty = bars + 14;    // [2] count 128: the peer consumed what this CTA sent
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  int* n_valid_tiles = reinterpret_cast<int*>(bars + 17);
-  int* start_status = reinterpret_cast<int*>(bars + 18);
+  uint64_t* x_full = bars + 12;     // [2][8] count 1 + 4096 transaction bytes: the peer warp's partial scores landed here
+  uint64_t* x_empty = bars + 28;    // [2][8] count 1: the peer warp consumed what this warp sent
+  uint64_t* pair_bar = bars + 44;   // [4] count 2: the two warps that share 32 rows exchanged their row maxima
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 48);
+  int* n_valid_tiles = reinterpret_cast<int*>(bars + 49);
+  int* start_status = reinterpret_cast<int*>(bars + 50);
+  float* pair = reinterpret_cast<float*>(smem + kOffPair);  // [2][256]
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint16_t* tile_list = reinterpret_cast<uint16_t*>(smem + kOffList);
 
@@ -141,15 +160,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   if (tid == 0) {
     *start_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
-      mbar_init(&x_full[i], 128); mbar_init(&x_empty[i], 128);
-    }
-    mbar_init(p_full, 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], kSoftmaxWarps); }
+    for (int i = 0; i < 16; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     mbar_init_fence();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -184,20 +202,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tO = tmem_base + kColO, tS = tmem_base + kColS, tQ = tmem_base + kColQ;
-  if (tid == 0) {  // compact list of tiles with at least one key taking part
+  if (tid == kMmaWarp * 32) {  // compact list of tiles with at least one key taking part
     int n = 0;
     for (int tile = 0; tile < ntiles; ++tile)
       if (masks[tile] != 0ull) tile_list[n++] = static_cast<uint16_t>(tile);
     *n_valid_tiles = n;
   }
-  if (warp < 4) {  // staging -> TMEM: lane = head row, column c holds dims (2c, 2c+1) of the CTA's latent slice
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  if (warp < kSoftmaxWarps) {
+    // staging -> TMEM: lane = head row, column c holds dims (2c, 2c+1) of the CTA's latent slice;
+    // warp w moves columns 64 (w >> 2) .. +63 of rows 32 (w & 3) .. +31
+    const int r = (warp & 3) * 32 + lane, ch = warp >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
 #pragma unroll 1
-    for (int cc = 0; cc < 4; ++cc) {
+    for (int cc = 2 * ch; cc < 2 * ch + 2; ++cc) {
       uint32_t w[32];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint4 v = *reinterpret_cast<const uint4*>(smem + tid * 512 + (((cc * 8 + j) ^ (tid & 31)) << 4));
+        const uint4 v = *reinterpret_cast<const uint4*>(smem + r * 512 + (((cc * 8 + j) ^ (r & 31)) << 4));
         w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
       }
       tmem_st32(tQ + lane_base + cc * 32, w);
@@ -213,13 +234,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   const int nvt = run ? *n_valid_tiles : 0;
   bool ok = true;
 
-  if (warp >= 5) {
+  if (warp >= kFirstGatherWarp) {
     // ================================ gather producers =============================================
-    const int pw = warp - 5;  // keys [16 pw, 16 pw + 16) of every tile
+    const int pw = warp - kFirstGatherWarp;  // keys [16 pw, 16 pw + 16) of every tile
+    const bool tracer = tid == kFirstGatherWarp * 32;
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
     for (int it = 0; it < nvt; ++it) {
       const int tile = tile_list[it], s = it % kStages;
+      if (tracer) DSA_TRACE_AT(0, 0, it);
       if (it >= kStages && !mbar_wait(&kv_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
+      if (tracer) DSA_TRACE_AT(0, 1, it);
       const uint32_t stage = sBase + s * kStageBytes;
       const int slot = tile * kBK + pw * 16 + (lane & 15);
       const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
@@ -236,9 +260,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           cp_async16(stage + 4 * kChunkBytes + sw128_offset(key, 4 * rank + lane), base + 1024 + (4 * rank + lane) * 16, v ? 16u : 0u);
       }
       cp_async_arrive_noinc(&kv_full[s]);
+      if (tracer) DSA_TRACE_AT(0, 2, it);
     }
     cp_async_wait<0>();
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ====================================================
     if (lane == 0 && nvt > 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
@@ -247,85 +272,107 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       auto issue_qk = [&](int it) -> bool {
         const int s = it % kStages, sb = it & 1;
         const uint32_t stage = sBase + s * kStageBytes;
+        DSA_TRACE_AT(1, 0, it);
         if (!mbar_wait(&kv_full[s], (it / kStages) & 1, p.status)) return false;
+        DSA_TRACE_AT(1, 1, it);
         if (it >= 2 && !mbar_wait(&s_empty[sb], ((it >> 1) + 1) & 1, p.status)) return false;
+        DSA_TRACE_AT(1, 2, it);
         fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
+        const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t db = make_smem_desc(stage + c * kChunkBytes + k * 32, 16, 1024, kSwizzle128B);
-            umma_ts(tS + sb * kBK, tQ + (c * 4 + k) * 8, db, idesc_qk, (c | k) != 0);
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_ts(tS + sb * kBK, tQ + (c * 4 + k) * 8, db0 + ((c * kChunkBytes + k * 32) >> 4), idesc_qk, (c | k) != 0);
         }
+        const uint64_t da0 = make_smem_desc(sQRope, 16, 1024, kSwizzle128B);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint32_t off = (2 * rank + k) * 32;
-          const uint64_t da = make_smem_desc(sQRope + off, 16, 1024, kSwizzle128B);
-          const uint64_t db = make_smem_desc(stage + 4 * kChunkBytes + off, 16, 1024, kSwizzle128B);
-          umma_ss(tS + sb * kBK, da, db, idesc_qk, 1);
+          umma_ss(tS + sb * kBK, da0 + (off >> 4), db0 + ((4 * kChunkBytes + off) >> 4), idesc_qk, 1);
         }
         umma_commit(&s_full[sb]);
+        DSA_TRACE_AT(1, 3, it);
         return true;
       };
       ok = issue_qk(0);
       for (int it = 0; ok && it < nvt; ++it) {
         if (it + 1 < nvt && !issue_qk(it + 1)) { ok = false; break; }
         if (!mbar_wait(p_full, it & 1, p.status)) { ok = false; break; }
+        DSA_TRACE_AT(1, 4, it);
         tc_fence_after();
         // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P K-major, V MN-major (this CTA's latent dims)
         const uint32_t stage = sBase + (it % kStages) * kStageBytes;
+        const uint64_t da0 = make_smem_desc(sP, 16, 1024, kSwizzle128B);
+        const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks) {
-          const uint64_t da = make_smem_desc(sP + ks * 32, 16, 1024, kSwizzle128B);
-          const uint64_t db = make_smem_desc(stage + ks * 2048, kChunkBytes, 1024, kSwizzle128B);
-          umma_ss(tO, da, db, idesc_pv, (it | ks) != 0);
-        }
+        for (int ks = 0; ks < kBK / 16; ++ks) umma_ss(tO, da0 + ((ks * 32) >> 4), db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
         umma_commit(&kv_empty[it % kStages]);
         umma_commit(pv_done);
+        DSA_TRACE_AT(1, 5, it);
       }
     }
   } else {
     // ================================ softmax + epilogue ============================================
-    const int r = tid;  // TMEM lane = head row
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // thread = (row r, column half ch): r = TMEM lane, ch selects 32 of the tile's 64 score columns
+    const int q4 = warp & 3, ch = warp >> 2;
+    const int r = q4 * 32 + lane;
+    const bool tracer = tid == 0;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x = map_to_cta(sX, peer);
     const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
     float m_used = -INFINITY, l = 0.f;
     for (int it = 0; it < nvt; ++it) {
-      const unsigned long long mask = masks[tile_list[it]];
+      const uint32_t mask = static_cast<uint32_t>(masks[tile_list[it]] >> (32 * ch));
       const int sb = it & 1;
-      uint32_t v[64];
-      if (!mbar_wait(&s_full[sb], (it >> 1) & 1, p.status)) { ok = false; break; }
+      const int xw = sb * 8 + warp;  // exchange barriers are per (buffer, warp): a warp only touches its rows and columns
+      uint32_t v[32];
+      if (tracer) DSA_TRACE_AT(2, 0, it);
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (it >> 1) & 1, p.status))) { ok = false; break; }
+      if (tracer) DSA_TRACE_AT(2, 1, it);
       tc_fence_after();
-      tmem_ld32(tS + sb * kBK + lane_base, v);
-      tmem_ld32(tS + sb * kBK + lane_base + 32, v + 32);
+      tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, v);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(&s_empty[sb]);
-      // ---- exchange partial scores with the peer CTA (row r, 16 units of 4 floats; unit-major layout) ----
-      if (it >= 2 && !mbar_wait_cluster(&x_empty[sb], ((it >> 1) + 1) & 1, p.status)) { ok = false; break; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (tracer) DSA_TRACE_AT(2, 2, it);
+      // ---- exchange partial scores with the peer CTA: 16-byte units, layout [unit][row] ----
+      if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait(&x_empty[xw], ((it >> 1) + 1) & 1, p.status))) { ok = false; break; }
+      if (lane == 0) mbar_arrive_expect_tx(&x_full[xw], 32 * 128);  // arm this warp's receive barrier for the tile
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        st_cluster_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-      mbar_arrive_cluster(peer_x_full + sb * 8);
-      if (!mbar_wait_cluster(&x_full[sb], (it >> 1) & 1, p.status)) { ok = false; break; }
+      for (int j = 0; j < 8; ++j)
+        st_async_v4(peer_x + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16, peer_x_full + xw * 8, __uint_as_float(v[4 * j]),
+                    __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      if (tracer) DSA_TRACE_AT(2, 3, it);
+      if (!__all_sync(0xffffffffu, mbar_wait(&x_full[xw], (it >> 1) & 1, p.status))) { ok = false; break; }
+      if (tracer) DSA_TRACE_AT(2, 4, it);
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + j * (kM * 16) + r * 16);
-        const float x0 = (__uint_as_float(v[4 * j]) + o.x) * p.scale_log2, x1 = (__uint_as_float(v[4 * j + 1]) + o.y) * p.scale_log2;
-        const float x2 = (__uint_as_float(v[4 * j + 2]) + o.z) * p.scale_log2, x3 = (__uint_as_float(v[4 * j + 3]) + o.w) * p.scale_log2;
+      for (int j = 0; j < 8; ++j) {
+        const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16);
+        const float x0 = __uint_as_float(v[4 * j]) + o.x, x1 = __uint_as_float(v[4 * j + 1]) + o.y;
+        const float x2 = __uint_as_float(v[4 * j + 2]) + o.z, x3 = __uint_as_float(v[4 * j + 3]) + o.w;
         v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
-        if ((mask >> (4 * j)) & 1ull) mx = fmaxf(mx, x0);
-        if ((mask >> (4 * j + 1)) & 1ull) mx = fmaxf(mx, x1);
-        if ((mask >> (4 * j + 2)) & 1ull) mx = fmaxf(mx, x2);
-        if ((mask >> (4 * j + 3)) & 1ull) mx = fmaxf(mx, x3);
       }
-      mbar_arrive_cluster(peer_x_empty + sb * 8);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + xw * 8);
+      if (mask == 0xffffffffu) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(v[j]));
+      }
+      // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory
+      pair[(it & 1) * 256 + tid] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[q4]);
+      if (!__all_sync(0xffffffffu, mbar_wait(&pair_bar[q4], it & 1, p.status))) { ok = false; break; }
+      mx = fmaxf(mx, pair[(it & 1) * 256 + (tid ^ 128)]) * p.scale_log2;
       // ---- online softmax with a lazily updated reference maximum ----
       float factor = 1.f;
       if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
@@ -333,12 +380,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         m_used = mx;
       }
       // P buffer free and O quiescent once the PV MMAs of the previous tile are done
-      if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1, p.status)) { ok = false; break; }
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (it - 1) & 1, p.status))) { ok = false; break; }
+      if (tracer) DSA_TRACE_AT(2, 5, it);
       if (it > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
         tc_fence_after();
         uint32_t o[32];
 #pragma unroll 1
-        for (int cc = 0; cc < kHalfDV / 32; ++cc) {
+        for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {  // this thread's half of the output columns
           tmem_ld32(tO + lane_base + cc * 32, o);
           tmem_wait_ld();
 #pragma unroll
@@ -349,39 +397,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       }
       l *= factor;
       float sum = 0.f;
-      uint8_t* prow = smem + kOffP;
+      const float neg_m = -m_used;
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {  // 8 keys -> one 16-byte unit of row r
+      for (int g = 0; g < 4; ++g) {  // 8 keys -> one 16-byte unit of row r
         uint32_t pk[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int c = 8 * g + 2 * j;
-          const float p0 = ((mask >> c) & 1ull) ? exp2f(__uint_as_float(v[c]) - m_used) : 0.f;
-          const float p1 = ((mask >> (c + 1)) & 1ull) ? exp2f(__uint_as_float(v[c + 1]) - m_used) : 0.f;
+          float p0 = exp2f(fmaf(__uint_as_float(v[c]), p.scale_log2, neg_m));
+          float p1 = exp2f(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, neg_m));
+          if (mask != 0xffffffffu) {
+            p0 = ((mask >> c) & 1u) ? p0 : 0.f;
+            p1 = ((mask >> (c + 1)) & 1u) ? p1 : 0.f;
+          }
           sum += p0 + p1;
           pk[j] = pack2<kBF16>(p0, p1);
         }
-        *reinterpret_cast<uint4*>(prow + sw128_offset(r, g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(smem + kOffP + sw128_offset(r, 4 * ch + g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l += sum;
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      if (tracer) DSA_TRACE_AT(2, 6, it);
     }
-    // ---- epilogue ----
+    // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
+    // row sum = sum of the two column halves, exchanged like the maxima
+    if (ok && nvt > 0) {
+      pair[(nvt & 1) * 256 + tid] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[q4]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&pair_bar[q4], nvt & 1, p.status));
+      l += pair[(nvt & 1) * 256 + (tid ^ 128)];
+    }
     const int h = h0 + r;
     T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
     if (run && nvt == 0) {
       if (h < p.H) {
-        for (int j = 0; j < kHalfDV / 8; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
-        if (rank == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+        for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
+        if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
       }
-    } else if (run && ok && mbar_wait(pv_done, (nvt - 1) & 1, p.status)) {
+    } else if (run && ok && __all_sync(0xffffffffu, mbar_wait(pv_done, (nvt - 1) & 1, p.status))) {
       tc_fence_after();
       const float inv_l = 1.f / l;
       uint32_t v[32];
 #pragma unroll 1
-      for (int cc = 0; cc < kHalfDV / 32; ++cc) {
+      for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
         tmem_ld32(tO + lane_base + cc * 32, v);
         tmem_wait_ld();
         if (h < p.H) {
@@ -396,7 +458,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           }
         }
       }
-      if (rank == 0 && p.lse && h < p.H)
+      if (rank == 0 && ch == 0 && p.lse && h < p.H)
         p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
     }
   }
@@ -404,7 +466,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   // ---- teardown: every thread of both CTAs comes here, also after a failed wait -----------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   cluster_sync_all();  // no CTA leaves while its peer may still write into its shared memory
 }
 
@@ -520,5 +582,11 @@ int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t st
     sparse_mla_fwd_generic_kernel<__half><<<grid, 256, smem, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifdef DSA_TRACE
+extern "C" int dsa_debug_set_trace(long long* buf) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)));
+}
+#endif
 
 }  // namespace dsa
