@@ -82,6 +82,28 @@ int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t 
                           int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
                           void* stream);
 
+/* Size in bytes of the scratch array built into the library image (per GPU, held until the process exits). */
+#define DSA_NOALLOC_SCRATCH_BYTES (32u << 20)
+size_t dsa_lightning_indexer_noalloc_max_bytes(void);
+
+/* dsa_lightning_indexer for callers that cannot allocate device memory -- a process whose own pool already owns
+ * all free GPU memory, or a loop that cannot take the device-wide synchronisation an allocation may cause.
+ * NO COUNTERPART IN THE REFERENCE (its adapter allocates workspaces with torch.empty on every call).
+ * Same arguments and results as dsa_lightning_indexer, minus the workspace: scores and per-row limits live in
+ * a DSA_NOALLOC_SCRATCH_BYTES array inside the library, and the kernels' status word too (this entry point
+ * never calls cudaMalloc / cudaFree and creates no status word of its own).  status_out: device int32 or NULL;
+ * receives the status word of this call (0 = ok) in stream order -- dsa_kernel_status does not see it.
+ * Limits: 256 + round256(4 B S1) + 4 B S1 S2 bytes must fit the array, otherwise the call fails with a
+ * message and launches nothing.  The first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress) with that device current: make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the previous call's contents (the call clears the
+ * status word itself; nothing else needs to start at zero).  Two calls that overlap on the GPU -- different
+ * streams, or different host threads -- race on it: serialise them. */
+int dsa_lightning_indexer_noalloc(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2,
+                                  int32_t N1, int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b,
+                                  const int32_t* k_len_b, int32_t top_k, int32_t* out_idx, float* out_val,
+                                  int32_t* status_out, void* stream);
+
 /* Sparse MLA forward.  q [B,S,H,D], kv [B,S_kv,1,D] (or [num_blocks,block_size,1,D] with a block
  * table), indices [B,S,1,topk] int32, out [B,S,H,DV] (dtype), lse [B,S,H] fp32 or NULL.
  * An index takes part iff 0 <= idx < kv_len and (not causal or idx <= q_start + t); -1 and S_kv are

@@ -27,6 +27,15 @@ namespace {
 
 thread_local std::string g_last_error;
 
+}  // namespace
+
+namespace dsa {
+// Lets the other translation units of the library report through dsa_get_last_error().
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace dsa
+
+namespace {
+
 int fail(const std::string& msg) {
   g_last_error = msg;
   return 1;
