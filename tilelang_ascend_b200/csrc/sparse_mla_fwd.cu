@@ -91,12 +91,10 @@ constexpr int kMaxTiles = 128;                        // topk <= 8192
 constexpr uint32_t kChunkBytes = kBK * 128;           // 8192: 64 keys x 64 dims, 128-byte swizzle
 constexpr uint32_t kStageBytes = 5 * kChunkBytes;     // 4 latent chunks + the rope chunk (half of each row in use)
 constexpr uint32_t kQRopeBytes = kM * 128;            // Q rope dims, same half-used row layout
-constexpr uint32_t kPBytes = kM * 128;                // P [128 x 64] bf16
 constexpr uint32_t kXBytes = kM * kBK * 4;            // peer's partial scores [128 x 64] fp32
 constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
-constexpr uint32_t kOffP = kOffQRope + kQRopeBytes;               // 139264
-constexpr uint32_t kOffX = kOffP + kPBytes;                       // 155648
-constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 221184
+constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 139264
+constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 204800
 constexpr uint32_t kOffPair = kOffBar + 512;                      // row maxima exchanged between the two column halves
 constexpr uint32_t kOffMask = kOffPair + 2 * 256 * 4;
 constexpr uint32_t kOffList = kOffMask + kMaxTiles * 8;
@@ -104,9 +102,11 @@ constexpr uint32_t kSmemBytes = kOffList + kMaxTiles * 2 + 1024;  // + slack to 
 constexpr int kSoftmaxWarps = 8;                      // warp w: rows 32 (w & 3) .. +31, score columns 32 (w >> 2) .. +31
 constexpr int kMmaWarp = 8;
 constexpr int kFirstGatherWarp = 9;
-constexpr int kThreads = 416;                         // 8 softmax warps, 1 MMA warp, 4 gather warps
+constexpr int kFirstExchangeWarp = 13;                // warp w sends rows 32 (w & 3) .. +31 of the partial scores to the peer
+constexpr int kThreads = 544;                         // 8 softmax warps, 1 MMA warp, 4 gather warps, 4 exchange warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
+// P (bf16, 32 columns) overwrites the first half of its tile's score buffer once every reader of the scores is done
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
 }  // namespace tc
 
@@ -129,17 +129,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sBase = smem_u32(smem);
-  const uint32_t sQRope = sBase + kOffQRope, sP = sBase + kOffP, sX = sBase + kOffX;
+  const uint32_t sQRope = sBase + kOffQRope, sX = sBase + kOffX;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
   uint64_t* kv_full = bars;         // [3] count 128: cp.async completion of the gather threads
   uint64_t* kv_empty = bars + 3;    // [3] count 1: commit after the PV MMAs of the stage
   uint64_t* s_full = bars + 6;      // [2] count 1: commit after the QK MMAs
-  uint64_t* s_empty = bars + 8;     // [2] count 8: one elected lane per softmax warp, scores read
-  uint64_t* p_full = bars + 10;     // count 8: softmax warps wrote P
+  uint64_t* s_read = bars + 8;      // [2] count 4: the exchange warps have read the partial scores out of TMEM
+  uint64_t* p_full = bars + 10;     // count 8: softmax warps wrote P into TMEM
   uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
-  uint64_t* x_full = bars + 12;     // [2][8] count 1 + 4096 transaction bytes: the peer warp's partial scores landed here
-  uint64_t* x_empty = bars + 28;    // [2][8] count 1: the peer warp consumed what this warp sent
-  uint64_t* pair_bar = bars + 44;   // [4] count 2: the two warps that share 32 rows exchanged their row maxima
+  uint64_t* x_full = bars + 12;     // [2][4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
+  uint64_t* x_empty = bars + 28;    // [2][4] count 2: both peer softmax warps of these rows consumed what this CTA sent
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 48);
   int* n_valid_tiles = reinterpret_cast<int*>(bars + 49);
   int* start_status = reinterpret_cast<int*>(bars + 50);
@@ -157,12 +156,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
 
   // ---- setup ------------------------------------------------------------------------------------------
+  if (tid == 0) DSA_TRACE_AT(0, 3, 0);
   if (tid == 0) {
     *start_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], kSoftmaxWarps); }
-    for (int i = 0; i < 16; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_read[i], 4); }
+    for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 2); }
     mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     mbar_init_fence();
@@ -200,6 +199,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) DSA_TRACE_AT(0, 4, 0);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tO = tmem_base + kColO, tS = tmem_base + kColS, tQ = tmem_base + kColQ;
   if (tid == kMmaWarp * 32) {  // compact list of tiles with at least one key taking part
@@ -230,11 +230,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   tc_fence_after();
   // both CTAs must have their barriers initialised before any remote arrive; every thread takes part
   cluster_sync_all();
+  if (tid == 0) DSA_TRACE_AT(0, 5, 0);
   const bool run = *start_status == kStatusOk && ctx.active;
   const int nvt = run ? *n_valid_tiles : 0;
   bool ok = true;
 
-  if (warp >= kFirstGatherWarp) {
+  if (warp >= kFirstExchangeWarp) {
+    // ================================ score exchange ================================================
+    // Sends this CTA's partial scores of 32 rows x 64 keys to the peer as soon as the QK MMAs of a tile are done,
+    // in 16-byte units laid out [unit][row]; the data lands through st.async, which also signals the peer's barrier.
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t peer_x = map_to_cta(sX, peer);
+    const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
+    for (int it = 0; it < nvt; ++it) {
+      const int sb = it & 1, xq = sb * 4 + q4;
+      uint32_t v[64];
+      if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (it >> 1) & 1, p.status))) { ok = false; break; }
+      tc_fence_after();
+      tmem_ld32(tS + sb * kBK + lane_base, v);
+      tmem_ld32(tS + sb * kBK + 32 + lane_base, v + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_read[sb]);
+      if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((it >> 1) + 1) & 1, p.status))) { ok = false; break; }
+      if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        st_async_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
+                    __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+    }
+  } else if (warp >= kFirstGatherWarp) {
     // ================================ gather producers =============================================
     const int pw = warp - kFirstGatherWarp;  // keys [16 pw, 16 pw + 16) of every tile
     const bool tracer = tid == kFirstGatherWarp * 32;
@@ -242,7 +270,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     for (int it = 0; it < nvt; ++it) {
       const int tile = tile_list[it], s = it % kStages;
       if (tracer) DSA_TRACE_AT(0, 0, it);
-      if (it >= kStages && !mbar_wait(&kv_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
+      if (it >= kStages && !mbar_wait<true>(&kv_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
       if (tracer) DSA_TRACE_AT(0, 1, it);
       const uint32_t stage = sBase + s * kStageBytes;
       const int slot = tile * kBK + pw * 16 + (lane & 15);
@@ -275,7 +303,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         DSA_TRACE_AT(1, 0, it);
         if (!mbar_wait(&kv_full[s], (it / kStages) & 1, p.status)) return false;
         DSA_TRACE_AT(1, 1, it);
-        if (it >= 2 && !mbar_wait(&s_empty[sb], ((it >> 1) + 1) & 1, p.status)) return false;
+        // the score buffer is free: its last readers (softmax, exchange warps) finished before P of tile it-2 was
+        // written, and the PV MMAs that read that P were issued before this point (MMAs execute in issue order)
         DSA_TRACE_AT(1, 2, it);
         fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
@@ -302,12 +331,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         if (!mbar_wait(p_full, it & 1, p.status)) { ok = false; break; }
         DSA_TRACE_AT(1, 4, it);
         tc_fence_after();
-        // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P K-major, V MN-major (this CTA's latent dims)
+        // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major
         const uint32_t stage = sBase + (it % kStages) * kStageBytes;
-        const uint64_t da0 = make_smem_desc(sP, 16, 1024, kSwizzle128B);
         const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks) umma_ss(tO, da0 + ((ks * 32) >> 4), db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
+        for (int ks = 0; ks < kBK / 16; ++ks)
+          umma_ts(tO, tS + (it & 1) * kBK + ks * 8, db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
         umma_commit(&kv_empty[it % kStages]);
         umma_commit(pv_done);
         DSA_TRACE_AT(1, 5, it);
@@ -320,34 +349,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     const int r = q4 * 32 + lane;
     const bool tracer = tid == 0;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-    const uint32_t peer_x = map_to_cta(sX, peer);
-    const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
     float m_used = -INFINITY, l = 0.f;
+    // A failed wait clears `ok` but does not leave the loop: the two warps of a row block meet at a named barrier
+    // every tile, so both keep walking the tiles (without further waits worth mentioning) to the end.
     for (int it = 0; it < nvt; ++it) {
       const uint32_t mask = static_cast<uint32_t>(masks[tile_list[it]] >> (32 * ch));
       const int sb = it & 1;
-      const int xw = sb * 8 + warp;  // exchange barriers are per (buffer, warp): a warp only touches its rows and columns
+      const int xq = sb * 4 + q4;  // exchange barriers are per (buffer, 32-row block)
       uint32_t v[32];
       if (tracer) DSA_TRACE_AT(2, 0, it);
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (it >> 1) & 1, p.status))) { ok = false; break; }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (it >> 1) & 1, p.status));
       if (tracer) DSA_TRACE_AT(2, 1, it);
       tc_fence_after();
       tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, v);
       tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
       if (tracer) DSA_TRACE_AT(2, 2, it);
-      // ---- exchange partial scores with the peer CTA: 16-byte units, layout [unit][row] ----
-      if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait(&x_empty[xw], ((it >> 1) + 1) & 1, p.status))) { ok = false; break; }
-      if (lane == 0) mbar_arrive_expect_tx(&x_full[xw], 32 * 128);  // arm this warp's receive barrier for the tile
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        st_async_v4(peer_x + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16, peer_x_full + xw * 8, __uint_as_float(v[4 * j]),
-                    __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-      if (tracer) DSA_TRACE_AT(2, 3, it);
-      if (!__all_sync(0xffffffffu, mbar_wait(&x_full[xw], (it >> 1) & 1, p.status))) { ok = false; break; }
+      // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[xq], (it >> 1) & 1, p.status));
       if (tracer) DSA_TRACE_AT(2, 4, it);
       float mx = -INFINITY;
 #pragma unroll
@@ -357,21 +376,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const float x2 = __uint_as_float(v[4 * j + 2]) + o.z, x3 = __uint_as_float(v[4 * j + 3]) + o.w;
         v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + xw * 8);
+      if (tracer) DSA_TRACE_AT(3, 0, it);
       if (mask == 0xffffffffu) {
+        float m4[4];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+        for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 4]));
+#pragma unroll
+        for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(v[j]));
       }
-      // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory
+      // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory.
+      // After this barrier both warps have also finished reading the scores of the tile (TMEM and exchange buffer).
+      if (tracer) DSA_TRACE_AT(3, 2, it);
       pair[(it & 1) * 256 + tid] = mx;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&pair_bar[q4]);
-      if (!__all_sync(0xffffffffu, mbar_wait(&pair_bar[q4], it & 1, p.status))) { ok = false; break; }
+      named_bar_sync(1 + q4, 64);
+      if (tracer) DSA_TRACE_AT(3, 3, it);
+      if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + xq * 8);  // one credit per warp: peer may overwrite these rows
       mx = fmaxf(mx, pair[(it & 1) * 256 + (tid ^ 128)]) * p.scale_log2;
       // ---- online softmax with a lazily updated reference maximum ----
       float factor = 1.f;
@@ -379,10 +403,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
         m_used = mx;
       }
-      // P buffer free and O quiescent once the PV MMAs of the previous tile are done
-      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (it - 1) & 1, p.status))) { ok = false; break; }
-      if (tracer) DSA_TRACE_AT(2, 5, it);
       if (it > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+        // O must be quiescent: the PV MMAs of the previous tile are done
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (it - 1) & 1, p.status));
         tc_fence_after();
         uint32_t o[32];
 #pragma unroll 1
@@ -393,30 +416,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
           tmem_st32(tO + lane_base + cc * 32, o);
         }
-        tmem_wait_st();
       }
+      if (tracer) DSA_TRACE_AT(2, 5, it);
       l *= factor;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_used;
+      uint32_t pk[16];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {  // 8 keys -> one 16-byte unit of row r
-        uint32_t pk[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int c = 8 * g + 2 * j;
-          float p0 = exp2f(fmaf(__uint_as_float(v[c]), p.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, neg_m));
-          if (mask != 0xffffffffu) {
-            p0 = ((mask >> c) & 1u) ? p0 : 0.f;
-            p1 = ((mask >> (c + 1)) & 1u) ? p1 : 0.f;
-          }
-          sum += p0 + p1;
-          pk[j] = pack2<kBF16>(p0, p1);
+      for (int j = 0; j < 16; ++j) {
+        float p0 = exp2f(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, neg_m));
+        float p1 = exp2f(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, neg_m));
+        if (mask != 0xffffffffu) {
+          p0 = ((mask >> (2 * j)) & 1u) ? p0 : 0.f;
+          p1 = ((mask >> (2 * j + 1)) & 1u) ? p1 : 0.f;
         }
-        *reinterpret_cast<uint4*>(smem + kOffP + sw128_offset(r, 4 * ch + g)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        sum4[j & 3] += p0 + p1;
+        pk[j] = pack2<kBF16>(p0, p1);
       }
-      l += sum;
-      fence_proxy_async_smem();
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (tracer) DSA_TRACE_AT(3, 4, it);
+      // P (column c = keys 2c, 2c+1) replaces the first 32 columns of this tile's score buffer; the exchange warps
+      // must have read their copy of the scores first
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_read[sb], (it >> 1) & 1, p.status));
+      tmem_st16(tS + sb * kBK + ch * 16 + lane_base, pk);
+      tmem_wait_st();
+      if (tracer) DSA_TRACE_AT(3, 5, it);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
@@ -424,11 +448,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     }
     // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
     // row sum = sum of the two column halves, exchanged like the maxima
-    if (ok && nvt > 0) {
+    if (nvt > 0) {
       pair[(nvt & 1) * 256 + tid] = l;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&pair_bar[q4]);
-      ok = __all_sync(0xffffffffu, mbar_wait(&pair_bar[q4], nvt & 1, p.status));
+      named_bar_sync(1 + q4, 64);
       l += pair[(nvt & 1) * 256 + (tid ^ 128)];
     }
     const int h = h0 + r;
@@ -464,8 +486,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   }
 
   // ---- teardown: every thread of both CTAs comes here, also after a failed wait -----------------------
+  if (tid == 0) DSA_TRACE_AT(0, 6, 0);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) DSA_TRACE_AT(0, 7, 0);
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   cluster_sync_all();  // no CTA leaves while its peer may still write into its shared memory
 }

@@ -32,7 +32,7 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 }
 
 // scores [rows, row_stride]; limits [rows] or null; out_idx [rows, top_k]; out_val [rows, top_k] or null.
-// Dynamic shared memory: n * 4 (keys) + kpow2 * 8 (sort buffer).
+// Dynamic shared memory: kpow2 * 8 (sort buffer) + n * 4 (keys) + 32 * 256 * 4 (per-warp first-digit histograms).
 __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
                                                                      const int32_t* __restrict__ limits, int top_k, int kpow2,
                                                                      int32_t* __restrict__ out_idx, float* __restrict__ out_val) {
@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
   extern __shared__ __align__(16) uint8_t smem_raw[];
   unsigned long long* sortbuf = reinterpret_cast<unsigned long long*>(smem_raw);            // [kpow2]
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(kpow2) * 8);  // [n]
+  uint32_t* whist = keys + n;                                                                // [kWarps][256]
   __shared__ uint32_t hist[256];
   __shared__ uint32_t warp_sums[kWarps];
   __shared__ uint32_t s_prefix, s_remaining, s_nvalid, s_count, s_tie_base;
@@ -49,14 +50,15 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
   const float* x = scores + static_cast<int64_t>(row) * row_stride;
   int lim = limits ? limits[row] : n;
   lim = lim < 0 ? 0 : (lim > n ? n : lim);
+  n = lim;  // entries at or beyond the limit are not candidates: none of the passes below looks at them
 
   if (tid == 0) { s_nvalid = 0; s_count = 0; s_tie_base = 0; }
-  if (tid < 256) hist[tid] = 0;
+  for (int i = tid; i < kWarps * 256; i += kThreads) whist[i] = 0;
   __syncthreads();
 
   // ---- load, convert, count candidates, first-digit histogram ---------------------------------------
   uint32_t my_valid = 0;
-  for (int base = 0; base < n; base += kThreads) {  // whole warps iterate together (full-mask match below)
+  for (int base = 0; base < n; base += kThreads) {
     const int i = base + tid;
     uint32_t k = 0;
     if (i < lim) {
@@ -64,12 +66,18 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
       if (f > -1e30f) { k = float_to_key(f); ++my_valid; }
     }
     if (i < n) keys[i] = k;  // 0 marks "not a candidate" (a real key is never 0 for a score > -1e30)
-    const uint32_t d = k ? (k >> 24) : 256u;
-    const uint32_t peers = __match_any_sync(0xffffffffu, d);
-    if (k && lane == __ffs(peers) - 1) atomicAdd(&hist[d], __popc(peers));
+    // sign + exponent bits crowd into a few bins: a private histogram per warp keeps the atomics apart
+    if (k) atomicAdd(&whist[warp * 256 + (k >> 24)], 1u);
   }
   for (int o = 16; o > 0; o >>= 1) my_valid += __shfl_xor_sync(0xffffffffu, my_valid, o);
   if (lane == 0 && my_valid) atomicAdd(&s_nvalid, my_valid);
+  __syncthreads();
+  if (tid < 256) {
+    uint32_t t = 0;
+#pragma unroll 8
+    for (int w = 0; w < kWarps; ++w) t += whist[w * 256 + tid];
+    hist[tid] = t;
+  }
   __syncthreads();
   const uint32_t nvalid = s_nvalid;
   const uint32_t kk = nvalid < static_cast<uint32_t>(top_k) ? nvalid : static_cast<uint32_t>(top_k);
@@ -90,10 +98,7 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
         for (int base = 0; base < n; base += kThreads) {
           const int i = base + tid;
           const uint32_t k = i < n ? keys[i] : 0u;
-          const bool in = k && (k & pmask) == prefix;
-          const uint32_t d = in ? ((k >> shift) & 0xffu) : 256u;
-          const uint32_t peers = __match_any_sync(0xffffffffu, d);
-          if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[d], __popc(peers));
+          if (k && (k & pmask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1u);  // few survivors, spread digits
         }
         __syncthreads();
       }
@@ -190,7 +195,7 @@ size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
   int kp = 2;
   while (kp < top_k) kp <<= 1;
   if (kpow2_out) *kpow2_out = kp;
-  return static_cast<size_t>(n) * 4 + static_cast<size_t>(kp) * 8;
+  return static_cast<size_t>(n) * 4 + static_cast<size_t>(kp) * 8 + static_cast<size_t>(topk::kWarps) * 256 * 4;
 }
 
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
