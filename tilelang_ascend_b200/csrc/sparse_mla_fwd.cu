@@ -68,7 +68,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // -------------------------------------------------------------------------------------------------
-// tcgen05 kernel: one 2-CTA cluster per (query, block of 128 heads)
+// tcgen05 kernel: persistent 2-CTA clusters, one (query, block of 128 heads) item at a time
 // -------------------------------------------------------------------------------------------------
 // TMEM (512 columns x 128 lanes) cannot hold a 128 x 512 fp32 output tile plus a score tile, so the
 // two CTAs of a cluster split the work of one query without duplicating any of it:
@@ -78,9 +78,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //     * sends S_r to its peer through distributed shared memory and adds the peer's S_(1-r),
 //     * runs the (identical) online softmax, and
 //     * accumulates O[:, 256 r : 256 r + 256] = P . V[:, its latent dims]   (output columns split).
-// Per CTA: Q latent dims live in TMEM as the A operand (no shared-memory re-read per MMA), the Q rope
-// dims and P in shared memory, KV tiles of 64 keys in a 3-stage cp.async ring, two score buffers in
-// TMEM so the QK^T of tile i+1 overlaps the softmax of tile i.
+// Per CTA: Q latent dims live in TMEM as the A operand, the Q rope dims in shared memory, KV tiles of 64
+// keys in a 3-stage cp.async ring, two score buffers in TMEM (P, as bf16, replaces the first half of its
+// tile's score buffer), so the QK^T of tile i+1 overlaps the softmax of tile i.
+//
+// The grid is one cluster per SM pair; cluster c walks the items  n-1-c, n-1-c-C, ...  (late = long queries
+// first).  Roles run ahead of each other across items: the gather warps build the next item's tile list and
+// start its KV gathers while the current item is still being reduced, the exchange warps load the next Q as
+// soon as the last QK^T of the current item is complete, and the first PV of an item only waits for the
+// previous item's output tile to be drained.  Tiles are numbered cumulatively (g) over the items of a
+// cluster; every ring buffer and barrier phase is a function of g.
 namespace tc {
 constexpr int kD = 576, kDV = 512;
 constexpr int kM = 128;                               // heads per cluster = UMMA M
@@ -95,10 +102,11 @@ constexpr uint32_t kXBytes = kM * kBK * 4;            // peer's partial scores [
 constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
 constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 139264
 constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 204800
-constexpr uint32_t kOffPair = kOffBar + 512;                      // row maxima exchanged between the two column halves
-constexpr uint32_t kOffMask = kOffPair + 2 * 256 * 4;
-constexpr uint32_t kOffList = kOffMask + kMaxTiles * 8;
-constexpr uint32_t kSmemBytes = kOffList + kMaxTiles * 2 + 1024;  // + slack to align the base to 1024 B
+constexpr uint32_t kOffPair = kOffBar + 512;                      // [3][256] floats exchanged between the two column halves
+constexpr uint32_t kOffMask = kOffPair + 3 * 256 * 4;             // [2][kMaxTiles] 64-bit validity masks (per item parity)
+constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;       // [2][kMaxTiles] 16-bit tile ids
+constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;       // [2] {tile count, run flag}
+constexpr uint32_t kSmemBytes = kOffInfo + 64 + 1024;             // + slack to align the base to 1024 B
 constexpr int kSoftmaxWarps = 8;                      // warp w: rows 32 (w & 3) .. +31, score columns 32 (w >> 2) .. +31
 constexpr int kMmaWarp = 8;
 constexpr int kFirstGatherWarp = 9;
@@ -106,22 +114,9 @@ constexpr int kFirstExchangeWarp = 13;                // warp w sends rows 32 (w
 constexpr int kThreads = 544;                         // 8 softmax warps, 1 MMA warp, 4 gather warps, 4 exchange warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
-// P (bf16, 32 columns) overwrites the first half of its tile's score buffer once every reader of the scores is done
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
+constexpr uint32_t kGatherBarrier = 5;                // named barrier of the 128 gather threads
 }  // namespace tc
-
-// Optional timeline of one cluster (compile with -DDSA_TRACE): clock64 at the hand-over points of the three
-// roles, [role][event][tile] in a buffer set through dsa_debug_set_trace.  Not part of normal builds.
-#ifdef DSA_TRACE
-__device__ long long* g_trace = nullptr;
-#define DSA_TRACE_AT(role, ev, it)                                                                      \
-  do {                                                                                                  \
-    if (g_trace && blockIdx.y == gridDim.y - 1 && blockIdx.z == 0 && rank == 0 && (it) < 64)           \
-      g_trace[((role) * 8 + (ev)) * 64 + (it)] = clock64();                                             \
-  } while (0)
-#else
-#define DSA_TRACE_AT(role, ev, it) do {} while (0)
-#endif
 
 template <bool kBF16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(const FwdParams p) {
@@ -138,358 +133,399 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   uint64_t* p_full = bars + 10;     // count 8: softmax warps wrote P into TMEM
   uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
   uint64_t* x_full = bars + 12;     // [2][4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
-  uint64_t* x_empty = bars + 28;    // [2][4] count 2: both peer softmax warps of these rows consumed what this CTA sent
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 48);
-  int* n_valid_tiles = reinterpret_cast<int*>(bars + 49);
-  int* start_status = reinterpret_cast<int*>(bars + 50);
-  float* pair = reinterpret_cast<float*>(smem + kOffPair);  // [2][256]
+  uint64_t* x_empty = bars + 20;    // [2][4] count 2: both peer softmax warps of these rows consumed what this CTA sent
+  uint64_t* info_full = bars + 28;  // [2] count 1: tile list of an item published by the gather warps
+  uint64_t* info_empty = bars + 30; // [2] count 13: MMA thread, softmax and exchange warps are done with the item's tile list
+  uint64_t* q_ready = bars + 32;    // count 4: the exchange warps put the item's Q into TMEM / shared memory
+  uint64_t* o_free = bars + 33;     // count 8: the softmax warps drained the previous item's output tile from TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
+  int* start_status = reinterpret_cast<int*>(bars + 35);
+  float* pair = reinterpret_cast<float*>(smem + kOffPair);
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint16_t* tile_list = reinterpret_cast<uint16_t*>(smem + kOffList);
+  int* info = reinterpret_cast<int*>(smem + kOffInfo);  // [2][2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();   // which half of the dims / output columns
   const uint32_t peer = rank ^ 1u;
-  const int bt = blockIdx.y;                 // flat (batch, query)
-  const int h0 = blockIdx.z * kM;            // first head of this cluster
-  const RowCtx ctx = make_row_ctx(p, bt);
+  const int num_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+  const int head_blocks = (p.H + kM - 1) / kM;
+  const int num_items = p.B * p.S * head_blocks;
   const int ntiles = (p.topk + kBK - 1) / kBK;
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  // k-th item of this cluster (late queries first), or -1
+  auto item_of = [&](int k) { const int it = num_items - 1 - cluster_id - k * num_clusters; return it; };
 
   // ---- setup ------------------------------------------------------------------------------------------
-  if (tid == 0) DSA_TRACE_AT(0, 3, 0);
   if (tid == 0) {
     *start_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_read[i], 4); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1); mbar_init(&s_read[i], 4);
+      mbar_init(&info_full[i], 1); mbar_init(&info_empty[i], 13);
+    }
     for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 2); }
     mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
+    mbar_init(q_ready, 4);
+    mbar_init(o_free, kSoftmaxWarps);
+    for (int i = 0; i < 4; ++i) info[i] = 0;
     mbar_init_fence();
   }
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  for (int tile = warp; tile < ntiles; tile += kThreads / 32) {
-    const int s0 = tile * kBK + lane, s1 = s0 + 32;
-    const int i0 = s0 < p.topk ? ctx.idx_row[s0] : -1;
-    const int i1 = s1 < p.topk ? ctx.idx_row[s1] : -1;
-    const uint32_t lo = __ballot_sync(0xffffffffu, index_valid(ctx, i0));
-    const uint32_t hi = __ballot_sync(0xffffffffu, index_valid(ctx, i1));
-    if (lane == 0) masks[tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
-  }
-  {  // Q: this CTA's 256 latent dims go to a staging area (later the KV ring), its 32 rope dims to sQRope
-    const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0) * (kD * 2);
-    for (int u = tid; u < kM * 32; u += kThreads) {
-      const int r = u >> 5, unit = u & 31;
-      const bool ok = h0 + r < p.H;
-      const uint8_t* src = ok ? qrow + static_cast<int64_t>(r) * (kD * 2) + rank * 512 + unit * 16 : reinterpret_cast<const uint8_t*>(p.q);
-      cp_async16(sBase + r * 512 + ((unit ^ (r & 31)) << 4), src, ok ? 16u : 0u);
-    }
-    for (int u = tid; u < kM * 4; u += kThreads) {
-      const int r = u >> 2, unit = 4 * rank + (u & 3);
-      const bool ok = h0 + r < p.H;
-      const uint8_t* src = ok ? qrow + static_cast<int64_t>(r) * (kD * 2) + 1024 + unit * 16 : reinterpret_cast<const uint8_t*>(p.q);
-      cp_async16(sQRope + sw128_offset(r, unit), src, ok ? 16u : 0u);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (tid == 0) DSA_TRACE_AT(0, 4, 0);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tO = tmem_base + kColO, tS = tmem_base + kColS, tQ = tmem_base + kColQ;
-  if (tid == kMmaWarp * 32) {  // compact list of tiles with at least one key taking part
-    int n = 0;
-    for (int tile = 0; tile < ntiles; ++tile)
-      if (masks[tile] != 0ull) tile_list[n++] = static_cast<uint16_t>(tile);
-    *n_valid_tiles = n;
-  }
-  if (warp < kSoftmaxWarps) {
-    // staging -> TMEM: lane = head row, column c holds dims (2c, 2c+1) of the CTA's latent slice;
-    // warp w moves columns 64 (w >> 2) .. +63 of rows 32 (w & 3) .. +31
-    const int r = (warp & 3) * 32 + lane, ch = warp >> 2;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-#pragma unroll 1
-    for (int cc = 2 * ch; cc < 2 * ch + 2; ++cc) {
-      uint32_t w[32];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint4 v = *reinterpret_cast<const uint4*>(smem + r * 512 + (((cc * 8 + j) ^ (r & 31)) << 4));
-        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
-      }
-      tmem_st32(tQ + lane_base + cc * 32, w);
-    }
-    tmem_wait_st();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   // both CTAs must have their barriers initialised before any remote arrive; every thread takes part
   cluster_sync_all();
-  if (tid == 0) DSA_TRACE_AT(0, 5, 0);
-  const bool run = *start_status == kStatusOk && ctx.active;
-  const int nvt = run ? *n_valid_tiles : 0;
+  const bool run_all = *start_status == kStatusOk;
   bool ok = true;
 
   if (warp >= kFirstExchangeWarp) {
-    // ================================ score exchange ================================================
-    // Sends this CTA's partial scores of 32 rows x 64 keys to the peer as soon as the QK MMAs of a tile are done,
-    // in 16-byte units laid out [unit][row]; the data lands through st.async, which also signals the peer's barrier.
+    // ================================ Q loader + score exchange =====================================
+    // Row r of the item's Q: the CTA's 256 latent dims go to TMEM (lane = row, column c = dims 2c, 2c+1), its 32
+    // rope dims to shared memory.  Then, per tile, the CTA's partial scores of 32 rows x 64 keys go to the peer
+    // as soon as the QK MMAs are done, in 16-byte units laid out [unit][row]; st.async signals the peer's barrier.
     const int q4 = warp & 3;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x = map_to_cta(sX, peer);
     const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
-    for (int it = 0; it < nvt; ++it) {
-      const int sb = it & 1, xq = sb * 4 + q4;
-      uint32_t v[64];
-      if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (it >> 1) & 1, p.status))) { ok = false; break; }
-      tc_fence_after();
-      tmem_ld32(tS + sb * kBK + lane_base, v);
-      tmem_ld32(tS + sb * kBK + 32 + lane_base, v + 32);
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_read[sb]);
-      if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((it >> 1) + 1) & 1, p.status))) { ok = false; break; }
-      if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
+    int g = 0;
+    for (int k = 0; run_all && ok; ++k) {
+      const int item = item_of(k);
+      if (item < 0) break;
+      const int qp = k & 1;
+      const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
+      if (!__all_sync(0xffffffffu, mbar_wait<true>(&info_full[qp], (k >> 1) & 1, p.status))) { ok = false; break; }
+      const int nvt = info[qp * 2];
+      if (nvt > 0) {
+        // all QK MMAs of the previous item are complete (their last s_full was waited for below): Q can be replaced
+        const bool row_ok = h0 + r < p.H;
+        const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0 + (row_ok ? r : 0)) * (kD * 2);
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        st_async_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
-                    __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        for (int u = 0; u < 4; ++u)
+          cp_async16(sQRope + sw128_offset(r, 4 * rank + u), qrow + 1024 + (4 * rank + u) * 16, row_ok ? 16u : 0u);
+        cp_async_commit();
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t w[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row_ok) v = __ldg(reinterpret_cast<const uint4*>(qrow + rank * 512 + (cc * 8 + j) * 16));
+            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+          }
+          tmem_st32(tQ + lane_base + cc * 32, w);
+        }
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_ready);
+      }
+      for (int it = 0; it < nvt; ++it, ++g) {
+        const int sb = g & 1, xq = sb * 4 + q4;
+        uint32_t v[64];
+        if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld32(tS + sb * kBK + lane_base, v);
+        tmem_ld32(tS + sb * kBK + 32 + lane_base, v + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_read[sb]);
+        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
+        if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          st_async_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
+                      __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&info_empty[qp]);
     }
   } else if (warp >= kFirstGatherWarp) {
-    // ================================ gather producers =============================================
+    // ================================ tile lists + gather producers =================================
+    // These warps never leave their loops early: they meet at a named barrier twice per item.
     const int pw = warp - kFirstGatherWarp;  // keys [16 pw, 16 pw + 16) of every tile
-    const bool tracer = tid == kFirstGatherWarp * 32;
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
-    for (int it = 0; it < nvt; ++it) {
-      const int tile = tile_list[it], s = it % kStages;
-      if (tracer) DSA_TRACE_AT(0, 0, it);
-      if (it >= kStages && !mbar_wait<true>(&kv_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
-      if (tracer) DSA_TRACE_AT(0, 1, it);
-      const uint32_t stage = sBase + s * kStageBytes;
-      const int slot = tile * kBK + pw * 16 + (lane & 15);
-      const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
-      const bool my_valid = index_valid(ctx, my_idx);
-      const long long my_row = my_valid ? kv_row(p, ctx.b, my_idx) : -1ll;
-#pragma unroll 4
-      for (int kk = 0; kk < 16; ++kk) {
-        const long long row = __shfl_sync(0xffffffffu, my_row, kk);
-        const bool v = row >= 0;
-        const int key = pw * 16 + kk;
-        const uint8_t* base = kv_bytes + (v ? row : 0) * (kD * 2);
-        cp_async16(stage + (lane >> 3) * kChunkBytes + sw128_offset(key, lane & 7), base + rank * 512 + lane * 16, v ? 16u : 0u);
-        if (lane < 4)
-          cp_async16(stage + 4 * kChunkBytes + sw128_offset(key, 4 * rank + lane), base + 1024 + (4 * rank + lane) * 16, v ? 16u : 0u);
+    int g = 0;
+    for (int k = 0; run_all; ++k) {
+      const int item = item_of(k);
+      if (item < 0) break;
+      const int qp = k & 1;
+      const int bt = item / head_blocks;
+      const RowCtx ctx = make_row_ctx(p, bt);
+      if (k >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait<true>(&info_empty[qp], ((k >> 1) + 1) & 1, p.status));
+      // validity masks of all tiles of the item, then the list of tiles with at least one key taking part
+      for (int tile = pw; tile < ntiles; tile += 4) {
+        const int s0 = tile * kBK + lane, s1 = s0 + 32;
+        const int i0 = s0 < p.topk ? __ldg(ctx.idx_row + s0) : -1;
+        const int i1 = s1 < p.topk ? __ldg(ctx.idx_row + s1) : -1;
+        const uint32_t lo = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i0));
+        const uint32_t hi = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i1));
+        if (lane == 0) masks[qp * kMaxTiles + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
       }
-      cp_async_arrive_noinc(&kv_full[s]);
-      if (tracer) DSA_TRACE_AT(0, 2, it);
+      named_bar_sync(kGatherBarrier, 128);
+      if (pw == 0) {
+        int n = 0;
+        for (int base = 0; base < ntiles; base += 32) {
+          const int tile = base + lane;
+          const bool nonempty = tile < ntiles && masks[qp * kMaxTiles + tile] != 0ull;
+          const uint32_t bal = __ballot_sync(0xffffffffu, nonempty);
+          if (nonempty) tile_list[qp * kMaxTiles + n + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(tile);
+          n += __popc(bal);
+        }
+        if (lane == 0) { info[qp * 2] = n; info[qp * 2 + 1] = ctx.active ? 1 : 0; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&info_full[qp]);
+      }
+      named_bar_sync(kGatherBarrier, 128);
+      const int nvt = info[qp * 2];
+      for (int it = 0; it < nvt; ++it, ++g) {
+        const int tile = tile_list[qp * kMaxTiles + it], s = g % kStages;
+        if (g >= kStages && ok) ok = mbar_wait<true>(&kv_empty[s], ((g / kStages) + 1) & 1, p.status);
+        if (!ok) continue;
+        const uint32_t stage = sBase + s * kStageBytes;
+        const int slot = tile * kBK + pw * 16 + (lane & 15);
+        const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
+        const bool my_valid = index_valid(ctx, my_idx);
+        const long long my_row = my_valid ? kv_row(p, ctx.b, my_idx) : -1ll;
+#pragma unroll 4
+        for (int kk = 0; kk < 16; ++kk) {
+          const long long row = __shfl_sync(0xffffffffu, my_row, kk);
+          const bool v = row >= 0;
+          const int key = pw * 16 + kk;
+          const uint8_t* base = kv_bytes + (v ? row : 0) * (kD * 2);
+          cp_async16(stage + (lane >> 3) * kChunkBytes + sw128_offset(key, lane & 7), base + rank * 512 + lane * 16, v ? 16u : 0u);
+          if (lane < 4)
+            cp_async16(stage + 4 * kChunkBytes + sw128_offset(key, 4 * rank + lane), base + 1024 + (4 * rank + lane) * 16, v ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(&kv_full[s]);
+      }
     }
     cp_async_wait<0>();
   } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ====================================================
-    if (lane == 0 && nvt > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, kHalfDV, 0, 1);
-      // S_r[128 x 64] = Q[:, dims of this CTA] . K^T : 16 steps with A in TMEM + 2 rope steps with A in smem
-      auto issue_qk = [&](int it) -> bool {
-        const int s = it % kStages, sb = it & 1;
+      // S_r[128 x 64] = Q[:, dims of this CTA] . K^T : 16 steps with A in TMEM + 2 rope steps with A in smem.
+      // The score buffer is free: its last readers finished before P of tile g-2 was written, and the PV MMAs that
+      // read that P were issued before this point (MMAs execute in issue order).
+      auto issue_qk = [&](int g) -> bool {
+        const int s = g % kStages, sb = g & 1;
         const uint32_t stage = sBase + s * kStageBytes;
-        DSA_TRACE_AT(1, 0, it);
-        if (!mbar_wait(&kv_full[s], (it / kStages) & 1, p.status)) return false;
-        DSA_TRACE_AT(1, 1, it);
-        // the score buffer is free: its last readers (softmax, exchange warps) finished before P of tile it-2 was
-        // written, and the PV MMAs that read that P were issued before this point (MMAs execute in issue order)
-        DSA_TRACE_AT(1, 2, it);
+        if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) return false;
         fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
         const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ts(tS + sb * kBK, tQ + (c * 4 + k) * 8, db0 + ((c * kChunkBytes + k * 32) >> 4), idesc_qk, (c | k) != 0);
+          for (int kq = 0; kq < 4; ++kq)
+            umma_ts(tS + sb * kBK, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
         }
         const uint64_t da0 = make_smem_desc(sQRope, 16, 1024, kSwizzle128B);
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t off = (2 * rank + k) * 32;
+        for (int kq = 0; kq < 2; ++kq) {
+          const uint32_t off = (2 * rank + kq) * 32;
           umma_ss(tS + sb * kBK, da0 + (off >> 4), db0 + ((4 * kChunkBytes + off) >> 4), idesc_qk, 1);
         }
         umma_commit(&s_full[sb]);
-        DSA_TRACE_AT(1, 3, it);
         return true;
       };
-      ok = issue_qk(0);
-      for (int it = 0; ok && it < nvt; ++it) {
-        if (it + 1 < nvt && !issue_qk(it + 1)) { ok = false; break; }
-        if (!mbar_wait(p_full, it & 1, p.status)) { ok = false; break; }
-        DSA_TRACE_AT(1, 4, it);
-        tc_fence_after();
-        // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major
-        const uint32_t stage = sBase + (it % kStages) * kStageBytes;
-        const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
+      int g = 0, ne = 0;  // cumulative tile count, number of non-empty items so far
+      for (int k = 0; run_all && ok; ++k) {
+        const int item = item_of(k);
+        if (item < 0) break;
+        const int qp = k & 1;
+        if (!mbar_wait(&info_full[qp], (k >> 1) & 1, p.status)) { ok = false; break; }
+        const int nvt = info[qp * 2];
+        if (nvt > 0) {  // items without a key neither load Q nor touch O: their barriers are skipped on both sides
+          if (!mbar_wait(q_ready, ne & 1, p.status)) { ok = false; break; }
+          tc_fence_after();
+          ok = issue_qk(g);
+        }
+        for (int it = 0; ok && it < nvt; ++it, ++g) {
+          if (it + 1 < nvt && !issue_qk(g + 1)) { ok = false; break; }
+          if (!mbar_wait(p_full, g & 1, p.status)) { ok = false; break; }
+          // the first PV of an item overwrites O: the previous non-empty item's output must have been read out
+          if (it == 0 && ne > 0 && !mbar_wait(o_free, (ne - 1) & 1, p.status)) { ok = false; break; }
+          tc_fence_after();
+          // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major
+          const uint32_t stage = sBase + (g % kStages) * kStageBytes;
+          const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
 #pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks)
-          umma_ts(tO, tS + (it & 1) * kBK + ks * 8, db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
-        umma_commit(&kv_empty[it % kStages]);
-        umma_commit(pv_done);
-        DSA_TRACE_AT(1, 5, it);
+          for (int ks = 0; ks < kBK / 16; ++ks)
+            umma_ts(tO, tS + (g & 1) * kBK + ks * 8, db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
+          umma_commit(&kv_empty[g % kStages]);
+          umma_commit(pv_done);
+        }
+        if (!ok) break;
+        if (nvt > 0) ++ne;
+        mbar_arrive(&info_empty[qp]);
       }
     }
   } else {
     // ================================ softmax + epilogue ============================================
-    // thread = (row r, column half ch): r = TMEM lane, ch selects 32 of the tile's 64 score columns
+    // thread = (row r, column half ch): r = TMEM lane, ch selects 32 of the tile's 64 score columns.
+    // A failed wait clears `ok` but does not leave the loops: the two warps of a row block meet at a named barrier
+    // every tile, so both keep walking the items and tiles (without further waits) to the end.
     const int q4 = warp & 3, ch = warp >> 2;
     const int r = q4 * 32 + lane;
-    const bool tracer = tid == 0;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
-    float m_used = -INFINITY, l = 0.f;
-    // A failed wait clears `ok` but does not leave the loop: the two warps of a row block meet at a named barrier
-    // every tile, so both keep walking the tiles (without further waits worth mentioning) to the end.
-    for (int it = 0; it < nvt; ++it) {
-      const uint32_t mask = static_cast<uint32_t>(masks[tile_list[it]] >> (32 * ch));
-      const int sb = it & 1;
-      const int xq = sb * 4 + q4;  // exchange barriers are per (buffer, 32-row block)
-      uint32_t v[32];
-      if (tracer) DSA_TRACE_AT(2, 0, it);
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (it >> 1) & 1, p.status));
-      if (tracer) DSA_TRACE_AT(2, 1, it);
-      tc_fence_after();
-      tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, v);
-      tmem_wait_ld();
-      if (tracer) DSA_TRACE_AT(2, 2, it);
-      // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[xq], (it >> 1) & 1, p.status));
-      if (tracer) DSA_TRACE_AT(2, 4, it);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16);
-        const float x0 = __uint_as_float(v[4 * j]) + o.x, x1 = __uint_as_float(v[4 * j + 1]) + o.y;
-        const float x2 = __uint_as_float(v[4 * j + 2]) + o.z, x3 = __uint_as_float(v[4 * j + 3]) + o.w;
-        v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
-      }
-      if (tracer) DSA_TRACE_AT(3, 0, it);
-      if (mask == 0xffffffffu) {
-        float m4[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 4]));
-#pragma unroll
-        for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(v[j]));
-      }
-      // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory.
-      // After this barrier both warps have also finished reading the scores of the tile (TMEM and exchange buffer).
-      if (tracer) DSA_TRACE_AT(3, 2, it);
-      pair[(it & 1) * 256 + tid] = mx;
-      named_bar_sync(1 + q4, 64);
-      if (tracer) DSA_TRACE_AT(3, 3, it);
-      if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + xq * 8);  // one credit per warp: peer may overwrite these rows
-      mx = fmaxf(mx, pair[(it & 1) * 256 + (tid ^ 128)]) * p.scale_log2;
-      // ---- online softmax with a lazily updated reference maximum ----
-      float factor = 1.f;
-      if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
-        factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
-        m_used = mx;
-      }
-      if (it > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
-        // O must be quiescent: the PV MMAs of the previous tile are done
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (it - 1) & 1, p.status));
+    int g = 0;
+    for (int k = 0; run_all; ++k) {
+      const int item = item_of(k);
+      if (item < 0) break;
+      const int qp = k & 1;
+      const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status));
+      const int nvt = info[qp * 2];  // read unconditionally: both warps of a row block must walk the same number of tiles
+      const bool active = ok && info[qp * 2 + 1] != 0;
+      float m_used = -INFINITY, l = 0.f;
+      for (int it = 0; it < nvt; ++it, ++g) {
+        const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (32 * ch));
+        const int sb = g & 1;
+        const int xq = sb * 4 + q4;  // exchange barriers are per (buffer, 32-row block)
+        uint32_t v[32];
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g >> 1) & 1, p.status));
         tc_fence_after();
-        uint32_t o[32];
-#pragma unroll 1
-        for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {  // this thread's half of the output columns
-          tmem_ld32(tO + lane_base + cc * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
-          tmem_st32(tO + lane_base + cc * 32, o);
-        }
-      }
-      if (tracer) DSA_TRACE_AT(2, 5, it);
-      l *= factor;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_used;
-      uint32_t pk[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float p0 = exp2f(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, neg_m));
-        float p1 = exp2f(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, neg_m));
-        if (mask != 0xffffffffu) {
-          p0 = ((mask >> (2 * j)) & 1u) ? p0 : 0.f;
-          p1 = ((mask >> (2 * j + 1)) & 1u) ? p1 : 0.f;
-        }
-        sum4[j & 3] += p0 + p1;
-        pk[j] = pack2<kBF16>(p0, p1);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (tracer) DSA_TRACE_AT(3, 4, it);
-      // P (column c = keys 2c, 2c+1) replaces the first 32 columns of this tile's score buffer; the exchange warps
-      // must have read their copy of the scores first
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_read[sb], (it >> 1) & 1, p.status));
-      tmem_st16(tS + sb * kBK + ch * 16 + lane_base, pk);
-      tmem_wait_st();
-      if (tracer) DSA_TRACE_AT(3, 5, it);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-      if (tracer) DSA_TRACE_AT(2, 6, it);
-    }
-    // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
-    // row sum = sum of the two column halves, exchanged like the maxima
-    if (nvt > 0) {
-      pair[(nvt & 1) * 256 + tid] = l;
-      named_bar_sync(1 + q4, 64);
-      l += pair[(nvt & 1) * 256 + (tid ^ 128)];
-    }
-    const int h = h0 + r;
-    T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
-    if (run && nvt == 0) {
-      if (h < p.H) {
-        for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
-        if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
-      }
-    } else if (run && ok && __all_sync(0xffffffffu, mbar_wait(pv_done, (nvt - 1) & 1, p.status))) {
-      tc_fence_after();
-      const float inv_l = 1.f / l;
-      uint32_t v[32];
-#pragma unroll 1
-      for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
-        tmem_ld32(tO + lane_base + cc * 32, v);
+        tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, v);
         tmem_wait_ld();
-        if (h < p.H) {
+        // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[xq], (g >> 1) & 1, p.status));
+        float mx = -INFINITY;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack2<kBF16>(__uint_as_float(v[8 * g + 0]) * inv_l, __uint_as_float(v[8 * g + 1]) * inv_l);
-            w.y = pack2<kBF16>(__uint_as_float(v[8 * g + 2]) * inv_l, __uint_as_float(v[8 * g + 3]) * inv_l);
-            w.z = pack2<kBF16>(__uint_as_float(v[8 * g + 4]) * inv_l, __uint_as_float(v[8 * g + 5]) * inv_l);
-            w.w = pack2<kBF16>(__uint_as_float(v[8 * g + 6]) * inv_l, __uint_as_float(v[8 * g + 7]) * inv_l);
-            reinterpret_cast<uint4*>(orow + cc * 32)[g] = w;
+        for (int j = 0; j < 8; ++j) {
+          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16);
+          const float x0 = __uint_as_float(v[4 * j]) + o.x, x1 = __uint_as_float(v[4 * j + 1]) + o.y;
+          const float x2 = __uint_as_float(v[4 * j + 2]) + o.z, x3 = __uint_as_float(v[4 * j + 3]) + o.w;
+          v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
+        }
+        if (mask == 0xffffffffu) {
+          float m4[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 4]));
+#pragma unroll
+          for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(v[j]));
+        }
+        // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory.
+        // After this barrier both warps have also finished reading the scores of the tile (TMEM and exchange buffer).
+        pair[(g & 1) * 256 + tid] = mx;
+        named_bar_sync(1 + q4, 64);
+        mx = fmaxf(mx, pair[(g & 1) * 256 + (tid ^ 128)]) * p.scale_log2;
+        // ---- online softmax with a lazily updated reference maximum ----
+        float factor = 1.f;
+        if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
+          factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+          m_used = mx;
+        }
+        if (it > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+          // O must be quiescent: the PV MMAs of the previous tile are done
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (g - 1) & 1, p.status));
+          tc_fence_after();
+          uint32_t o[32];
+#pragma unroll 1
+          for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {  // this thread's half of the output columns
+            tmem_ld32(tO + lane_base + cc * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+            tmem_st32(tO + lane_base + cc * 32, o);
           }
         }
+        l *= factor;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float neg_m = -m_used;
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float p0 = exp2f(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, neg_m));
+          float p1 = exp2f(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, neg_m));
+          if (mask != 0xffffffffu) {
+            p0 = ((mask >> (2 * j)) & 1u) ? p0 : 0.f;
+            p1 = ((mask >> (2 * j + 1)) & 1u) ? p1 : 0.f;
+          }
+          sum4[j & 3] += p0 + p1;
+          pk[j] = pack2<kBF16>(p0, p1);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        // P (column c = keys 2c, 2c+1) replaces the first 32 columns of this tile's score buffer; the exchange warps
+        // must have read their copy of the scores first
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_read[sb], (g >> 1) & 1, p.status));
+        tmem_st16(tS + sb * kBK + ch * 16 + lane_base, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(p_full);
+          mbar_arrive_cluster_relaxed(peer_x_empty + xq * 8);  // one credit per warp: the peer may overwrite these rows
+        }
       }
-      if (rank == 0 && ch == 0 && p.lse && h < p.H)
-        p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
+      // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
+      if (nvt > 0) {  // row sum = sum of the two column halves, exchanged like the maxima
+        pair[2 * 256 + tid] = l;
+        named_bar_sync(1 + q4, 64);
+        l += pair[2 * 256 + (tid ^ 128)];  // (the slot is rewritten only after the next tile's barrier)
+      }
+      const int h = h0 + r;
+      T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
+      if (active && nvt == 0) {
+        if (h < p.H) {
+          for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
+          if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+        }
+      } else if (nvt > 0) {
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (g - 1) & 1, p.status));
+        tc_fence_after();
+        const float inv_l = 1.f / l;
+        uint32_t v[32];
+#pragma unroll 1
+        for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
+          tmem_ld32(tO + lane_base + cc * 32, v);
+          tmem_wait_ld();
+          if (ok && h < p.H) {
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+              uint4 w;
+              w.x = pack2<kBF16>(__uint_as_float(v[8 * gq + 0]) * inv_l, __uint_as_float(v[8 * gq + 1]) * inv_l);
+              w.y = pack2<kBF16>(__uint_as_float(v[8 * gq + 2]) * inv_l, __uint_as_float(v[8 * gq + 3]) * inv_l);
+              w.z = pack2<kBF16>(__uint_as_float(v[8 * gq + 4]) * inv_l, __uint_as_float(v[8 * gq + 5]) * inv_l);
+              w.w = pack2<kBF16>(__uint_as_float(v[8 * gq + 6]) * inv_l, __uint_as_float(v[8 * gq + 7]) * inv_l);
+              reinterpret_cast<uint4*>(orow + cc * 32)[gq] = w;
+            }
+          }
+        }
+        if (ok && rank == 0 && ch == 0 && p.lse && h < p.H)
+          p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (nvt > 0) mbar_arrive(o_free);  // the output tile may be overwritten by the next item's first PV
+        mbar_arrive(&info_empty[qp]);      // the item's tile list is no longer needed here
+      }
     }
   }
 
   // ---- teardown: every thread of both CTAs comes here, also after a failed wait -----------------------
-  if (tid == 0) DSA_TRACE_AT(0, 6, 0);
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) DSA_TRACE_AT(0, 7, 0);
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   cluster_sync_all();  // no CTA leaves while its peer may still write into its shared memory
 }
@@ -592,8 +628,14 @@ int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream)
   auto kern = bf16 ? sparse_mla_fwd_tc_kernel<true> : sparse_mla_fwd_tc_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tc::kSmemBytes));
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(2, p.B * p.S, (p.H + tc::kM - 1) / tc::kM);
-  kern<<<grid, tc::kThreads, tc::kSmemBytes, stream>>>(p);
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(e);
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e);
+  // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
+  const long long items = static_cast<long long>(p.B) * p.S * ((p.H + tc::kM - 1) / tc::kM);
+  long long clusters = sms / 2 > 0 ? sms / 2 : 1;
+  if (clusters > items) clusters = items;
+  kern<<<dim3(static_cast<unsigned>(2 * clusters)), tc::kThreads, tc::kSmemBytes, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -607,10 +649,5 @@ int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t st
   return static_cast<int>(cudaGetLastError());
 }
 
-#ifdef DSA_TRACE
-extern "C" int dsa_debug_set_trace(long long* buf) {
-  return static_cast<int>(cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)));
-}
-#endif
 
 }  // namespace dsa
