@@ -102,16 +102,17 @@ constexpr uint32_t kXBytes = kM * kBK * 4;            // peer's partial scores [
 constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
 constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 139264
 constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 204800
-constexpr uint32_t kOffPair = kOffBar + 512;                      // [3][256] floats exchanged between the two column halves
-constexpr uint32_t kOffMask = kOffPair + 3 * 256 * 4;             // [2][kMaxTiles] 64-bit validity masks (per item parity)
+constexpr uint32_t kOffPair = kOffBar + 512;                      // [3][512] floats exchanged between the four column quarters
+constexpr uint32_t kOffMask = kOffPair + 3 * 512 * 4;             // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;       // [2][kMaxTiles] 16-bit tile ids
 constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;       // [2] {tile count, run flag}
 constexpr uint32_t kSmemBytes = kOffInfo + 64 + 1024;             // + slack to align the base to 1024 B
-constexpr int kSoftmaxWarps = 8;                      // warp w: rows 32 (w & 3) .. +31, score columns 32 (w >> 2) .. +31
-constexpr int kMmaWarp = 8;
-constexpr int kFirstGatherWarp = 9;
-constexpr int kFirstExchangeWarp = 13;                // warp w sends rows 32 (w & 3) .. +31 of the partial scores to the peer
-constexpr int kThreads = 544;                         // 8 softmax warps, 1 MMA warp, 4 gather warps, 4 exchange warps
+constexpr int kSoftmaxWarps = 16;                     // warp w: rows 32 (w & 3) .. +31, score columns 16 (w >> 2) .. +15
+constexpr int kMmaWarp = 16;
+constexpr int kFirstGatherWarp = 17;
+constexpr int kFirstExchangeWarp = 21;                // warp w sends rows 32 (w & 3) .. +31 of the partial scores to the peer
+constexpr int kPvWarp = 25;                           // second MMA-issuing warp (PV), on another scheduler than the QK issuer
+constexpr int kThreads = 832;                         // 16 softmax warps, 2 MMA warps, 4 gather warps, 4 exchange warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
@@ -130,16 +131,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   uint64_t* kv_empty = bars + 3;    // [3] count 1: commit after the PV MMAs of the stage
   uint64_t* s_full = bars + 6;      // [2] count 1: commit after the QK MMAs
   uint64_t* s_read = bars + 8;      // [2] count 4: the exchange warps have read the partial scores out of TMEM
-  uint64_t* p_full = bars + 10;     // count 8: softmax warps wrote P into TMEM
+  uint64_t* p_full = bars + 10;     // count 16: softmax warps wrote P into TMEM
   uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
   uint64_t* x_full = bars + 12;     // [2][4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
-  uint64_t* x_empty = bars + 20;    // [2][4] count 2: both peer softmax warps of these rows consumed what this CTA sent
+  uint64_t* x_empty = bars + 20;    // [2][4] count 4: all peer softmax warps of these rows consumed what this CTA sent
   uint64_t* info_full = bars + 28;  // [2] count 1: tile list of an item published by the gather warps
-  uint64_t* info_empty = bars + 30; // [2] count 13: MMA thread, softmax and exchange warps are done with the item's tile list
+  uint64_t* info_empty = bars + 30; // [2] count 22: both MMA threads, softmax and exchange warps are done with the item's tile list
   uint64_t* q_ready = bars + 32;    // count 4: the exchange warps put the item's Q into TMEM / shared memory
-  uint64_t* o_free = bars + 33;     // count 8: the softmax warps drained the previous item's output tile from TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
-  int* start_status = reinterpret_cast<int*>(bars + 35);
+  uint64_t* o_free = bars + 33;     // count 16: the softmax warps drained the previous item's output tile from TMEM
+  uint64_t* s_free = bars + 34;     // [2] count 1: commit after the PV MMAs that read P out of this score buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 36);
+  int* start_status = reinterpret_cast<int*>(bars + 37);
   float* pair = reinterpret_cast<float*>(smem + kOffPair);
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint16_t* tile_list = reinterpret_cast<uint16_t*>(smem + kOffList);
@@ -162,9 +164,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1); mbar_init(&s_read[i], 4);
-      mbar_init(&info_full[i], 1); mbar_init(&info_empty[i], 13);
+      mbar_init(&info_full[i], 1); mbar_init(&info_empty[i], 2 + kSoftmaxWarps + 4);
+      mbar_init(&s_free[i], 1);
     }
-    for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 2); }
+    for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 4); }
     mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     mbar_init(q_ready, 4);
@@ -186,7 +189,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   const bool run_all = *start_status == kStatusOk;
   bool ok = true;
 
-  if (warp >= kFirstExchangeWarp) {
+  if (warp >= kFirstExchangeWarp && warp < kPvWarp) {
     // ================================ Q loader + score exchange =====================================
     // Row r of the item's Q: the CTA's 256 latent dims go to TMEM (lane = row, column c = dims 2c, 2c+1), its 32
     // rope dims to shared memory.  Then, per tile, the CTA's partial scores of 32 rows x 64 keys go to the peer
@@ -230,28 +233,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         __syncwarp();
         if (lane == 0) mbar_arrive(q_ready);
       }
+      {  // pull the next item's Q rows towards L2 while this item is being worked on
+        const int nitem = item_of(k + 1);
+        if (nitem >= 0) {
+          const int nbt = nitem / head_blocks, nh = (nitem - nbt * head_blocks) * kM + r;
+          if (nh < p.H) {
+            const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * (kD * 2);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) prefetch_l2(nq + rank * 512 + j * 128);
+            prefetch_l2(nq + 1024 + rank * 64);
+          }
+        }
+      }
       for (int it = 0; it < nvt; ++it, ++g) {
         const int sb = g & 1, xq = sb * 4 + q4;
-        uint32_t v[64];
+        uint32_t v[32];
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
+        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
+        if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
         tc_fence_after();
-        tmem_ld32(tS + sb * kBK + lane_base, v);
-        tmem_ld32(tS + sb * kBK + 32 + lane_base, v + 32);
-        tmem_wait_ld();
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          tmem_ld32(tS + sb * kBK + hf * 32 + lane_base, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_async_v4(peer_x + sb * kXBytes + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
+                        __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_read[sb]);
-        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
-        if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          st_async_v4(peer_x + sb * kXBytes + j * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
-                      __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&info_empty[qp]);
     }
-  } else if (warp >= kFirstGatherWarp) {
+  } else if (warp >= kFirstGatherWarp && warp < kFirstExchangeWarp) {
     // ================================ tile lists + gather producers =================================
     // These warps never leave their loops early: they meet at a named barrier twice per item.
     const int pw = warp - kFirstGatherWarp;  // keys [16 pw, 16 pw + 16) of every tile
@@ -313,35 +330,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     }
     cp_async_wait<0>();
   } else if (warp == kMmaWarp) {
-    // ================================ MMA issuer ====================================================
+    // ================================ QK^T issuer ===================================================
+    // S_r[128 x 64] = Q[:, dims of this CTA] . K^T : 16 steps with A in TMEM + 2 rope steps with A in smem.
+    // Runs ahead of the PV issuer as far as the two score buffers allow.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, kHalfDV, 0, 1);
-      // S_r[128 x 64] = Q[:, dims of this CTA] . K^T : 16 steps with A in TMEM + 2 rope steps with A in smem.
-      // The score buffer is free: its last readers finished before P of tile g-2 was written, and the PV MMAs that
-      // read that P were issued before this point (MMAs execute in issue order).
-      auto issue_qk = [&](int g) -> bool {
-        const int s = g % kStages, sb = g & 1;
-        const uint32_t stage = sBase + s * kStageBytes;
-        if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) return false;
-        fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
-        tc_fence_after();
-        const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int kq = 0; kq < 4; ++kq)
-            umma_ts(tS + sb * kBK, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
-        }
-        const uint64_t da0 = make_smem_desc(sQRope, 16, 1024, kSwizzle128B);
-#pragma unroll
-        for (int kq = 0; kq < 2; ++kq) {
-          const uint32_t off = (2 * rank + kq) * 32;
-          umma_ss(tS + sb * kBK, da0 + (off >> 4), db0 + ((4 * kChunkBytes + off) >> 4), idesc_qk, 1);
-        }
-        umma_commit(&s_full[sb]);
-        return true;
-      };
       int g = 0, ne = 0;  // cumulative tile count, number of non-empty items so far
       for (int k = 0; run_all && ok; ++k) {
         const int item = item_of(k);
@@ -351,22 +344,60 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const int nvt = info[qp * 2];
         if (nvt > 0) {  // items without a key neither load Q nor touch O: their barriers are skipped on both sides
           if (!mbar_wait(q_ready, ne & 1, p.status)) { ok = false; break; }
-          tc_fence_after();
-          ok = issue_qk(g);
+          ++ne;
         }
         for (int it = 0; ok && it < nvt; ++it, ++g) {
-          if (it + 1 < nvt && !issue_qk(g + 1)) { ok = false; break; }
+          const int s = g % kStages, sb = g & 1;
+          const uint32_t stage = sBase + s * kStageBytes;
+          if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
+          // the score buffer still holds P of tile g-2 until the PV MMAs of that tile have read it
+          if (g >= 2 && !mbar_wait(&s_free[sb], ((g >> 1) + 1) & 1, p.status)) { ok = false; break; }
+          fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
+          tc_fence_after();
+          const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int kq = 0; kq < 4; ++kq)
+              umma_ts(tS + sb * kBK, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
+          }
+          const uint64_t da0 = make_smem_desc(sQRope, 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int kq = 0; kq < 2; ++kq) {
+            const uint32_t off = (2 * rank + kq) * 32;
+            umma_ss(tS + sb * kBK, da0 + (off >> 4), db0 + ((4 * kChunkBytes + off) >> 4), idesc_qk, 1);
+          }
+          umma_commit(&s_full[sb]);
+        }
+        if (!ok) break;
+        mbar_arrive(&info_empty[qp]);
+      }
+    }
+  } else if (warp == kPvWarp) {
+    // ================================ PV issuer =====================================================
+    // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major.
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, kHalfDV, 0, 1);
+      int g = 0, ne = 0;
+      for (int k = 0; run_all && ok; ++k) {
+        const int item = item_of(k);
+        if (item < 0) break;
+        const int qp = k & 1;
+        if (!mbar_wait(&info_full[qp], (k >> 1) & 1, p.status)) { ok = false; break; }
+        const int nvt = info[qp * 2];
+        for (int it = 0; ok && it < nvt; ++it, ++g) {
           if (!mbar_wait(p_full, g & 1, p.status)) { ok = false; break; }
           // the first PV of an item overwrites O: the previous non-empty item's output must have been read out
           if (it == 0 && ne > 0 && !mbar_wait(o_free, (ne - 1) & 1, p.status)) { ok = false; break; }
+          fence_proxy_async_smem();
           tc_fence_after();
-          // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major
           const uint32_t stage = sBase + (g % kStages) * kStageBytes;
           const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
 #pragma unroll
           for (int ks = 0; ks < kBK / 16; ++ks)
             umma_ts(tO, tS + (g & 1) * kBK + ks * 8, db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
           umma_commit(&kv_empty[g % kStages]);
+          umma_commit(&s_free[g & 1]);
           umma_commit(pv_done);
         }
         if (!ok) break;
@@ -376,10 +407,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     }
   } else {
     // ================================ softmax + epilogue ============================================
-    // thread = (row r, column half ch): r = TMEM lane, ch selects 32 of the tile's 64 score columns.
-    // A failed wait clears `ok` but does not leave the loops: the two warps of a row block meet at a named barrier
-    // every tile, so both keep walking the items and tiles (without further waits) to the end.
-    const int q4 = warp & 3, ch = warp >> 2;
+    // thread = (row r, column quarter cq): r = TMEM lane, cq selects 16 of the tile's 64 score columns (and 64 of
+    // the CTA's 256 output columns).  A failed wait clears `ok` but does not leave the loops: the four warps of a
+    // row block meet at a named barrier every tile, so all keep walking the items and tiles to the end.
+    const int q4 = warp & 3, cq = warp >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
@@ -390,45 +421,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       const int qp = k & 1;
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status));
-      const int nvt = info[qp * 2];  // read unconditionally: both warps of a row block must walk the same number of tiles
+      const int nvt = info[qp * 2];  // read unconditionally: all warps of a row block must walk the same number of tiles
       const bool active = ok && info[qp * 2 + 1] != 0;
       float m_used = -INFINITY, l = 0.f;
       for (int it = 0; it < nvt; ++it, ++g) {
-        const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (32 * ch));
+        const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (16 * cq)) & 0xffffu;
         const int sb = g & 1;
         const int xq = sb * 4 + q4;  // exchange barriers are per (buffer, 32-row block)
-        uint32_t v[32];
+        uint32_t v[16];
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g >> 1) & 1, p.status));
         tc_fence_after();
-        tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, v);
+        tmem_ld16(tS + sb * kBK + cq * 16 + lane_base, v);
         tmem_wait_ld();
         // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[xq], (g >> 1) & 1, p.status));
-        float mx = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (8 * ch + j) * (kM * 16) + r * 16);
-          const float x0 = __uint_as_float(v[4 * j]) + o.x, x1 = __uint_as_float(v[4 * j + 1]) + o.y;
-          const float x2 = __uint_as_float(v[4 * j + 2]) + o.z, x3 = __uint_as_float(v[4 * j + 3]) + o.w;
-          v[4 * j] = __float_as_uint(x0); v[4 * j + 1] = __float_as_uint(x1); v[4 * j + 2] = __float_as_uint(x2); v[4 * j + 3] = __float_as_uint(x3);
+        for (int j = 0; j < 4; ++j) {
+          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (4 * cq + j) * (kM * 16) + r * 16);
+          v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o.x);
+          v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o.y);
+          v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o.z);
+          v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o.w);
         }
-        if (mask == 0xffffffffu) {
+        float mx = -INFINITY;
+        if (mask == 0xffffu) {
           float m4[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 4]));
 #pragma unroll
-          for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+          for (int j = 8; j < 16; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
           mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < 16; ++j)
             if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(v[j]));
         }
-        // the other column half of this row lives in warp (w ^ 4): combine the maxima through shared memory.
-        // After this barrier both warps have also finished reading the scores of the tile (TMEM and exchange buffer).
-        pair[(g & 1) * 256 + tid] = mx;
-        named_bar_sync(1 + q4, 64);
-        mx = fmaxf(mx, pair[(g & 1) * 256 + (tid ^ 128)]) * p.scale_log2;
+        // the other column quarters of this row live in warps with the same (w & 3): combine the maxima through
+        // shared memory.  After this barrier all four warps have also finished reading the scores of the tile.
+        float* slot = pair + (g & 1) * 512;
+        slot[cq * 128 + r] = mx;
+        named_bar_sync(1 + q4, 128);
+        mx = fmaxf(fmaxf(slot[r], slot[128 + r]), fmaxf(slot[256 + r], slot[384 + r])) * p.scale_log2;
         // ---- online softmax with a lazily updated reference maximum ----
         float factor = 1.f;
         if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
@@ -441,7 +474,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           tc_fence_after();
           uint32_t o[32];
 #pragma unroll 1
-          for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {  // this thread's half of the output columns
+          for (int cc = 2 * cq; cc < 2 * cq + 2; ++cc) {  // this thread's quarter of the output columns
             tmem_ld32(tO + lane_base + cc * 32, o);
             tmem_wait_ld();
 #pragma unroll
@@ -452,12 +485,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         l *= factor;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const float neg_m = -m_used;
-        uint32_t pk[16];
+        uint32_t pk[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < 8; ++j) {
           float p0 = exp2f(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, neg_m));
           float p1 = exp2f(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, neg_m));
-          if (mask != 0xffffffffu) {
+          if (mask != 0xffffu) {
             p0 = ((mask >> (2 * j)) & 1u) ? p0 : 0.f;
             p1 = ((mask >> (2 * j + 1)) & 1u) ? p1 : 0.f;
           }
@@ -468,7 +501,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         // P (column c = keys 2c, 2c+1) replaces the first 32 columns of this tile's score buffer; the exchange warps
         // must have read their copy of the scores first
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_read[sb], (g >> 1) & 1, p.status));
-        tmem_st16(tS + sb * kBK + ch * 16 + lane_base, pk);
+        tmem_st8(tS + sb * kBK + cq * 8 + lane_base, pk);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -477,18 +510,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           mbar_arrive_cluster_relaxed(peer_x_empty + xq * 8);  // one credit per warp: the peer may overwrite these rows
         }
       }
-      // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
-      if (nvt > 0) {  // row sum = sum of the two column halves, exchanged like the maxima
-        pair[2 * 256 + tid] = l;
-        named_bar_sync(1 + q4, 64);
-        l += pair[2 * 256 + (tid ^ 128)];  // (the slot is rewritten only after the next tile's barrier)
+      // ---- epilogue: each thread normalises and stores its 64 of the CTA's 256 output columns ----
+      if (nvt > 0) {  // row sum = sum of the four column quarters, exchanged like the maxima
+        float* slot = pair + 2 * 512;
+        slot[cq * 128 + r] = l;
+        named_bar_sync(1 + q4, 128);
+        l = (slot[r] + slot[128 + r]) + (slot[256 + r] + slot[384 + r]);  // (the slot is rewritten only after the next tile's barrier)
       }
       const int h = h0 + r;
       T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
       if (active && nvt == 0) {
         if (h < p.H) {
-          for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
-          if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+          for (int j = 8 * cq; j < 8 * cq + 8; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
+          if (rank == 0 && cq == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
         }
       } else if (nvt > 0) {
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (g - 1) & 1, p.status));
@@ -496,7 +530,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const float inv_l = 1.f / l;
         uint32_t v[32];
 #pragma unroll 1
-        for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
+        for (int cc = 2 * cq; cc < 2 * cq + 2; ++cc) {
           tmem_ld32(tO + lane_base + cc * 32, v);
           tmem_wait_ld();
           if (ok && h < p.H) {
@@ -511,7 +545,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
             }
           }
         }
-        if (ok && rank == 0 && ch == 0 && p.lse && h < p.H)
+        if (ok && rank == 0 && cq == 0 && p.lse && h < p.H)
           p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
       }
       tc_fence_before();
