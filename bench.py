@@ -115,6 +115,50 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def _time_ms(fn, reps: int = 10, warm: int = 3) -> float:
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def measure_other_stages(dev, peaks) -> dict:
+    """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator(device=dev).manual_seed(7)
+    S1, S2, K = 4096, 8192, 2048
+    qi = torch.randn((1, S1, 64, 128), generator=g, device=dev).to(torch.bfloat16)
+    ki = torch.randn((1, S2, 1, 128), generator=g, device=dev).to(torch.bfloat16)
+    wi = (torch.randn((1, S1, 64), generator=g, device=dev) / 8).float()
+    t_sc = _time_ms(lambda: dsa.indexer_scores_raw(qi, ki, wi, sparse_mode=3, fill_masked=False))
+    t_all = _time_ms(lambda: dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=K, sparse_mode=3))
+    pairs = int((np.arange(S1, dtype=np.int64) + (S2 - S1) + 1).sum())
+    sc_tflops = pairs * 64 * 256 / (t_sc * 1e-3) / 1e12
+    del qi, ki, wi
+    B, S_kv, H, topk = 64, 32768, 128, 2048
+    qd = torch.randn((B, 1, H, 576), generator=g, device=dev).to(torch.bfloat16)
+    kvd = torch.randn((B, S_kv, 1, 576), generator=g, device=dev).to(torch.bfloat16)
+    idxd = torch.stack([torch.randperm(S_kv, generator=g, device=dev)[:topk] for _ in range(B)]).to(torch.int32).view(B, 1, 1, topk)
+    t_dec = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd, kvd, idxd, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=20)
+    dec_bytes = B * (topk * 1152 + H * 576 * 2 + H * 512 * 2 + topk * 4)
+    dec_gbs = dec_bytes / (t_dec * 1e-3) / 1e9
+    assert dsa.kernel_status() == 0
+    return {
+        "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
+                           "workload": "S_q=4096 S_kv=8192 64 heads x 128, causal"},
+        "indexer_plus_topk": {"ms": t_all, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
+        "decode": {"us": t_dec * 1e3, "tokens_per_s": B / (t_dec * 1e-3), "algorithmic_gb_per_s": dec_gbs,
+                   "frac_of_hbm_peak": dec_gbs / peaks["hbm_gbs"], "algorithmic_bytes": dec_bytes,
+                   "workload": "B=64 x 1 token, S_kv=32768, H=128, topk=2048 (KV cache 2.4 GB, larger than L2)"},
+    }
+
+
 def cpu_oracle_sample(q, kv, idx, rows: np.ndarray):
     """Oracle forward on a sample of query rows (host cores): returns (out, lse, seconds, threads)."""
     from oracle import dsa_oracle as orc
@@ -285,6 +329,10 @@ def main() -> None:
         "gpu_launches": args.steps,
         "clocks": clocks.summary(),
     }
+
+    # ---- the rest of the path on its BASELINE shapes (N=1 only; reported beside the headline, not part of it) ----
+    if rank == 0 and world == 1 and not args.queries:
+        line["other_stages"] = measure_other_stages(dev, peaks)
 
     # ---- CPU baseline (rank 0, N=1 only): the oracle on a bounded sample; doubles as a parity check -----
     if rank == 0 and world == 1 and args.cpu_sample > 0:

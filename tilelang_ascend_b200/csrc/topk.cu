@@ -7,9 +7,10 @@
 // distinct values this is also torch.topk's answer (examples/topk_selector/example_topk_selector.py:57-58).
 //
 // One CTA per row.  The row is converted to order-preserving 32-bit keys in shared memory, four
-// 8-bit most-significant-digit-first histogram passes find the k-th largest key, one ordered
-// compaction pass takes everything above it plus the lowest-index ties, and a bitonic sort of the
-// <= k survivors on (key, ~index) fixes the output order.
+// 8-bit most-significant-digit-first histogram passes find the k-th largest key, an index-ordered
+// compaction (per-warp counts, prefix over warps, ordered write) takes everything above it plus the
+// lowest-index ties, and a bitonic sort of the <= k survivors on (key, ~index) fixes the output order;
+// its strides below 64 run inside warps with shuffles.
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -42,8 +43,8 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(kpow2) * 8);  // [n]
   uint32_t* whist = keys + n;                                                                // [kWarps][256]
   __shared__ uint32_t hist[256];
-  __shared__ uint32_t warp_sums[kWarps];
-  __shared__ uint32_t s_prefix, s_remaining, s_nvalid, s_count, s_tie_base;
+  __shared__ uint32_t warp_sums[kWarps], warp_ties[kWarps];
+  __shared__ uint32_t s_prefix, s_remaining, s_nvalid;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x;
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
   lim = lim < 0 ? 0 : (lim > n ? n : lim);
   n = lim;  // entries at or beyond the limit are not candidates: none of the passes below looks at them
 
-  if (tid == 0) { s_nvalid = 0; s_count = 0; s_tie_base = 0; }
+  if (tid == 0) s_nvalid = 0;
   for (int i = tid; i < kWarps * 256; i += kThreads) whist[i] = 0;
   __syncthreads();
 
@@ -134,45 +135,99 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
 
   // ---- ordered compaction: keys > T in any order, keys == T by ascending index until need_ties ----------
   for (int i = tid; i < kpow2; i += kThreads) sortbuf[i] = 0ull;
-  __syncthreads();
   const bool take_all = nvalid <= static_cast<uint32_t>(top_k);
-  for (int base = 0; base < n; base += kThreads) {
-    const int i = base + tid;
-    const uint32_t k = i < n ? keys[i] : 0u;
-    const bool gt = k != 0 && (take_all || k > thresh);
-    const bool eq = !take_all && k != 0 && k == thresh;
-    // rank of this tie among the ties seen so far (index order): block-wide exclusive scan of eq
-    const uint32_t bal = __ballot_sync(0xffffffffu, eq);
-    const uint32_t in_warp = __popc(bal & ((1u << lane) - 1u));
-    if (lane == 0) warp_sums[warp] = __popc(bal);
-    __syncthreads();
-    uint32_t before = s_tie_base;
-    for (int w = 0; w < warp; ++w) before += warp_sums[w];
-    const bool take_tie = eq && (before + in_warp) < need_ties;
-    if (gt || take_tie) {
-      const uint32_t pos = atomicAdd(&s_count, 1u);
-      sortbuf[pos] = (static_cast<unsigned long long>(k) << 32) | static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(i));
+  {
+    // warp w owns the contiguous index range [w * per, w * per + per): count, prefix over warps, then write in order
+    const int per = ((n + kWarps - 1) / kWarps + 31) & ~31;
+    const int beg = warp * per, end = min(n, beg + per);
+    uint32_t n_gt = 0, n_eq = 0;
+    for (int base = beg; base < end; base += 32) {
+      const int i = base + lane;
+      const uint32_t k = i < end ? keys[i] : 0u;
+      n_gt += __popc(__ballot_sync(0xffffffffu, k != 0 && (take_all || k > thresh)));
+      n_eq += __popc(__ballot_sync(0xffffffffu, !take_all && k != 0 && k == thresh));
     }
+    if (lane == 0) { warp_sums[warp] = n_gt; warp_ties[warp] = n_eq; }
     __syncthreads();
-    if (tid == 0) {
-      uint32_t t = 0;
-      for (int w = 0; w < kWarps; ++w) t += warp_sums[w];
-      s_tie_base += t;
+    uint32_t tie_rank = 0, out_pos = 0;  // ties / selected elements in the warps before this one
+    for (int w = 0; w < warp; ++w) {
+      const uint32_t e = warp_ties[w];
+      const uint32_t taken = tie_rank >= need_ties ? 0u : min(e, need_ties - tie_rank);
+      out_pos += warp_sums[w] + taken;
+      tie_rank += e;
     }
-    __syncthreads();
+    for (int base = beg; base < end; base += 32) {
+      const int i = base + lane;
+      const uint32_t k = i < end ? keys[i] : 0u;
+      const bool gt = k != 0 && (take_all || k > thresh);
+      const bool eq = !take_all && k != 0 && k == thresh;
+      const uint32_t bal_eq = __ballot_sync(0xffffffffu, eq);
+      const bool take = gt || (eq && tie_rank + __popc(bal_eq & ((1u << lane) - 1u)) < need_ties);
+      const uint32_t bal = __ballot_sync(0xffffffffu, take);
+      if (take)
+        sortbuf[out_pos + __popc(bal & ((1u << lane) - 1u))] =
+            (static_cast<unsigned long long>(k) << 32) | static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(i));
+      out_pos += __popc(bal);
+      tie_rank += __popc(bal_eq);
+    }
   }
+  __syncthreads();
 
   // ---- bitonic sort, descending on (key, ~index): larger score first, then lower index ---------------------
-  for (int size = 2; size <= kpow2; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
-        const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
-        const int hi = lo | stride;
-        const bool desc = (lo & size) == 0;
-        const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
-        if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+  // Strides below 64 stay inside one warp (two elements per lane, exchanged with shuffles); only the wider
+  // strides go through shared memory with a block barrier.
+  if (kpow2 >= 64) {
+    const int nblk = kpow2 >> 6;
+    auto warp_phase = [&](int size_lo, int size_hi) {  // all (size, stride) steps with stride <= 32 for sizes in [lo, hi]
+      for (int blk = warp; blk < nblk; blk += kWarps) {
+        const int i0 = blk * 64 + lane, i1 = i0 + 32;
+        unsigned long long a = sortbuf[i0], b = sortbuf[i1];
+        for (int size = size_lo; size <= size_hi; size <<= 1) {
+          const bool d0 = (i0 & size) == 0, d1 = (i1 & size) == 0;
+          int stride = min(size >> 1, 32);
+          if (stride == 32) {
+            if ((a < b) == d0) { const unsigned long long t = a; a = b; b = t; }
+            stride = 16;
+          }
+          for (; stride > 0; stride >>= 1) {
+            const bool lower = (lane & stride) == 0;
+            const unsigned long long oa = __shfl_xor_sync(0xffffffffu, a, stride), ob = __shfl_xor_sync(0xffffffffu, b, stride);
+            a = (lower == d0) ? (a > oa ? a : oa) : (a < oa ? a : oa);
+            b = (lower == d1) ? (b > ob ? b : ob) : (b < ob ? b : ob);
+          }
+        }
+        sortbuf[i0] = a;
+        sortbuf[i1] = b;
       }
+    };
+    warp_phase(2, 64);
+    __syncthreads();
+    for (int size = 128; size <= kpow2; size <<= 1) {
+      for (int stride = size >> 1; stride >= 64; stride >>= 1) {
+        for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
+          const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
+          const int hi = lo | stride;
+          const bool desc = (lo & size) == 0;
+          const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
+          if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+        }
+        __syncthreads();
+      }
+      warp_phase(size, size);
       __syncthreads();
+    }
+  } else {
+    for (int size = 2; size <= kpow2; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
+          const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
+          const int hi = lo | stride;
+          const bool desc = (lo & size) == 0;
+          const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
+          if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+        }
+        __syncthreads();
+      }
     }
   }
 
