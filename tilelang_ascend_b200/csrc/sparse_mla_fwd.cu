@@ -80,7 +80,9 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //     * accumulates O[:, 256 r : 256 r + 256] = P . V[:, its latent dims]   (output columns split).
 // Per CTA: Q latent dims live in TMEM as the A operand, the Q rope dims in shared memory, KV tiles of 64
 // keys in a 3-stage cp.async ring, two score buffers in TMEM (P, as bf16, replaces the first half of its
-// tile's score buffer), so the QK^T of tile i+1 overlaps the softmax of tile i.
+// tile's score buffer), so the QK^T of tile i+1 overlaps the softmax of tile i.  Warp roles: 16 softmax warps
+// (32 rows x 16 score columns each), one warp issuing the QK^T MMAs and one the PV MMAs, 4 gather warps, 4
+// warps that load Q and ship the partial scores to the peer CTA.
 //
 // The grid is one cluster per SM pair; cluster c walks the items  n-1-c, n-1-c-C, ...  (late = long queries
 // first).  Roles run ahead of each other across items: the gather warps build the next item's tile list and
@@ -250,6 +252,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         uint32_t v[32];
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
         if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
+        // this CTA's receive barrier is armed once per use of the buffer: its previous phase (tile g-2) must be complete
+        // first -- the peer's credit above says the peer read OUR data, not that ITS data has fully landed here
+        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
         if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
         tc_fence_after();
 #pragma unroll
