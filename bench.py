@@ -30,6 +30,8 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(B=1, S=4096, S_kv=4096, H=128, D=576, DV=512, topk=2048)
 FLOP_PER_PAIR_HEAD = 2 * 576 + 2 * 512  # QK^T over 576 dims + PV over 512 dims
 METRIC, UNIT = "dsa_prefill_tokens_per_s", "tokens/s"
+# DRAM bytes per query of the forward kernel: (96 936 448 read + 35 241 728 written) / 592 queries, one ncu capture
+DRAM_BYTES_PER_QUERY = (96936448 + 35241728) / 592
 
 
 def valid_pairs(S: int, S_kv: int, topk: int) -> int:
@@ -128,11 +130,12 @@ def _time_ms(fn, reps: int = 10, warm: int = 3) -> float:
     return e0.elapsed_time(e1) / reps
 
 
-def measure_other_stages(dev, peaks) -> dict:
-    """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU."""
+def measure_other_stages(dev, peaks, small: bool = False) -> dict:
+    """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU.
+    small: the last 1024 queries / 16 sequences only (for profiler captures)."""
     import tilelang_ascend_b200 as dsa
     g = torch.Generator(device=dev).manual_seed(7)
-    S1, S2, K = 4096, 8192, 2048
+    S1, S2, K = (1024 if small else 4096), 8192, 2048
     qi = torch.randn((1, S1, 64, 128), generator=g, device=dev).to(torch.bfloat16)
     ki = torch.randn((1, S2, 1, 128), generator=g, device=dev).to(torch.bfloat16)
     wi = (torch.randn((1, S1, 64), generator=g, device=dev) / 8).float()
@@ -141,7 +144,7 @@ def measure_other_stages(dev, peaks) -> dict:
     pairs = int((np.arange(S1, dtype=np.int64) + (S2 - S1) + 1).sum())
     sc_tflops = pairs * 64 * 256 / (t_sc * 1e-3) / 1e12
     del qi, ki, wi
-    B, S_kv, H, topk = 64, 32768, 128, 2048
+    B, S_kv, H, topk = (16 if small else 64), 32768, 128, 2048
     qd = torch.randn((B, 1, H, 576), generator=g, device=dev).to(torch.bfloat16)
     kvd = torch.randn((B, S_kv, 1, 576), generator=g, device=dev).to(torch.bfloat16)
     idxd = torch.stack([torch.randperm(S_kv, generator=g, device=dev)[:topk] for _ in range(B)]).to(torch.int32).view(B, 1, 1, topk)
@@ -151,31 +154,31 @@ def measure_other_stages(dev, peaks) -> dict:
     assert dsa.kernel_status() == 0
     return {
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
-                           "workload": "S_q=4096 S_kv=8192 64 heads x 128, causal"},
+                           "workload": f"S_q={S1} S_kv=8192 64 heads x 128, causal"},
         "indexer_plus_topk": {"ms": t_all, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
         "decode": {"us": t_dec * 1e3, "tokens_per_s": B / (t_dec * 1e-3), "algorithmic_gb_per_s": dec_gbs,
                    "frac_of_hbm_peak": dec_gbs / peaks["hbm_gbs"], "algorithmic_bytes": dec_bytes,
-                   "workload": "B=64 x 1 token, S_kv=32768, H=128, topk=2048 (KV cache 2.4 GB, larger than L2)"},
+                   "workload": f"B={B} x 1 token, S_kv=32768, H=128, topk=2048 (KV cache {B * S_kv * 1152 / 1e9:.1f} GB, larger than L2)"},
     }
 
 
-def cpu_oracle_sample(q, kv, idx, rows: np.ndarray):
-    """Oracle forward on a sample of query rows (host cores): returns (out, lse, seconds, threads)."""
+def cpu_oracle_sample(q, kv, idx, starts: np.ndarray, block: int):
+    """Oracle forward on blocks of `block` consecutive query rows starting at `starts` (host cores):
+    returns (row indices, out, lse, seconds, threads)."""
     from oracle import dsa_oracle as orc
     w = WORKLOAD
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    rows_t = torch.from_numpy(rows)
-    qs, ix = q[:, rows_t].contiguous(), idx[:, rows_t].contiguous()
-    outs, lses = [], []
+    outs, lses, rows = [], [], []
     t0 = time.perf_counter()
-    # rows are arbitrary positions: run them one oracle call per row block with its own start position
-    for j, r in enumerate(rows.tolist()):
-        o, l = orc.sparse_mla_fwd(qs[:, j:j + 1], kv, ix[:, j:j + 1], q_start_index_s=(w["S_kv"] - w["S"]) + r)
+    for s0 in starts.tolist():
+        e0 = min(s0 + block, w["S"])
+        o, l = orc.sparse_mla_fwd(q[:, s0:e0], kv, idx[:, s0:e0], q_start_index_s=(w["S_kv"] - w["S"]) + s0, q_chunk=32)
         outs.append(o)
         lses.append(l)
+        rows.append(np.arange(s0, e0))
     dt = time.perf_counter() - t0
-    return torch.cat(outs, 1), torch.cat(lses, 1), dt, threads
+    return np.concatenate(rows), torch.cat(outs, 1), torch.cat(lses, 1), dt, threads
 
 
 def run_reference_arm(args, rank: int) -> None:
@@ -218,7 +221,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--cpu-sample", type=int, default=96, help="queries the CPU baseline / parity sample covers")
+    ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
+    ap.add_argument("--stage", default="prefill", choices=["prefill", "others"],
+                    help="profiling aid: 'others' runs only the indexer / top-k / decode measurements and prints them")
+    ap.add_argument("--cpu-sample", type=int, default=4096, help="queries the CPU baseline / parity sample covers")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
                          "the printed line is then not a benchmark result")
@@ -247,6 +253,10 @@ def main() -> None:
 
     w = WORKLOAD
     peaks = load_peaks()
+    if args.stage == "others":
+        if rank == 0:
+            print(json.dumps({"other_stages": measure_other_stages(dev, peaks, small=bool(args.queries))}), flush=True)
+        return
     q, kv, idx = make_inputs_cuda(1000 + rank, dev)
     kernel = dsa.sparse_attention_fwd(heads=w["H"], dim=w["DV"], tail_dim=w["D"] - w["DV"], topk=w["topk"], kv_stride=1,
                                       return_softmax_lse=True)
@@ -283,15 +293,11 @@ def main() -> None:
     idx_h = torch.empty(idx.shape, dtype=idx.dtype, pin_memory=True).copy_(idx)
     out_h = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
     lse_h = torch.empty(lse.shape, dtype=lse.dtype, pin_memory=True)
-    q_d, kv_d, idx_d = torch.empty_like(q), torch.empty_like(kv), torch.empty_like(idx)
+    # the package's host-buffer entry: query chunks are copied in, computed and copied out on three streams
+    host_fwd = dsa.HostPipelinedForward(kernel, q.shape, kv.shape, idx.shape, w["DV"], chunks=args.e2e_chunks, device=dev)
 
     def e2e_step():
-        q_d.copy_(q_h, non_blocking=True)
-        kv_d.copy_(kv_h, non_blocking=True)
-        idx_d.copy_(idx_h, non_blocking=True)
-        o, l = kernel(q_d, kv_d, idx_d)
-        out_h.copy_(o, non_blocking=True)
-        lse_h.copy_(l, non_blocking=True)
+        host_fwd(q_h, kv_h, idx_h, out_h, lse_h)
 
     e2e_ms = float("nan")
     if args.e2e_steps > 0:
@@ -322,7 +328,9 @@ def main() -> None:
                    "l2": "inputs and outputs of one step (1.18 GB) exceed the 126 MB L2; no extra flush"},
         "tflops_per_gpu": achieved,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"] + " (burst)",
+                     "frac": achieved / peaks["bf16_tflops"], "traffic": DRAM_BYTES_PER_QUERY * w["B"] * w["S"],
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 592-query launch, scaled by queries",
+                     "peak_source": peaks["source"] + " (burst)",
                      "kernel": "sparse_mla_fwd_tc_kernel", "algorithmic_flop_per_launch": flop},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
@@ -336,14 +344,17 @@ def main() -> None:
 
     # ---- CPU baseline (rank 0, N=1 only): the oracle on a bounded sample; doubles as a parity check -----
     if rank == 0 and world == 1 and args.cpu_sample > 0:
-        rows = np.unique(np.linspace(0, w["S"] - 1, args.cpu_sample).astype(np.int64))
-        ref_o, ref_l, sec, threads = cpu_oracle_sample(q.cpu(), kv.cpu(), idx.cpu(), rows)
+        block = 64
+        nblk = max(1, min(args.cpu_sample // block, w["S"] // block))
+        starts = np.unique((np.linspace(0, w["S"] - block, nblk).astype(np.int64) // block) * block)
+        rows, ref_o, ref_l, sec, threads = cpu_oracle_sample(q.cpu(), kv.cpu(), idx.cpu(), starts, block)
         got_o = out[:, torch.from_numpy(rows).to(dev)].float().cpu()
         got_l = lse[:, torch.from_numpy(rows).to(dev)].cpu()
         err_o = float((got_o - ref_o).abs().max())
         err_l = float((got_l - ref_l).abs().max())
         line["cpu_baseline"] = {"value": len(rows) / sec, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{len(rows)} evenly spaced queries of the same workload, fp32 torch oracle, {sec:.1f} s"}
+                                "sample": f"{len(rows)} queries ({len(starts)} evenly spaced blocks of {block}) of the same workload, "
+                                          f"fp32 torch oracle, {sec:.1f} s"}
         line["parity_sample"] = {"queries": len(rows), "max_abs_err_out": err_o, "max_abs_err_lse": err_l,
                                  "ok": bool(err_o <= 2e-2 + 1e-2 * float(ref_o.abs().max()) and err_l <= 2e-2 + 1e-2 * float(ref_l.abs().max()))}
     if rank == 0:

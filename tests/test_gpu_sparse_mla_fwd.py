@@ -164,3 +164,22 @@ def test_rejects_bad_inputs():
         dsa.sparse_attention_fwd(16, 512, 64, 100, 1)                # topk % block_I
     with pytest.raises(AssertionError):
         dsa.sparse_attention_fwd(16, 512, 64, 64, 1, is_causal=False)
+
+
+def test_host_buffer_pipeline_matches_direct_call():
+    import tilelang_ascend_b200 as dsa
+    B, S, S_kv, H, topk = 1, 100, 512, 128, 128
+    q, kv, idx = orc.make_sparse_mla_inputs(B, S, S_kv, H, topk, seed=8)
+    kernel = dsa.sparse_attention_fwd(H, 512, 64, topk, 1, return_softmax_lse=True)
+    ref_o, ref_l = kernel(q.cuda(), kv.cuda(), idx.cuda())
+    pipe = dsa.HostPipelinedForward(kernel, q.shape, kv.shape, idx.shape, 512, chunks=7)
+    out_h = torch.empty((B, S, H, 512), dtype=torch.bfloat16).pin_memory()
+    lse_h = torch.empty((B, S, H), dtype=torch.float32).pin_memory()
+    for _ in range(2):  # staging buffers are reused across calls
+        out_h.zero_()
+        pipe(q.pin_memory(), kv.pin_memory(), idx.pin_memory(), out_h, lse_h)
+        torch.cuda.synchronize()
+        check_status()
+        assert torch.equal(out_h, ref_o.cpu()) and torch.equal(lse_h, ref_l.cpu())
+    with pytest.raises(ValueError):
+        pipe(q, kv.pin_memory(), idx.pin_memory(), out_h, lse_h)  # not pinned

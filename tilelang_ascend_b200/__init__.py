@@ -3,6 +3,7 @@ the TileLang-Ascend examples: lightning indexer -> top-k selector -> sparse MLA 
 backward).  Python / PyTorch host code over a C-ABI CUDA library; there is no CPU fallback."""
 from . import _lib
 from .deepseek_mla import mla_decode
+from .host_pipeline import HostPipelinedForward
 from .lightning_indexer import indexer, indexer_scores_raw, lightning_indexer, lightning_indexer_raw
 from .sharding import shard_batch, shard_queries, shard_range
 from .sparse_flash_attention import (sparse_attention_fwd, sparse_attn_tilelang, sparse_mla, sparse_mla_bwd_raw,
@@ -14,5 +15,5 @@ kernel_status = _lib.kernel_status
 __all__ = [
     "indexer", "lightning_indexer", "simple_topk_selector", "sparse_attention_fwd", "sparse_attn_tilelang", "mla_decode",
     "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
-    "topk_select_raw", "shard_range", "shard_queries", "shard_batch", "kernel_status",
+    "topk_select_raw", "HostPipelinedForward", "shard_range", "shard_queries", "shard_batch", "kernel_status",
 ]
