@@ -122,12 +122,33 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same, issued only after `dep` has been computed: pass a value derived from the loads whose completion the
+// credit stands for, so that neither the compiler nor the scoreboard can let the arrive overtake them.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr, uint32_t dep) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];  // after %1" ::"r"(cluster_addr), "r"(dep) : "memory");
+}
 // Asynchronous 16-byte store into another CTA's shared memory; on landing it subtracts 16 from the
 // transaction count of the mbarrier at `cluster_mbar` (same CTA as the data).  No fence is needed.
 __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t cluster_mbar, float a, float b, float c, float d) {
   asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
                "f"(a), "f"(b), "f"(c), "f"(d), "r"(cluster_mbar)
                : "memory");
+}
+// 16-byte store to this CTA's shared memory.
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// TMA gather: four rows (r0..r3, any order, out-of-range rows read as zeros) of a 2-D tensor, columns x .. x + box
+// width, land as four consecutive rows at `smem_dst` in the tensor map's swizzle; 4 x box-width bytes are
+// subtracted from the transaction count of `mbar` (this CTA).  x times the element size must be a multiple of 16.
+__device__ __forceinline__ void tma_gather4(uint32_t smem_dst, const void* tensor_map, uint32_t mbar, int x, int r0, int r1, int r2, int r3) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(
+                   smem_dst),
+               "l"(tensor_map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(mbar)
+               : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
 // Local arrive (count 1) that also adds `tx_bytes` to the barrier's expected transaction count.
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t tx_bytes) {
@@ -277,5 +298,8 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, uint32_t M, uin
 // Byte offset of the 16-byte unit `unit` (0..7) of row `row` inside a [rows x 128 B] tile laid
 // out with the 128-byte swizzle (tile base aligned to 1024 B): unit index XOR (row mod 8).
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t unit) { return row * 128u + ((unit ^ (row & 7u)) << 4); }
+// Same for rows of 64 bytes in the 64-byte swizzle: 16-byte unit u (0..3) of row r, relative to a 512-byte aligned
+// base; the unit index is XORed with bits 1..2 of the row (address bits 4..5 with bits 7..8).
+__device__ __forceinline__ uint32_t sw64_offset(uint32_t row, uint32_t unit) { return row * 64u + ((unit ^ ((row >> 1) & 3u)) << 4); }
 
 }  // namespace dsa

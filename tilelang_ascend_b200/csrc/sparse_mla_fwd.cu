@@ -79,7 +79,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //     * runs the (identical) online softmax, and
 //     * accumulates O[:, 256 r : 256 r + 256] = P . V[:, its latent dims]   (output columns split).
 // Per CTA: Q latent dims live in TMEM as the A operand, the Q rope dims in shared memory, KV tiles of 64
-// keys in a 3-stage cp.async ring, two score buffers in TMEM (P, as bf16, replaces the first half of its
+// keys in a 4-stage cp.async ring, two score buffers in TMEM (P, as bf16, replaces the first half of its
 // tile's score buffer), so the QK^T of tile i+1 overlaps the softmax of tile i.  Warp roles: 16 softmax warps
 // (32 rows x 16 score columns each), one warp issuing the QK^T MMAs and one the PV MMAs, 4 gather warps, 4
 // warps that load Q and ship the partial scores to the peer CTA.
@@ -94,16 +94,19 @@ namespace tc {
 constexpr int kD = 576, kDV = 512;
 constexpr int kM = 128;                               // heads per cluster = UMMA M
 constexpr int kBK = 64;                               // keys per tile
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kHalfDV = 256;                          // output columns (and latent dims) per CTA
 constexpr int kMaxTiles = 128;                        // topk <= 8192
 constexpr uint32_t kChunkBytes = kBK * 128;           // 8192: 64 keys x 64 dims, 128-byte swizzle
-constexpr uint32_t kStageBytes = 5 * kChunkBytes;     // 4 latent chunks + the rope chunk (half of each row in use)
-constexpr uint32_t kQRopeBytes = kM * 128;            // Q rope dims, same half-used row layout
+constexpr uint32_t kRopeOff = 4 * kChunkBytes;        // the CTA's 32 rope dims of the 64 keys: rows of 64 bytes, 64-byte swizzle
+constexpr uint32_t kStageBytes = kRopeOff + kBK * 64; // 36864: 4 latent chunks + the rope chunk
+constexpr uint32_t kQRopeBytes = kM * 64;             // Q rope dims, same 64-byte rows
 constexpr uint32_t kXBytes = kM * kBK * 4;            // peer's partial scores [128 x 64] fp32
-constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 122880
-constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 139264
-constexpr uint32_t kOffBar = kOffX + 2 * kXBytes;                 // 204800
+constexpr uint32_t kPBytes = kM * kBK * 2;            // P of one tile [128 x 64] bf16/fp16, 128-byte swizzle (A operand of PV)
+constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 147456
+constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 155648
+constexpr uint32_t kOffP = kOffX + kXBytes;                       // 188416: two P buffers
+constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;                 // 221184
 constexpr uint32_t kOffPair = kOffBar + 512;                      // [3][512] floats exchanged between the four column quarters
 constexpr uint32_t kOffMask = kOffPair + 3 * 512 * 4;             // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;       // [2][kMaxTiles] 16-bit tile ids
@@ -117,6 +120,7 @@ constexpr int kPvWarp = 25;                           // second MMA-issuing warp
 constexpr int kThreads = 832;                         // 16 softmax warps, 2 MMA warps, 4 gather warps, 4 exchange warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
+static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8
 constexpr uint32_t kGatherBarrier = 5;                // named barrier of the 128 gather threads
 }  // namespace tc
@@ -129,19 +133,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   const uint32_t sBase = smem_u32(smem);
   const uint32_t sQRope = sBase + kOffQRope, sX = sBase + kOffX;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
-  uint64_t* kv_full = bars;         // [3] count 128: cp.async completion of the gather threads
-  uint64_t* kv_empty = bars + 3;    // [3] count 1: commit after the PV MMAs of the stage
-  uint64_t* s_full = bars + 6;      // [2] count 1: commit after the QK MMAs
-  uint64_t* s_read = bars + 8;      // [2] count 4: the exchange warps have read the partial scores out of TMEM
-  uint64_t* p_full = bars + 10;     // count 16: softmax warps wrote P into TMEM
+  uint64_t* kv_full = bars;         // [4] count 128: cp.async completion of the gather threads
+  uint64_t* kv_empty = bars + 4;    // [4] count 1: commit after the PV MMAs of the stage
+  uint64_t* s_full = bars + 8;      // [2] count 1: commit after the QK MMAs
+  uint64_t* p_full = bars + 10;     // count 16: softmax warps wrote P into shared memory
   uint64_t* pv_done = bars + 11;    // count 1: commit after the PV MMAs of a tile
-  uint64_t* x_full = bars + 12;     // [2][4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
-  uint64_t* x_empty = bars + 20;    // [2][4] count 4: all peer softmax warps of these rows consumed what this CTA sent
+  uint64_t* x_full = bars + 12;     // [4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
+  uint64_t* x_empty = bars + 20;    // [4] count 4: all peer softmax warps of these rows have read what this CTA sent
   uint64_t* info_full = bars + 28;  // [2] count 1: tile list of an item published by the gather warps
   uint64_t* info_empty = bars + 30; // [2] count 22: both MMA threads, softmax and exchange warps are done with the item's tile list
   uint64_t* q_ready = bars + 32;    // count 4: the exchange warps put the item's Q into TMEM / shared memory
   uint64_t* o_free = bars + 33;     // count 16: the softmax warps drained the previous item's output tile from TMEM
-  uint64_t* s_free = bars + 34;     // [2] count 1: commit after the PV MMAs that read P out of this score buffer
+  uint64_t* s_free = bars + 34;     // [2] count 16: the softmax warps have read the scores of this buffer out of TMEM
+  uint64_t* p_free = bars + 24;     // [2] count 1: commit after the PV MMAs that read this P buffer
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 36);
   int* start_status = reinterpret_cast<int*>(bars + 37);
   float* pair = reinterpret_cast<float*>(smem + kOffPair);
@@ -165,11 +169,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     *start_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&s_read[i], 4);
+      mbar_init(&s_full[i], 1);
       mbar_init(&info_full[i], 1); mbar_init(&info_empty[i], 2 + kSoftmaxWarps + 4);
-      mbar_init(&s_free[i], 1);
+      mbar_init(&s_free[i], kSoftmaxWarps); mbar_init(&p_free[i], 1);
     }
-    for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 4); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 4); }
     mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     mbar_init(q_ready, 4);
@@ -215,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0 + (row_ok ? r : 0)) * (kD * 2);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-          cp_async16(sQRope + sw128_offset(r, 4 * rank + u), qrow + 1024 + (4 * rank + u) * 16, row_ok ? 16u : 0u);
+          cp_async16(sQRope + sw64_offset(r, u), qrow + 1024 + (4 * rank + u) * 16, row_ok ? 16u : 0u);
         cp_async_commit();
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
@@ -248,14 +252,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         }
       }
       for (int it = 0; it < nvt; ++it, ++g) {
-        const int sb = g & 1, xq = sb * 4 + q4;
+        const int sb = g & 1;
         uint32_t v[32];
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
-        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
-        // this CTA's receive barrier is armed once per use of the buffer: its previous phase (tile g-2) must be complete
+        // the peer's softmax warps have read tile g-1 of these rows out of their receive buffer
+        if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[q4], (g + 1) & 1, p.status))) { ok = false; break; }
+        // this CTA's receive barrier is armed once per tile: its previous phase (tile g-1) must be complete
         // first -- the peer's credit above says the peer read OUR data, not that ITS data has fully landed here
-        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[xq], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
-        if (lane == 0) mbar_arrive_expect_tx(&x_full[xq], 32 * 256);  // arm this CTA's receive barrier for the same rows
+        if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[q4], (g + 1) & 1, p.status))) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
@@ -263,12 +267,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            st_async_v4(peer_x + sb * kXBytes + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + xq * 8, __uint_as_float(v[4 * j]),
+            st_async_v4(peer_x + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + q4 * 8, __uint_as_float(v[4 * j]),
                         __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
+        // Arm this CTA's receive barrier for the same rows only now: its completion then tells the softmax warps of
+        // this row block three things at once -- the peer's partial scores have landed, this CTA's own QK MMAs of the
+        // tile are complete (s_full was waited for above), and this warp has read its copy of the scores out of TMEM,
+        // so they may be overwritten by P.
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_read[sb]);
+        if (lane == 0) mbar_arrive_expect_tx(&x_full[q4], 32 * 256);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&info_empty[qp]);
@@ -313,22 +321,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       const int nvt = info[qp * 2];
       for (int it = 0; it < nvt; ++it, ++g) {
         const int tile = tile_list[qp * kMaxTiles + it], s = g % kStages;
-        if (g >= kStages && ok) ok = mbar_wait<true>(&kv_empty[s], ((g / kStages) + 1) & 1, p.status);
-        if (!ok) continue;
-        const uint32_t stage = sBase + s * kStageBytes;
+        // the row numbers are fetched before the wait for the stage, so their latency is hidden behind it
         const int slot = tile * kBK + pw * 16 + (lane & 15);
         const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
         const bool my_valid = index_valid(ctx, my_idx);
-        const long long my_row = my_valid ? kv_row(p, ctx.b, my_idx) : -1ll;
+        // byte offset of the row inside kv (lanes 0..15 and 16..31 hold the same 16 keys); keys that do not take part
+        // are fetched with a source size of zero, which fills the destination with zeros
+        const long long my_off = my_valid ? kv_row(p, ctx.b, my_idx) * (kD * 2) : 0ll;
+        const uint32_t vmask = __ballot_sync(0xffffffffu, my_valid);
+        if (g >= kStages && ok) ok = mbar_wait<true>(&kv_empty[s], ((g / kStages) + 1) & 1, p.status);
+        if (!ok) continue;
+        const uint32_t stage = sBase + s * kStageBytes;
+        const uint8_t* lat_src = kv_bytes + rank * 512 + lane * 16;
+        const uint32_t lat_dst = stage + (lane >> 3) * kChunkBytes;
 #pragma unroll 4
         for (int kk = 0; kk < 16; ++kk) {
-          const long long row = __shfl_sync(0xffffffffu, my_row, kk);
-          const bool v = row >= 0;
-          const int key = pw * 16 + kk;
-          const uint8_t* base = kv_bytes + (v ? row : 0) * (kD * 2);
-          cp_async16(stage + (lane >> 3) * kChunkBytes + sw128_offset(key, lane & 7), base + rank * 512 + lane * 16, v ? 16u : 0u);
-          if (lane < 4)
-            cp_async16(stage + 4 * kChunkBytes + sw128_offset(key, 4 * rank + lane), base + 1024 + (4 * rank + lane) * 16, v ? 16u : 0u);
+          const long long off = __shfl_sync(0xffffffffu, my_off, kk);
+          cp_async16(lat_dst + sw128_offset(pw * 16 + kk, lane & 7), lat_src + off, ((vmask >> kk) & 1u) ? 16u : 0u);
+        }
+        // the 64 rope bytes of the 16 keys: 4 lanes per key, two instructions
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const int kk = hh * 8 + (lane >> 2);
+          const long long off = __shfl_sync(0xffffffffu, my_off, kk);
+          cp_async16(stage + kRopeOff + sw64_offset(pw * 16 + kk, lane & 3), kv_bytes + off + 1024 + (4 * rank + (lane & 3)) * 16,
+                     ((vmask >> kk) & 1u) ? 16u : 0u);
         }
         cp_async_arrive_noinc(&kv_full[s]);
       }
@@ -355,7 +372,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           const int s = g % kStages, sb = g & 1;
           const uint32_t stage = sBase + s * kStageBytes;
           if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
-          // the score buffer still holds P of tile g-2 until the PV MMAs of that tile have read it
+          // the softmax warps must have read the scores of tile g-2 out of this buffer
           if (g >= 2 && !mbar_wait(&s_free[sb], ((g >> 1) + 1) & 1, p.status)) { ok = false; break; }
           fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
           tc_fence_after();
@@ -366,12 +383,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
             for (int kq = 0; kq < 4; ++kq)
               umma_ts(tS + sb * kBK, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
           }
-          const uint64_t da0 = make_smem_desc(sQRope, 16, 1024, kSwizzle128B);
+          const uint64_t da0 = make_smem_desc(sQRope, 16, 512, kSwizzle64B);
+          const uint64_t dr0 = make_smem_desc(stage + kRopeOff, 16, 512, kSwizzle64B);
 #pragma unroll
-          for (int kq = 0; kq < 2; ++kq) {
-            const uint32_t off = (2 * rank + kq) * 32;
-            umma_ss(tS + sb * kBK, da0 + (off >> 4), db0 + ((4 * kChunkBytes + off) >> 4), idesc_qk, 1);
-          }
+          for (int kq = 0; kq < 2; ++kq) umma_ss(tS + sb * kBK, da0 + ((kq * 32) >> 4), dr0 + ((kq * 32) >> 4), idesc_qk, 1);
           umma_commit(&s_full[sb]);
         }
         if (!ok) break;
@@ -380,7 +395,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     }
   } else if (warp == kPvWarp) {
     // ================================ PV issuer =====================================================
-    // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P in TMEM (16 keys = 8 columns per step), V MN-major.
+    // O_r[128 x 256] += P[128 x 64] . V[64 x 256] : P K-major in shared memory (16 keys = 32 bytes per step), V MN-major.
     if (lane == 0) {
       constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, kHalfDV, 0, 1);
       int g = 0, ne = 0;
@@ -398,11 +413,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           tc_fence_after();
           const uint32_t stage = sBase + (g % kStages) * kStageBytes;
           const uint64_t db0 = make_smem_desc(stage, kChunkBytes, 1024, kSwizzle128B);
+          const uint64_t dp0 = make_smem_desc(sBase + kOffP + (g & 1) * kPBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int ks = 0; ks < kBK / 16; ++ks)
-            umma_ts(tO, tS + (g & 1) * kBK + ks * 8, db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
+            umma_ss(tO, dp0 + ((ks * 32) >> 4), db0 + ((ks * 2048) >> 4), idesc_pv, (it | ks) != 0);
           umma_commit(&kv_empty[g % kStages]);
-          umma_commit(&s_free[g & 1]);
+          umma_commit(&p_free[g & 1]);
           umma_commit(pv_done);
         }
         if (!ok) break;
@@ -432,22 +448,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       for (int it = 0; it < nvt; ++it, ++g) {
         const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (16 * cq)) & 0xffffu;
         const int sb = g & 1;
-        const int xq = sb * 4 + q4;  // exchange barriers are per (buffer, 32-row block)
         uint32_t v[16];
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g >> 1) & 1, p.status));
+        // one wait per tile: x_full completes after the peer's partial scores landed AND this CTA's exchange warp of the
+        // same rows armed it, which it does after s_full and after its own read of the scores (see there)
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[q4], g & 1, p.status));
         tc_fence_after();
         tmem_ld16(tS + sb * kBK + cq * 16 + lane_base, v);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[sb]);  // the QK^T of tile g+2 may overwrite the buffer
         // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[xq], (g >> 1) & 1, p.status));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + sb * kXBytes + (4 * cq + j) * (kM * 16) + r * 16);
+          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + (4 * cq + j) * (kM * 16) + r * 16);
           v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o.x);
           v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o.y);
           v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o.z);
           v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o.w);
         }
+        // the peer's scores are in registers (the sums above consumed them): one credit per warp lets the peer send the
+        // next tile's rows into the single receive buffer
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + q4 * 8, v[0]);
         float mx = -INFINITY;
         if (mask == 0xffffu) {
           float m4[4];
@@ -465,6 +488,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         // shared memory.  After this barrier all four warps have also finished reading the scores of the tile.
         float* slot = pair + (g & 1) * 512;
         slot[cq * 128 + r] = mx;
+        // exponentials relative to this quarter's own maximum, before the barrier: the MUFU work overlaps the wait for
+        // the slower warps, and only one correction factor per thread is left for afterwards
+        const float m_loc = mx * p.scale_log2;                      // -inf when no key of this quarter takes part
+        const float neg_loc = (mx == -INFINITY) ? 0.f : -m_loc;
+        float pe[16];
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float e = exp2f(fmaf(__uint_as_float(v[j]), p.scale_log2, neg_loc));
+          if (mask != 0xffffu) e = ((mask >> j) & 1u) ? e : 0.f;
+          pe[j] = e;
+          sum4[j & 3] += e;
+        }
         named_bar_sync(1 + q4, 128);
         mx = fmaxf(fmaxf(slot[r], slot[128 + r]), fmaxf(slot[256 + r], slot[384 + r])) * p.scale_log2;
         // ---- online softmax with a lazily updated reference maximum ----
@@ -487,33 +523,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
             tmem_st32(tO + lane_base + cc * 32, o);
           }
         }
-        l *= factor;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float neg_m = -m_used;
+        const float corr = exp2f(m_loc - m_used);                  // <= 2^8; 0 for a quarter without keys
+        l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * corr;
         uint32_t pk[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float p0 = exp2f(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, neg_m));
-          if (mask != 0xffffu) {
-            p0 = ((mask >> (2 * j)) & 1u) ? p0 : 0.f;
-            p1 = ((mask >> (2 * j + 1)) & 1u) ? p1 : 0.f;
-          }
-          sum4[j & 3] += p0 + p1;
-          pk[j] = pack2<kBF16>(p0, p1);
-        }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        // P (column c = keys 2c, 2c+1) replaces the first 32 columns of this tile's score buffer; the exchange warps
-        // must have read their copy of the scores first
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&s_read[sb], (g >> 1) & 1, p.status));
-        tmem_st8(tS + sb * kBK + cq * 8 + lane_base, pk);
-        tmem_wait_st();
-        tc_fence_before();
+        for (int j = 0; j < 8; ++j) pk[j] = pack2<kBF16>(pe[2 * j] * corr, pe[2 * j + 1] * corr);
+        // P goes to shared memory as the K-major A operand of the PV MMAs: row r, keys 16 cq .. 16 cq + 15 = two 16-byte
+        // units.  The buffer was last read by the PV MMAs of tile g-2.
+        if (g >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((g >> 1) + 1) & 1, p.status));
+        const uint32_t prow = sBase + kOffP + sb * kPBytes;
+        st_shared_v4(prow + sw128_offset(r, 2 * cq), pk[0], pk[1], pk[2], pk[3]);
+        st_shared_v4(prow + sw128_offset(r, 2 * cq + 1), pk[4], pk[5], pk[6], pk[7]);
+        fence_proxy_async_smem();  // read by the tensor core (async proxy)
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(p_full);
-          mbar_arrive_cluster_relaxed(peer_x_empty + xq * 8);  // one credit per warp: the peer may overwrite these rows
-        }
+        if (lane == 0) mbar_arrive(p_full);
       }
       // ---- epilogue: each thread normalises and stores its 64 of the CTA's 256 output columns ----
       if (nvt > 0) {  // row sum = sum of the four column quarters, exchanged like the maxima
