@@ -107,16 +107,17 @@ constexpr uint32_t kOffQRope = kStages * kStageBytes;             // 147456
 constexpr uint32_t kOffX = kOffQRope + kQRopeBytes;               // 155648
 constexpr uint32_t kOffP = kOffX + kXBytes;                       // 188416: two P buffers
 constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;                 // 221184
-constexpr uint32_t kOffMask = kOffBar + 512;                      // [2][kMaxTiles] 64-bit validity masks (per item parity)
+constexpr uint32_t kOffHalfMax = kOffBar + 512;                   // [3][2][128] floats exchanged between the two column halves
+constexpr uint32_t kOffMask = kOffHalfMax + 3 * 256 * 4;          // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;       // [2][kMaxTiles] 16-bit tile ids
 constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;       // [2] {tile count, run flag}
 constexpr uint32_t kSmemBytes = kOffInfo + 64 + 1024;             // + slack to align the base to 1024 B
-constexpr int kSoftmaxWarps = 4;                      // warp w: rows 32 w .. 32 w + 31, one thread per row
-constexpr int kFirstExchangeWarp = 4;                 // warp w sends rows 32 (w & 3) .. +31 of the partial scores to the peer
-constexpr int kFirstGatherWarp = 8;
-constexpr int kMmaWarp = 12;                          // QK^T issuer
-constexpr int kPvWarp = 13;                           // second MMA-issuing warp (PV), on another scheduler than the QK issuer
-constexpr int kThreads = 448;                         // 4 softmax warps, 4 exchange warps, 4 gather warps, 2 MMA warps
+constexpr int kSoftmaxWarps = 8;                      // warp w: rows 32 (w & 3) .. +31, score columns 32 (w >> 2) .. +31
+constexpr int kFirstExchangeWarp = 8;                 // warp w sends rows 32 (w & 3) .. +31 of the partial scores to the peer
+constexpr int kFirstGatherWarp = 12;
+constexpr int kMmaWarp = 16;                          // QK^T issuer
+constexpr int kPvWarp = 17;                           // second MMA-issuing warp (PV), on another scheduler than the QK issuer
+constexpr int kThreads = 576;                         // 8 softmax warps, 4 exchange warps, 4 gather warps, 2 MMA warps
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384;  // O 256 | S0 64 | S1 64 | Q latent 128 (256 bf16 dims)
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
@@ -135,18 +136,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   uint64_t* kv_full = bars;         // [4] count 128: cp.async completion of the gather threads
   uint64_t* kv_empty = bars + 4;    // [4] count 1: commit after the PV MMAs of the stage
   uint64_t* s_full = bars + 8;      // [2] count 1: commit after the QK MMAs
-  uint64_t* p_full = bars + 26;     // [2] count 4: softmax warps wrote P into this buffer (one barrier per buffer: the
+  uint64_t* p_full = bars + 40;     // [2] count 8: softmax warps wrote P into this buffer (one barrier per buffer: the
                                     // softmax warps are not in step with each other, one may be a tile ahead of another)
-  uint64_t* x_full = bars + 12;     // [4] count 1 + 8192 transaction bytes: 32 rows of the peer's partial scores landed here
-  uint64_t* x_empty = bars + 20;    // [4] count 1: the peer's softmax warp of these rows has read what this CTA sent
+  uint64_t* x_full = bars + 12;     // [4][2] count 1 + 4096 transaction bytes: 32 rows x 32 columns of the peer's partial scores landed here
+  uint64_t* x_empty = bars + 20;    // [4][2] count 1: the peer's softmax warp of these rows and columns has read what this CTA sent
   uint64_t* info_full = bars + 28;  // [2] count 1: tile list of an item published by the gather warps
-  uint64_t* info_empty = bars + 30; // [2] count 10: both MMA threads, softmax and exchange warps are done with the item's tile list
+  uint64_t* info_empty = bars + 30; // [2] count 14: both MMA threads, softmax and exchange warps are done with the item's tile list
   uint64_t* q_ready = bars + 32;    // count 4: the exchange warps put the item's Q into TMEM / shared memory
-  uint64_t* o_free = bars + 33;     // count 4: the softmax warps drained the previous item's output tile from TMEM
-  uint64_t* s_free = bars + 34;     // [2] count 4: the softmax warps have read the scores of this buffer out of TMEM
-  uint64_t* p_free = bars + 24;     // [2] count 1: commit after the PV MMAs that read this P buffer (= that tile's PV is complete)
+  uint64_t* o_free = bars + 33;     // count 8: the softmax warps drained the previous item's output tile from TMEM
+  uint64_t* s_free = bars + 34;     // [2] count 8: the softmax warps have read the scores of this buffer out of TMEM
+  uint64_t* p_free = bars + 38;     // [2] count 1: commit after the PV MMAs that read this P buffer (= that tile's PV is complete)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 36);
   int* start_status = reinterpret_cast<int*>(bars + 37);
+  float* halfmax = reinterpret_cast<float*>(smem + kOffHalfMax);
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(smem + kOffMask);
   uint16_t* tile_list = reinterpret_cast<uint16_t*>(smem + kOffList);
   int* info = reinterpret_cast<int*>(smem + kOffInfo);  // [2][2]
@@ -171,7 +173,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       mbar_init(&info_full[i], 1); mbar_init(&info_empty[i], 2 + kSoftmaxWarps + 4);
       mbar_init(&s_free[i], kSoftmaxWarps); mbar_init(&p_free[i], 1);
     }
-    for (int i = 0; i < 4; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+    for (int i = 0; i < 8; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
     mbar_init(&p_full[0], kSoftmaxWarps); mbar_init(&p_full[1], kSoftmaxWarps);
     mbar_init(q_ready, 4);
     mbar_init(o_free, kSoftmaxWarps);
@@ -252,28 +254,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const int sb = g & 1;
         uint32_t v[32];
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
-        // the peer's softmax warps have read tile g-1 of these rows out of their receive buffer
-        if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[q4], (g + 1) & 1, p.status))) { ok = false; break; }
-        // this CTA's receive barrier is armed once per tile: its previous phase (tile g-1) must be complete
-        // first -- the peer's credit above says the peer read OUR data, not that ITS data has fully landed here
-        if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[q4], (g + 1) & 1, p.status))) { ok = false; break; }
         tc_fence_after();
+        // The receive buffer is handled in two column halves with their own barriers, so that the peer's first half
+        // can be on its way while the second half of the previous tile is still being read there.
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
+          const int xb = q4 * 2 + hf;
+          // the peer's softmax warp has read this half of tile g-1 out of its receive buffer
+          if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_empty[xb], (g + 1) & 1, p.status))) { ok = false; break; }
+          // this CTA's receive barrier is armed once per tile: its previous phase (tile g-1) must be complete first --
+          // the peer's credit above says the peer read OUR data, not that ITS data has fully landed here
+          if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[xb], (g + 1) & 1, p.status))) { ok = false; break; }
           tmem_ld32(tS + sb * kBK + hf * 32 + lane_base, v);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            st_async_v4(peer_x + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + q4 * 8, __uint_as_float(v[4 * j]),
+            st_async_v4(peer_x + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + xb * 8, __uint_as_float(v[4 * j]),
                         __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+          // Arm this CTA's receive barrier for the same rows and columns only now: its completion then tells the softmax
+          // warp of this block three things at once -- the peer's partial scores have landed, this CTA's own QK MMAs of
+          // the tile are complete (s_full was waited for above), and this warp has read its copy of these scores out
+          // of TMEM (the softmax warps report the score buffer free after their own read).
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_expect_tx(&x_full[xb], 32 * 128);
         }
-        // Arm this CTA's receive barrier for the same rows only now: its completion then tells the softmax warps of
-        // this row block three things at once -- the peer's partial scores have landed, this CTA's own QK MMAs of the
-        // tile are complete (s_full was waited for above), and this warp has read its copy of the scores out of TMEM,
-        // so they may be overwritten by P.
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_expect_tx(&x_full[q4], 32 * 256);
+        if (!ok) break;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&info_empty[qp]);
@@ -424,60 +430,86 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     }
   } else {
     // ================================ softmax + epilogue ============================================
-    // thread = row r (= TMEM lane) of the 128 heads: it owns all 64 scores of the row in a tile and all 256 output
-    // columns of the CTA, so neither the row maximum nor the row sum needs another thread.
-    const int q4 = warp;  // 32-row block
+    // thread = (row r, column half ch): r = TMEM lane, ch selects 32 of the tile's 64 score columns and 128 of the
+    // CTA's 256 output columns.  The two warps of a row block combine their row maxima through shared memory and
+    // a 64-thread named barrier once per tile; everything else is thread-local.  A failed wait clears `ok` but does
+    // not leave the loops (the partner warp would wait at the named barrier): the remaining tiles are walked
+    // without waiting.
+    const int q4 = warp & 3, ch = warp >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
     int g = 0;
-    for (int k = 0; run_all && ok; ++k) {
+    for (int k = 0; run_all; ++k) {
       const int item = item_of(k);
       if (item < 0) break;
       const int qp = k & 1;
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
-      if (!__all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status))) { ok = false; break; }
-      const int nvt = info[qp * 2];
-      const bool active = info[qp * 2 + 1] != 0;
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status));
+      const int nvt = info[qp * 2];  // read unconditionally: both warps of a row block must walk the same number of tiles
+      const bool active = ok && info[qp * 2 + 1] != 0;
       float m_used = -INFINITY, l = 0.f;
       for (int it = 0; it < nvt; ++it, ++g) {
-        const unsigned long long mask = masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]];
+        const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (32 * ch));
         const int sb = g & 1;
-        uint32_t sc[64];  // scores as raw bits (TMEM loads), used as floats below
+        uint32_t sc[32];  // scores as raw bits (TMEM loads), used as floats below
         // one wait per tile: x_full completes after the peer's partial scores landed AND this CTA's exchange warp of the
         // same rows armed it, which it does after s_full and after its own read of the scores (see there)
-        if (!__all_sync(0xffffffffu, mbar_wait(&x_full[q4], g & 1, p.status))) { ok = false; break; }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[q4 * 2 + ch], g & 1, p.status));
         tc_fence_after();
-        tmem_ld32(tS + sb * kBK + lane_base, sc);
-        tmem_ld32(tS + sb * kBK + 32 + lane_base, sc + 32);
+        tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, sc);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free[sb]);  // the QK^T of tile g+2 may overwrite the buffer
         // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + u * (kM * 16) + r * 16);
-          sc[4 * u] = __float_as_uint(__uint_as_float(sc[4 * u]) + o.x);
-          sc[4 * u + 1] = __float_as_uint(__uint_as_float(sc[4 * u + 1]) + o.y);
-          sc[4 * u + 2] = __float_as_uint(__uint_as_float(sc[4 * u + 2]) + o.z);
-          sc[4 * u + 3] = __float_as_uint(__uint_as_float(sc[4 * u + 3]) + o.w);
+        for (int j = 0; j < 8; ++j) {
+          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + (8 * ch + j) * (kM * 16) + r * 16);
+          sc[4 * j] = __float_as_uint(__uint_as_float(sc[4 * j]) + o.x);
+          sc[4 * j + 1] = __float_as_uint(__uint_as_float(sc[4 * j + 1]) + o.y);
+          sc[4 * j + 2] = __float_as_uint(__uint_as_float(sc[4 * j + 2]) + o.z);
+          sc[4 * j + 3] = __float_as_uint(__uint_as_float(sc[4 * j + 3]) + o.w);
         }
         // the peer's scores are in registers (the sums above consumed them): one credit per warp lets the peer send the
         // next tile's rows into the single receive buffer
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + q4 * 8, sc[63]);
-        const bool full = mask == ~0ull;
+        if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + (q4 * 2 + ch) * 8, sc[31]);
+        const bool full = mask == 0xffffffffu;
         float mx;
-        {
-          float m8[8];
+        if (full) {
+          float m4[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) m8[j] = (full || ((mask >> j) & 1ull)) ? __uint_as_float(sc[j]) : -INFINITY;
+          for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(sc[j]), __uint_as_float(sc[j + 4]));
 #pragma unroll
-          for (int j = 8; j < 64; ++j) m8[j & 7] = fmaxf(m8[j & 7], (full || ((mask >> j) & 1ull)) ? __uint_as_float(sc[j]) : -INFINITY);
-          mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7]))) * p.scale_log2;
+          for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(sc[j]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        } else {
+          mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(sc[j]));
         }
-        // ---- online softmax with a lazily updated reference maximum ----
+        // the other column half of this row lives in the warp with the same (w & 3): combine the maxima through shared
+        // memory (double-buffered by tile parity)
+        float* slot = halfmax + (g & 1) * 256;
+        slot[ch * 128 + r] = mx;
+        // exponentials relative to this half's own maximum, before the barrier: the MUFU work overlaps the wait for the
+        // partner warp, and only one correction factor per thread is left for afterwards
+        const float m_loc = mx * p.scale_log2;                      // -inf when no key of this half takes part
+        const float neg_loc = (mx == -INFINITY) ? 0.f : -m_loc;
+        float pe[32];
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float e = exp2f(fmaf(__uint_as_float(sc[j]), p.scale_log2, neg_loc));
+          if (!full) e = ((mask >> j) & 1u) ? e : 0.f;
+          pe[j] = e;
+          sum4[j & 3] += e;
+        }
+        named_bar_sync(1 + q4, 64);
+        mx = fmaxf(slot[r], slot[128 + r]) * p.scale_log2;
+        // ---- online softmax with a lazily updated reference maximum (identical in both warps of the row block) ----
         float factor = 1.f;
         if (mx > m_used + kRescaleThreshold || m_used == -INFINITY) {
           factor = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
@@ -487,11 +519,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           // O must be quiescent: the PV MMAs of the previous tile are done.  (Waited for on that tile's P buffer barrier:
           // its phase before -- tile g-3 -- was already waited for when P of tile g-1 was written, so the parity
           // test cannot be fooled by a barrier that is two phases behind.)
-          if (!__all_sync(0xffffffffu, mbar_wait(&p_free[(g - 1) & 1], ((g - 1) >> 1) & 1, p.status))) { ok = false; break; }
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&p_free[(g - 1) & 1], ((g - 1) >> 1) & 1, p.status));
           tc_fence_after();
           uint32_t o[32];
 #pragma unroll 1
-          for (int cc = 0; cc < kHalfDV / 32; ++cc) {
+          for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {  // this thread's half of the output columns
             tmem_ld32(tO + lane_base + cc * 32, o);
             tmem_wait_ld();
 #pragma unroll
@@ -501,51 +533,46 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           tmem_wait_st();
           tc_fence_before();
         }
-        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[32];
+        const float corr = exp2f(m_loc - m_used);                  // <= 2^8; 0 for a half without keys
+        l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * corr;
+        uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float e0 = exp2f(fmaf(__uint_as_float(sc[2 * j]), p.scale_log2, neg_m));
-          float e1 = exp2f(fmaf(__uint_as_float(sc[2 * j + 1]), p.scale_log2, neg_m));
-          if (!full) {
-            e0 = ((mask >> (2 * j)) & 1ull) ? e0 : 0.f;
-            e1 = ((mask >> (2 * j + 1)) & 1ull) ? e1 : 0.f;
-          }
-          sum4[j & 3] += e0 + e1;
-          pk[j] = pack2<kBF16>(e0, e1);
-        }
-        l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        // P goes to shared memory as the K-major A operand of the PV MMAs: row r = eight 16-byte units of 8 keys.
-        // The buffer was last read by the PV MMAs of tile g-2.
-        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
+        for (int j = 0; j < 16; ++j) pk[j] = pack2<kBF16>(pe[2 * j] * corr, pe[2 * j + 1] * corr);
+        // P goes to shared memory as the K-major A operand of the PV MMAs: row r, keys 32 ch .. 32 ch + 31 = four 16-byte
+        // units.  The buffer was last read by the PV MMAs of tile g-2.
+        if (g >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((g >> 1) + 1) & 1, p.status));
         const uint32_t prow = sBase + kOffP + sb * kPBytes;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) st_shared_v4(prow + sw128_offset(r, u), pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        for (int u = 0; u < 4; ++u) st_shared_v4(prow + sw128_offset(r, 4 * ch + u), pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         fence_proxy_async_smem();  // read by the tensor core (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[sb]);
       }
-      if (!ok) break;
-      // ---- epilogue: each thread normalises and stores its row of the CTA's 256 output columns ----
+      // ---- epilogue: each thread normalises and stores its 128 of the CTA's 256 output columns ----
+      if (nvt > 0) {  // row sum = sum of the two column halves, exchanged like the maxima
+        float* slot = halfmax + 2 * 256;
+        slot[ch * 128 + r] = l;
+        named_bar_sync(1 + q4, 64);
+        l = slot[r] + slot[128 + r];  // (the slot is rewritten only after the next item's barriers)
+      }
       const int h = h0 + r;
       T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
       if (active && nvt == 0) {
         if (h < p.H) {
-          for (int j = 0; j < kHalfDV / 8; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
-          if (rank == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+          for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
+          if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
         }
       } else if (nvt > 0) {
         // the last PV of the item is complete (same barrier and argument as for the rescale above)
-        if (!__all_sync(0xffffffffu, mbar_wait(&p_free[(g - 1) & 1], ((g - 1) >> 1) & 1, p.status))) { ok = false; break; }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&p_free[(g - 1) & 1], ((g - 1) >> 1) & 1, p.status));
         tc_fence_after();
         const float inv_l = 1.f / l;
         uint32_t v[32];
 #pragma unroll 1
-        for (int cc = 0; cc < kHalfDV / 32; ++cc) {
+        for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
           tmem_ld32(tO + lane_base + cc * 32, v);
           tmem_wait_ld();
-          if (h < p.H) {
+          if (ok && h < p.H) {
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
               uint4 w;
@@ -557,7 +584,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
             }
           }
         }
-        if (rank == 0 && p.lse && h < p.H) p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
+        if (ok && rank == 0 && ch == 0 && p.lse && h < p.H) p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
       }
       tc_fence_before();
       __syncwarp();
