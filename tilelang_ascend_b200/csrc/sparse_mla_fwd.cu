@@ -328,27 +328,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const int slot = tile * kBK + pw * 16 + (lane & 15);
         const int my_idx = slot < p.topk ? __ldg(ctx.idx_row + slot) : -1;
         const bool my_valid = index_valid(ctx, my_idx);
-        // byte offset of the row inside kv (lanes 0..15 and 16..31 hold the same 16 keys); keys that do not take part
-        // are fetched with a source size of zero, which fills the destination with zeros
-        const long long my_off = my_valid ? kv_row(p, ctx.b, my_idx) * (kD * 2) : 0ll;
-        const uint32_t vmask = __ballot_sync(0xffffffffu, my_valid);
+        // row number inside kv (lanes 0..15 and 16..31 hold the same 16 keys), -1 for a key that does not take part: it is
+        // fetched with a source size of zero, which fills the destination with zeros
+        const int my_row = my_valid ? static_cast<int>(kv_row(p, ctx.b, my_idx)) : -1;
+        int rows[16];
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) rows[kk] = __shfl_sync(0xffffffffu, my_row, kk);
         if (g >= kStages && ok) ok = mbar_wait<true>(&kv_empty[s], ((g / kStages) + 1) & 1, p.status);
         if (!ok) continue;
         const uint32_t stage = sBase + s * kStageBytes;
         const uint8_t* lat_src = kv_bytes + rank * 512 + lane * 16;
-        const uint32_t lat_dst = stage + (lane >> 3) * kChunkBytes;
-#pragma unroll 4
+        const uint32_t lat_dst = stage + (lane >> 3) * kChunkBytes + pw * 2048;
+#pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
-          const long long off = __shfl_sync(0xffffffffu, my_off, kk);
-          cp_async16(lat_dst + sw128_offset(pw * 16 + kk, lane & 7), lat_src + off, ((vmask >> kk) & 1u) ? 16u : 0u);
+          const uint32_t row = static_cast<uint32_t>(rows[kk] < 0 ? 0 : rows[kk]);
+          cp_async16(lat_dst + sw128_offset(kk, lane & 7), lat_src + static_cast<size_t>(row) * (kD * 2), rows[kk] < 0 ? 0u : 16u);
         }
         // the 64 rope bytes of the 16 keys: 4 lanes per key, two instructions
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           const int kk = hh * 8 + (lane >> 2);
-          const long long off = __shfl_sync(0xffffffffu, my_off, kk);
-          cp_async16(stage + kRopeOff + sw64_offset(pw * 16 + kk, lane & 3), kv_bytes + off + 1024 + (4 * rank + (lane & 3)) * 16,
-                     ((vmask >> kk) & 1u) ? 16u : 0u);
+          const int row = __shfl_sync(0xffffffffu, my_row, kk);
+          cp_async16(stage + kRopeOff + sw64_offset(pw * 16 + kk, lane & 3),
+                     kv_bytes + static_cast<size_t>(row < 0 ? 0 : row) * (kD * 2) + 1024 + (4 * rank + (lane & 3)) * 16, row < 0 ? 0u : 16u);
         }
         cp_async_arrive_noinc(&kv_full[s]);
       }
@@ -693,7 +695,8 @@ __global__ void __launch_bounds__(256) sparse_mla_fwd_generic_kernel(const FwdPa
 // host launchers (return a cudaError_t as int; 0 = launched)
 // -------------------------------------------------------------------------------------------------
 bool sparse_mla_fwd_tc_supported(const FwdParams& p) {
-  return p.D == tc::kD && p.DV == tc::kDV && p.topk <= tc::kMaxTiles * tc::kBK;
+  // (row numbers inside kv are kept in 32 bits by the gather warps)
+  return p.D == tc::kD && p.DV == tc::kDV && p.topk <= tc::kMaxTiles * tc::kBK && static_cast<long long>(p.B) * p.S_kv <= 0x7fffffffLL;
 }
 
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream) {
