@@ -122,10 +122,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// The same, issued only after `dep` has been computed: pass a value derived from the loads whose completion the
-// credit stands for, so that neither the compiler nor the scoreboard can let the arrive overtake them.
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr, uint32_t dep) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];  // after %1" ::"r"(cluster_addr), "r"(dep) : "memory");
+// Volatile 4-byte store to this CTA's shared memory.  Used to pin an instruction behind loads: a warp issues in order,
+// and this store cannot issue before the register it stores has been filled.
+__device__ __forceinline__ void st_shared_u32_volatile(uint32_t addr, uint32_t v) {
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 // Asynchronous 16-byte store into another CTA's shared memory; on landing it subtracts 16 from the
 // transaction count of the mbarrier at `cluster_mbar` (same CTA as the data).  No fence is needed.

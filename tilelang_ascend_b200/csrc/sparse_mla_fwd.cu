@@ -458,25 +458,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         // one wait per tile: x_full completes after the peer's partial scores landed AND this CTA's exchange warp of the
         // same rows armed it, which it does after s_full and after its own read of the scores (see there)
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&x_full[q4 * 2 + ch], g & 1, p.status));
+        // Pull the peer's partial scores (16-byte units, layout [unit][row]) into registers and return the credit before
+        // anything else: the peer's next send into the single receive buffer waits for it.  The credit must not overtake
+        // the loads.  A warp issues its instructions in order and a store cannot issue before its source register is
+        // filled, so a (dummy) store of a word derived from all eight loads, placed before the arrive, holds the arrive
+        // back until the values are in registers.  (Naming the value as an unused operand of the arrive would not: the
+        // instruction would not read the register.)
+        float4 xr[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xr[j] = *reinterpret_cast<const float4*>(smem + kOffX + (8 * ch + j) * (kM * 16) + r * 16);
+        {
+          uint32_t dep = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dep ^= __float_as_uint(xr[j].x);
+          st_shared_u32_volatile(sBase + kOffInfo + 32 + warp * 4, dep);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + (q4 * 2 + ch) * 8);
+        }
         tc_fence_after();
         tmem_ld32(tS + sb * kBK + ch * 32 + lane_base, sc);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_free[sb]);  // the QK^T of tile g+2 may overwrite the buffer
-        // ---- add the peer CTA's partial scores (sent by its exchange warps; 16-byte units, layout [unit][row]) ----
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float4 o = *reinterpret_cast<const float4*>(smem + kOffX + (8 * ch + j) * (kM * 16) + r * 16);
-          sc[4 * j] = __float_as_uint(__uint_as_float(sc[4 * j]) + o.x);
-          sc[4 * j + 1] = __float_as_uint(__uint_as_float(sc[4 * j + 1]) + o.y);
-          sc[4 * j + 2] = __float_as_uint(__uint_as_float(sc[4 * j + 2]) + o.z);
-          sc[4 * j + 3] = __float_as_uint(__uint_as_float(sc[4 * j + 3]) + o.w);
+          sc[4 * j] = __float_as_uint(__uint_as_float(sc[4 * j]) + xr[j].x);
+          sc[4 * j + 1] = __float_as_uint(__uint_as_float(sc[4 * j + 1]) + xr[j].y);
+          sc[4 * j + 2] = __float_as_uint(__uint_as_float(sc[4 * j + 2]) + xr[j].z);
+          sc[4 * j + 3] = __float_as_uint(__uint_as_float(sc[4 * j + 3]) + xr[j].w);
         }
-        // the peer's scores are in registers (the sums above consumed them): one credit per warp lets the peer send the
-        // next tile's rows into the single receive buffer
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster_relaxed(peer_x_empty + (q4 * 2 + ch) * 8, sc[31]);
         const bool full = mask == 0xffffffffu;
         float mx;
         if (full) {
