@@ -30,8 +30,8 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(B=1, S=4096, S_kv=4096, H=128, D=576, DV=512, topk=2048)
 FLOP_PER_PAIR_HEAD = 2 * 576 + 2 * 512  # QK^T over 576 dims + PV over 512 dims
 METRIC, UNIT = "dsa_prefill_tokens_per_s", "tokens/s"
-# DRAM bytes per query of the forward kernel: (96 936 448 read + 35 241 728 written) / 592 queries, one ncu capture
-DRAM_BYTES_PER_QUERY = (96936448 + 35241728) / 592
+# DRAM bytes per query of the forward kernel: (96 930 304 read + 36 243 456 written) / 592 queries, one ncu capture
+DRAM_BYTES_PER_QUERY = (96930304 + 36243456) / 592
 
 
 def valid_pairs(S: int, S_kv: int, topk: int) -> int:
