@@ -79,10 +79,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 //     * runs the (identical) online softmax, and
 //     * accumulates O[:, 256 r : 256 r + 256] = P . V[:, its latent dims]   (output columns split).
 // Per CTA: Q latent dims live in TMEM as the A operand, the Q rope dims in shared memory, KV tiles of 64
-// keys in a 4-stage cp.async ring, two score buffers in TMEM (P, as bf16, replaces the first half of its
-// tile's score buffer), so the QK^T of tile i+1 overlaps the softmax of tile i.  Warp roles: 16 softmax warps
-// (32 rows x 16 score columns each), one warp issuing the QK^T MMAs and one the PV MMAs, 4 gather warps, 4
-// warps that load Q and ship the partial scores to the peer CTA.
+// keys in a 4-stage cp.async ring, two score buffers in TMEM that are released as soon as the softmax warps
+// have read them, P (bf16) in two shared-memory buffers as the A operand of PV, one receive buffer for the
+// peer's partial scores.  Warp roles: 8 softmax warps (32 rows x 32 score columns each), 4 warps that load Q
+// and ship the partial scores to the peer CTA, 4 gather warps, one warp issuing the QK^T MMAs and one the PV
+// MMAs.
 //
 // The grid is one cluster per SM pair; cluster c walks the items  n-1-c, n-1-c-C, ...  (late = long queries
 // first).  Roles run ahead of each other across items: the gather warps build the next item's tile list and
