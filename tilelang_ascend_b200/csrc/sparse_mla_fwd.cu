@@ -298,14 +298,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       const int bt = item / head_blocks;
       const RowCtx ctx = make_row_ctx(p, bt);
       if (k >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait<true>(&info_empty[qp], ((k >> 1) + 1) & 1, p.status));
-      // validity masks of all tiles of the item, then the list of tiles with at least one key taking part
-      for (int tile = pw; tile < ntiles; tile += 4) {
-        const int s0 = tile * kBK + lane, s1 = s0 + 32;
-        const int i0 = s0 < p.topk ? __ldg(ctx.idx_row + s0) : -1;
-        const int i1 = s1 < p.topk ? __ldg(ctx.idx_row + s1) : -1;
-        const uint32_t lo = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i0));
-        const uint32_t hi = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i1));
-        if (lane == 0) masks[qp * kMaxTiles + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
+      // validity masks of all tiles of the item, then the list of tiles with at least one key taking part.  The indices
+      // of eight tiles are loaded before the first of them is used, so that their latencies overlap (with a single
+      // item per cluster -- decode -- this prologue is not hidden behind a previous item)
+      for (int t0 = pw; t0 < ntiles; t0 += 32) {
+        int i0[8], i1[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int tile = t0 + 4 * u;
+          const int s0 = tile * kBK + lane, s1 = s0 + 32;
+          i0[u] = (tile < ntiles && s0 < p.topk) ? __ldg(ctx.idx_row + s0) : -1;
+          i1[u] = (tile < ntiles && s1 < p.topk) ? __ldg(ctx.idx_row + s1) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int tile = t0 + 4 * u;
+          const uint32_t lo = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i0[u]));
+          const uint32_t hi = __ballot_sync(0xffffffffu, ctx.active && index_valid(ctx, i1[u]));
+          if (lane == 0 && tile < ntiles) masks[qp * kMaxTiles + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
+        }
       }
       named_bar_sync(kGatherBarrier, 128);
       if (pw == 0) {
