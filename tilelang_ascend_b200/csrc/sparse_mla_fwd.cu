@@ -205,6 +205,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t peer_x = map_to_cta(sX, peer);
     const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
+    // pulls this thread's Q row of an item towards L2 (the CTA's 4 latent lines and its rope line)
+    auto prefetch_q = [&](int it_item) {
+      if (it_item < 0) return;
+      const int nbt = it_item / head_blocks, nh = (it_item - nbt * head_blocks) * kM + r;
+      if (nh >= p.H) return;
+      const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * (kD * 2);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) prefetch_l2(nq + rank * 512 + j * 128);
+      prefetch_l2(nq + 1024 + rank * 64);
+    };
+    if (run_all) prefetch_q(item_of(0));  // the first item's rows: behind the wait for its tile list
     int g = 0;
     for (int k = 0; run_all && ok; ++k) {
       const int item = item_of(k);
@@ -239,18 +250,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         __syncwarp();
         if (lane == 0) mbar_arrive(q_ready);
       }
-      {  // pull the next item's Q rows towards L2 while this item is being worked on
-        const int nitem = item_of(k + 1);
-        if (nitem >= 0) {
-          const int nbt = nitem / head_blocks, nh = (nitem - nbt * head_blocks) * kM + r;
-          if (nh < p.H) {
-            const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * (kD * 2);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) prefetch_l2(nq + rank * 512 + j * 128);
-            prefetch_l2(nq + 1024 + rank * 64);
-          }
-        }
-      }
+      prefetch_q(item_of(k + 1));  // the next item's rows, while this item is being worked on
       for (int it = 0; it < nvt; ++it, ++g) {
         const int sb = g & 1;
         uint32_t v[32];
