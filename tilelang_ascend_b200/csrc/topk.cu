@@ -18,7 +18,7 @@
 namespace dsa {
 
 namespace topk {
-constexpr int kThreads = 1024;
+constexpr int kThreads = 512;                     // 4 rows (CTAs) per SM hide each other's barrier phases
 constexpr int kWarps = kThreads / 32;
 }  // namespace topk
 
@@ -33,15 +33,17 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 }
 
 // scores [rows, row_stride]; limits [rows] or null; out_idx [rows, top_k]; out_val [rows, top_k] or null.
-// Dynamic shared memory: kpow2 * 8 (sort buffer) + n * 4 (keys) + 32 * 256 * 4 (per-warp first-digit histograms).
-__global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
+// Dynamic shared memory: max(kpow2 * 8 (sort buffer), kWarps * 256 * 4 (per-warp first-digit histograms, used before the
+// sort buffer)) + n * 4 (keys).
+__global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
                                                                      const int32_t* __restrict__ limits, int top_k, int kpow2,
                                                                      int32_t* __restrict__ out_idx, float* __restrict__ out_val) {
   using namespace topk;
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  unsigned long long* sortbuf = reinterpret_cast<unsigned long long*>(smem_raw);            // [kpow2]
-  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + static_cast<size_t>(kpow2) * 8);  // [n]
-  uint32_t* whist = keys + n;                                                                // [kWarps][256]
+  const size_t front = max(static_cast<size_t>(kpow2) * 8, static_cast<size_t>(kWarps) * 256 * 4);
+  unsigned long long* sortbuf = reinterpret_cast<unsigned long long*>(smem_raw);  // [kpow2]
+  uint32_t* whist = reinterpret_cast<uint32_t*>(smem_raw);                         // [kWarps][256], dead before sortbuf is written
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + front);                  // [n]
   __shared__ uint32_t hist[256];
   __shared__ uint32_t warp_sums[kWarps], warp_ties[kWarps];
   __shared__ uint32_t s_prefix, s_remaining, s_nvalid;
@@ -49,6 +51,7 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x;
   const float* x = scores + static_cast<int64_t>(row) * row_stride;
+  const bool whole_groups = (n & 3) == 0;  // 16-byte groups never reach past the end of the row
   int lim = limits ? limits[row] : n;
   lim = lim < 0 ? 0 : (lim > n ? n : lim);
   n = lim;  // entries at or beyond the limit are not candidates: none of the passes below looks at them
@@ -59,16 +62,36 @@ __global__ void __launch_bounds__(topk::kThreads) topk_select_kernel(const float
 
   // ---- load, convert, count candidates, first-digit histogram ---------------------------------------
   uint32_t my_valid = 0;
-  for (int base = 0; base < n; base += kThreads) {
-    const int i = base + tid;
+  auto take = [&](int i, float f) {
     uint32_t k = 0;
-    if (i < lim) {
-      const float f = x[i];
-      if (f > -1e30f) { k = float_to_key(f); ++my_valid; }
-    }
+    if (i < lim && f > -1e30f) { k = float_to_key(f); ++my_valid; }
     if (i < n) keys[i] = k;  // 0 marks "not a candidate" (a real key is never 0 for a score > -1e30)
     // sign + exponent bits crowd into a few bins: a private histogram per warp keeps the atomics apart
     if (k) atomicAdd(&whist[warp * 256 + (k >> 24)], 1u);
+  };
+  if (whole_groups && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    // 16-byte loads, four of them in flight per thread before the first is used: a row of 8192 scores is two round
+    // trips to memory instead of sixteen
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int n4 = (n + 3) >> 2;
+    for (int base = 0; base < n4; base += 4 * kThreads) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i4 = base + u * kThreads + tid;
+        v[u] = i4 < n4 ? __ldg(x4 + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = (base + u * kThreads + tid) * 4;
+        take(i, v[u].x); take(i + 1, v[u].y); take(i + 2, v[u].z); take(i + 3, v[u].w);
+      }
+    }
+  } else {
+    for (int base = 0; base < n; base += kThreads) {
+      const int i = base + tid;
+      take(i, i < lim ? x[i] : 0.f);
+    }
   }
   for (int o = 16; o > 0; o >>= 1) my_valid += __shfl_xor_sync(0xffffffffu, my_valid, o);
   if (lane == 0 && my_valid) atomicAdd(&s_nvalid, my_valid);
@@ -250,7 +273,8 @@ size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
   int kp = 2;
   while (kp < top_k) kp <<= 1;
   if (kpow2_out) *kpow2_out = kp;
-  return static_cast<size_t>(n) * 4 + static_cast<size_t>(kp) * 8 + static_cast<size_t>(topk::kWarps) * 256 * 4;
+  const size_t front = static_cast<size_t>(kp) * 8 > static_cast<size_t>(topk::kWarps) * 256 * 4 ? static_cast<size_t>(kp) * 8 : static_cast<size_t>(topk::kWarps) * 256 * 4;
+  return static_cast<size_t>(n) * 4 + front;
 }
 
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
