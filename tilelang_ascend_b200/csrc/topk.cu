@@ -9,8 +9,9 @@
 // One CTA per row.  The row is converted to order-preserving 32-bit keys in shared memory, four
 // 8-bit most-significant-digit-first histogram passes find the k-th largest key, an index-ordered
 // compaction (per-warp counts, prefix over warps, ordered write) takes everything above it plus the
-// lowest-index ties, and a bitonic sort of the <= k survivors on (key, ~index) fixes the output order;
-// its strides below 64 run inside warps with shuffles.
+// lowest-index ties, and a stable least-significant-digit radix sort (four 8-bit passes, descending) of the
+// <= k survivors fixes the output order: the compaction leaves equal keys in ascending index order and
+// a stable sort keeps them so.
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -34,8 +35,10 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 
 // scores [rows, row_stride]; limits [rows] or null; out_idx [rows, top_k]; out_val [rows, top_k] or null.
 // Dynamic shared memory: max(kpow2 * 8 (sort buffer), kWarps * 256 * 4 (per-warp first-digit histograms, used before the
-// sort buffer)) + n * 4 (keys).
-__global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
+// sort buffer)) + max(n * 4 (keys), kpow2 * 8 + kWarps * 256 * 2 (second sort buffer + digit counters, used after the keys)).
+// kMaxRounds: 32-element rounds per warp in the sort, top_k <= kWarps * 32 * kMaxRounds.
+template <int kMaxRounds>
+__global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
                                                                      const int32_t* __restrict__ limits, int top_k, int kpow2,
                                                                      int32_t* __restrict__ out_idx, float* __restrict__ out_val) {
   using namespace topk;
@@ -44,7 +47,7 @@ __global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const fl
   unsigned long long* sortbuf = reinterpret_cast<unsigned long long*>(smem_raw);  // [kpow2]
   uint32_t* whist = reinterpret_cast<uint32_t*>(smem_raw);                         // [kWarps][256], dead before sortbuf is written
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw + front);                  // [n]
-  __shared__ uint32_t hist[256];
+  __shared__ uint32_t hist[256], dbase[256];
   __shared__ uint32_t warp_sums[kWarps], warp_ties[kWarps];
   __shared__ uint32_t s_prefix, s_remaining, s_nvalid;
 
@@ -157,7 +160,6 @@ __global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const fl
   }
 
   // ---- ordered compaction: keys > T in any order, keys == T by ascending index until need_ties ----------
-  for (int i = tid; i < kpow2; i += kThreads) sortbuf[i] = 0ull;
   const bool take_all = nvalid <= static_cast<uint32_t>(top_k);
   {
     // warp w owns the contiguous index range [w * per, w * per + per): count, prefix over warps, then write in order
@@ -196,70 +198,114 @@ __global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const fl
   }
   __syncthreads();
 
-  // ---- bitonic sort, descending on (key, ~index): larger score first, then lower index ---------------------
-  // Strides below 64 stay inside one warp (two elements per lane, exchanged with shuffles); only the wider
-  // strides go through shared memory with a block barrier.
-  if (kpow2 >= 64) {
-    const int nblk = kpow2 >> 6;
-    auto warp_phase = [&](int size_lo, int size_hi) {  // all (size, stride) steps with stride <= 32 for sizes in [lo, hi]
-      for (int blk = warp; blk < nblk; blk += kWarps) {
-        const int i0 = blk * 64 + lane, i1 = i0 + 32;
-        unsigned long long a = sortbuf[i0], b = sortbuf[i1];
-        for (int size = size_lo; size <= size_hi; size <<= 1) {
-          const bool d0 = (i0 & size) == 0, d1 = (i1 & size) == 0;
-          int stride = min(size >> 1, 32);
-          if (stride == 32) {
-            if ((a < b) == d0) { const unsigned long long t = a; a = b; b = t; }
-            stride = 16;
-          }
-          for (; stride > 0; stride >>= 1) {
-            const bool lower = (lane & stride) == 0;
-            const unsigned long long oa = __shfl_xor_sync(0xffffffffu, a, stride), ob = __shfl_xor_sync(0xffffffffu, b, stride);
-            a = (lower == d0) ? (a > oa ? a : oa) : (a < oa ? a : oa);
-            b = (lower == d1) ? (b > ob ? b : ob) : (b < ob ? b : ob);
-          }
+  // ---- stable radix sort of the kk survivors, descending by key --------------------------------------------------
+  // Four passes over 8-bit digits, least significant first, ping-pong between the sort buffer and the (now free) key
+  // array.  Warp w owns the contiguous slice [w * per, w * per + per) of the current order.  Rank of an element inside
+  // its digit = (elements of that digit in earlier warps) + (in earlier 32-element rounds of this warp) + (in lower
+  // lanes of this round, from match_any).  Per-warp digit counters are 16-bit and only ever touched by their own warp.
+  unsigned long long* src = sortbuf;
+  unsigned long long* dst = reinterpret_cast<unsigned long long*>(keys);
+  uint16_t* wcnt = reinterpret_cast<uint16_t*>(keys) + static_cast<size_t>(kpow2) * 4;  // [kWarps][256], behind the second buffer
+  if (kk <= 64u) {
+    // up to 64 survivors: one warp sorts them in registers (two per lane, bitonic network, descending on the whole
+    // 64-bit element = key, then lower index), no block barriers
+    if (warp == 0) {
+      const int i0 = lane, i1 = lane + 32;
+      unsigned long long a = i0 < static_cast<int>(kk) ? sortbuf[i0] : 0ull, b = i1 < static_cast<int>(kk) ? sortbuf[i1] : 0ull;
+      for (int size = 2; size <= 64; size <<= 1) {
+        const bool d0 = (i0 & size) == 0, d1 = (i1 & size) == 0;
+        int stride = min(size >> 1, 32);
+        if (stride == 32) {
+          if ((a < b) == d0) { const unsigned long long t = a; a = b; b = t; }
+          stride = 16;
         }
-        sortbuf[i0] = a;
-        sortbuf[i1] = b;
-      }
-    };
-    warp_phase(2, 64);
-    __syncthreads();
-    for (int size = 128; size <= kpow2; size <<= 1) {
-      for (int stride = size >> 1; stride >= 64; stride >>= 1) {
-        for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
-          const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
-          const int hi = lo | stride;
-          const bool desc = (lo & size) == 0;
-          const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
-          if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+        for (; stride > 0; stride >>= 1) {
+          const bool lower = (lane & stride) == 0;
+          const unsigned long long oa = __shfl_xor_sync(0xffffffffu, a, stride), ob = __shfl_xor_sync(0xffffffffu, b, stride);
+          a = (lower == d0) ? (a > oa ? a : oa) : (a < oa ? a : oa);
+          b = (lower == d1) ? (b > ob ? b : ob) : (b < ob ? b : ob);
         }
-        __syncthreads();
       }
-      warp_phase(size, size);
-      __syncthreads();
+      sortbuf[i0] = a;
+      sortbuf[i1] = b;
     }
-  } else {
-    for (int size = 2; size <= kpow2; size <<= 1) {
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        for (int i = tid; i < (kpow2 >> 1); i += kThreads) {
-          const int lo = ((i & ~(stride - 1)) << 1) | (i & (stride - 1));
-          const int hi = lo | stride;
-          const bool desc = (lo & size) == 0;
-          const unsigned long long a = sortbuf[lo], b = sortbuf[hi];
-          if ((a < b) == desc) { sortbuf[lo] = b; sortbuf[hi] = a; }
+    __syncthreads();
+  } else
+  {
+    const int cnt = static_cast<int>(kk);
+    const int per = ((cnt + kWarps - 1) / kWarps + 31) & ~31;
+    const int rounds = per >> 5;  // <= kMaxRounds (checked by the launcher)
+    const int beg = warp * per;
+    const int nw = (cnt + per - 1) / per;  // warps that own elements: the counters of the others are never looked at
+    for (int pass = 0; pass < 4 && cnt > 1; ++pass) {
+      const int shift = 32 + 8 * pass;  // the key is the upper word of the element
+      for (int i = tid; i < nw * 256; i += kThreads) wcnt[i] = 0;
+      __syncthreads();
+      unsigned long long e[kMaxRounds];
+      uint32_t dig[kMaxRounds], rk[kMaxRounds];
+#pragma unroll
+      for (int j = 0; j < kMaxRounds; ++j) {
+        if (j < rounds) {
+          const int i = beg + j * 32 + lane;
+          const bool live = i < cnt;
+          e[j] = live ? src[i] : 0ull;
+          dig[j] = live ? static_cast<uint32_t>(e[j] >> shift) & 0xffu : 0x100u + lane;  // dead lanes match nobody
+          const uint32_t peers = __match_any_sync(0xffffffffu, dig[j]);
+          uint32_t old = 0;
+          if (live) old = wcnt[warp * 256 + dig[j]];
+          __syncwarp();
+          if (live && (__ffs(peers) - 1) == lane) wcnt[warp * 256 + dig[j]] = static_cast<uint16_t>(old + __popc(peers));
+          __syncwarp();
+          rk[j] = old + __popc(peers & ((1u << lane) - 1u));
         }
-        __syncthreads();
       }
+      __syncthreads();
+      // per digit: exclusive prefix over the warps, total
+      if (tid < 256) {
+        uint32_t run = 0;
+#pragma unroll 4
+        for (int w = 0; w < nw; ++w) {
+          const uint32_t c = wcnt[w * 256 + tid];
+          wcnt[w * 256 + tid] = static_cast<uint16_t>(run);
+          run += c;
+        }
+        hist[tid] = run;
+      }
+      __syncthreads();
+      // descending order: digit d starts after all larger digits (warp 0, lane l holds digits 255 - 8l .. 248 - 8l)
+      if (warp == 0) {
+        uint32_t c[8], tot = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { c[j] = hist[255 - (lane * 8 + j)]; tot += c[j]; }
+        uint32_t incl = tot;
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        uint32_t above = incl - tot;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { dbase[255 - (lane * 8 + j)] = above; above += c[j]; }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < kMaxRounds; ++j) {
+        if (j < rounds) {
+          const int i = beg + j * 32 + lane;
+          if (i < cnt) dst[dbase[dig[j]] + wcnt[warp * 256 + dig[j]] + rk[j]] = e[j];
+        }
+      }
+      __syncthreads();
+      unsigned long long* t = src; src = dst; dst = t;
     }
   }
+  const unsigned long long* sorted = src;
 
   // ---- output ---------------------------------------------------------------------------------------------
   int32_t* oi = out_idx + static_cast<int64_t>(row) * top_k;
   float* ov = out_val ? out_val + static_cast<int64_t>(row) * top_k : nullptr;
   for (int i = tid; i < top_k; i += kThreads) {
     if (static_cast<uint32_t>(i) < kk) {
-      const unsigned long long e = sortbuf[i];
+      const unsigned long long e = sorted[i];
       oi[i] = static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(e & 0xffffffffull));
       if (ov) ov[i] = key_to_float(static_cast<uint32_t>(e >> 32));
     } else {
@@ -270,21 +316,25 @@ __global__ void __launch_bounds__(topk::kThreads, 4) topk_select_kernel(const fl
 }
 
 size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
-  int kp = 2;
-  while (kp < top_k) kp <<= 1;
+  int kp = 32;  // buffer length: top_k rounded up to a multiple of 32 (name kept from the power-of-two days of a bitonic sort)
+  while (kp < top_k) kp += 32;
   if (kpow2_out) *kpow2_out = kp;
   const size_t front = static_cast<size_t>(kp) * 8 > static_cast<size_t>(topk::kWarps) * 256 * 4 ? static_cast<size_t>(kp) * 8 : static_cast<size_t>(topk::kWarps) * 256 * 4;
-  return static_cast<size_t>(n) * 4 + front;
+  const size_t back_sort = static_cast<size_t>(kp) * 8 + static_cast<size_t>(topk::kWarps) * 256 * 2;
+  const size_t back = static_cast<size_t>(n) * 4 > back_sort ? static_cast<size_t>(n) * 4 : back_sort;
+  return front + back;
 }
 
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
                        int32_t* out_idx, float* out_val, cudaStream_t stream) {
   int kp = 0;
   const size_t smem = topk_smem_bytes(n, top_k, &kp);
-  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (top_k > topk::kWarps * 32 * 16) return static_cast<int>(cudaErrorInvalidValue);
+  const bool small = top_k <= topk::kWarps * 32 * 4;
+  auto kern = small ? topk_select_kernel<4> : topk_select_kernel<16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  topk_select_kernel<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx,
-                                                                                   out_val);
+  kern<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx, out_val);
   return static_cast<int>(cudaGetLastError());
 }
 
