@@ -138,18 +138,6 @@ __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t clus
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-// TMA gather: four rows (r0..r3, any order, out-of-range rows read as zeros) of a 2-D tensor, columns x .. x + box
-// width, land as four consecutive rows at `smem_dst` in the tensor map's swizzle; 4 x box-width bytes are
-// subtracted from the transaction count of `mbar` (this CTA).  x times the element size must be a multiple of 16.
-__device__ __forceinline__ void tma_gather4(uint32_t smem_dst, const void* tensor_map, uint32_t mbar, int x, int r0, int r1, int r2, int r3) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(
-                   smem_dst),
-               "l"(tensor_map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(mbar)
-               : "memory");
-}
-__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
-}
 // Local arrive (count 1) that also adds `tx_bytes` to the barrier's expected transaction count.
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t tx_bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(tx_bytes) : "memory");
