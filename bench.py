@@ -151,8 +151,23 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     t_dec = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd, kvd, idxd, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=20)
     dec_bytes = B * (topk * 1152 + H * 576 * 2 + H * 512 * 2 + topk * 4)
     dec_gbs = dec_bytes / (t_dec * 1e-3) / 1e9
+    del qd, kvd, idxd
+    # backward at the prefill shape (last S_b queries of the workload; dKV accumulated in fp32)
+    S_b = 256 if small else WORKLOAD["S"]
+    saved = WORKLOAD["S"]
+    q, kv, idx = make_inputs_cuda(11, dev)
+    q, idx = q[:, saved - S_b:].contiguous(), idx[:, saved - S_b:].contiguous()
+    scale, q0 = WORKLOAD["D"] ** -0.5, WORKLOAD["S_kv"] - S_b
+    out, lse = dsa.sparse_mla_fwd_raw(q, kv, idx, sm_scale=scale, q_start=q0, causal=True, dv=WORKLOAD["DV"], return_lse=True)
+    d_out = torch.randn(out.shape, generator=g, device=dev).to(torch.bfloat16)
+    t_bwd = _time_ms(lambda: dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=q0, causal=True), reps=2, warm=1)
+    bwd_pairs = int((idx >= 0).sum().item())
+    bwd_tflops = bwd_pairs * WORKLOAD["H"] * 5504 / (t_bwd * 1e-3) / 1e12
+    del q, kv, idx, out, lse, d_out
     assert dsa.kernel_status() == 0
     return {
+        "backward": {"ms": t_bwd, "tokens_per_s": S_b / (t_bwd * 1e-3), "tflops": bwd_tflops, "frac_of_bf16_peak": bwd_tflops / peaks["bf16_tflops"],
+                     "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (CUDA-core kernel)"},
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
                            "workload": f"S_q={S1} S_kv=8192 64 heads x 128, causal"},
         "indexer_plus_topk": {"ms": t_all, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
