@@ -43,7 +43,9 @@ constexpr uint32_t kOffK = kQBytes;
 constexpr uint32_t kOffW = kOffK + kStages * kKStageBytes;  // 163840
 constexpr uint32_t kOffBar = kOffW + kN * 4;
 constexpr uint32_t kSmemBytes = kOffBar + 256 + 1024;
-constexpr int kThreads = 288;
+constexpr int kEpilogueWarps = 8;                  // warp w: keys 32 (w & 3) .. +31 of a tile, half (w >> 2) of the CTA's queries
+constexpr int kMmaWarp = 8;
+constexpr int kThreads = 416;                      // 8 reduce warps, the MMA warp, 4 producer warps
 constexpr uint32_t kTmemCols = 512;
 }  // namespace itc
 
@@ -61,7 +63,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
   uint64_t* k_full = bars;          // [3] count 128
   uint64_t* k_empty = bars + 3;     // [3] count 1 (commit)
   uint64_t* acc_full = bars + 6;    // [2] count 1 (commit)
-  uint64_t* acc_empty = bars + 8;   // [2] count 128
+  uint64_t* acc_empty = bars + 8;   // [2] count 256
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   int* start_status = reinterpret_cast<int*>(bars + 11);
 
@@ -86,10 +88,10 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&k_full[i], 128); mbar_init(&k_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpilogueWarps * 32); }
     mbar_init_fence();
   }
-  if (warp == 4) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  if (warp == kMmaWarp) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
   {  // Q rows (query, head) -> B operand rows; weights
     const T* qbase = reinterpret_cast<const T*>(p.q) + (static_cast<int64_t>(b) * p.S1 + q0) * N1 * kD;
     for (int u = tid; u < kN * 16; u += kThreads) {
@@ -114,9 +116,9 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp >= 5) {
+  if (warp > kMmaWarp) {
     // ================================ key-tile producers ============================================
-    const int pt = tid - 160;
+    const int pt = tid - (kMmaWarp + 1) * 32;
     const T* kbase = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(b) * p.S2 * kD;
     for (int it = 0; it < ntiles_mma; ++it) {
       const int s = it % kStages;
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
       fence_proxy_async_smem();
       mbar_arrive(&k_full[(ntiles_mma - 1) % kStages]);
     }
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ====================================================
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kBF16, kKeys, kN, 0, 0);
@@ -168,39 +170,51 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
     }
   } else {
     // ================================ reduce over heads + store ====================================
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    int lim[QB];
+    // thread = (key, half of the CTA's queries): the accumulator row of its key, the columns of its queries
+    const int q4 = warp & 3, half = warp >> 2;
+    const int krow = q4 * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    constexpr int QH = QB / 2;  // queries per thread
+    int lim[QH];
 #pragma unroll
-    for (int i = 0; i < QB; ++i) {
+    for (int i = 0; i < QH; ++i) {
       int dummy;
-      lim[i] = (q0 + i < p.S1) ? indexer_limit(p, b, q0 + i, &dummy) : 0;
+      const int qi = half * QH + i;
+      lim[i] = (q0 + qi < p.S1) ? indexer_limit(p, b, q0 + qi, &dummy) : 0;
     }
-    float* out = p.scores + (static_cast<int64_t>(b) * p.S1 + q0) * p.S2;
+    float* out = p.scores + (static_cast<int64_t>(b) * p.S1 + q0 + half * QH) * p.S2;
     for (int it = 0; it < ntiles_all; ++it) {
-      const int key = it * kKeys + tid;
+      const int key = it * kKeys + krow;
       if (it < ntiles_mma) {
         const int a = it & 1;
         if (!mbar_wait(&acc_full[a], (it >> 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tacc = tmem_base + a * kN + lane_base;
+        const uint32_t tacc = tmem_base + a * kN + half * (kN / 2) + lane_base;
+        const float4* w4 = reinterpret_cast<const float4*>(sW + half * (kN / 2));  // weights of this half, 4 per (broadcast) load
         if constexpr (N1 >= 32) {
 #pragma unroll
-          for (int i = 0; i < QB; ++i) {
-            float sum = 0.f;
+          for (int i = 0; i < QH; ++i) {
+            float s0 = 0.f, s1 = 0.f;
 #pragma unroll
             for (int cc = 0; cc < N1 / 32; ++cc) {
               uint32_t v[32];
               tmem_ld32(tacc + i * N1 + cc * 32, v);
               tmem_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) sum = fmaf(sW[i * N1 + cc * 32 + j], fmaxf(__uint_as_float(v[j]), 0.f), sum);
+              for (int j = 0; j < 8; ++j) {
+                const float4 w = w4[(i * N1 + cc * 32) / 4 + j];
+                s0 = fmaf(w.x, fmaxf(__uint_as_float(v[4 * j]), 0.f), s0);
+                s1 = fmaf(w.y, fmaxf(__uint_as_float(v[4 * j + 1]), 0.f), s1);
+                s0 = fmaf(w.z, fmaxf(__uint_as_float(v[4 * j + 2]), 0.f), s0);
+                s1 = fmaf(w.w, fmaxf(__uint_as_float(v[4 * j + 3]), 0.f), s1);
+              }
             }
-            if (q0 + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? sum : -INFINITY;
+            if (q0 + half * QH + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? s0 + s1 : -INFINITY;
           }
         } else {
           constexpr int QPC = 32 / N1;  // queries per 32-column chunk
 #pragma unroll
-          for (int cc = 0; cc < kN / 32; ++cc) {
+          for (int cc = 0; cc < kN / 64; ++cc) {
             uint32_t v[32];
             tmem_ld32(tacc + cc * 32, v);
             tmem_wait_ld();
@@ -208,10 +222,15 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
             for (int qq = 0; qq < QPC; ++qq) {
               float sum = 0.f;
 #pragma unroll
-              for (int j = 0; j < N1; ++j)
-                sum = fmaf(sW[cc * 32 + qq * N1 + j], fmaxf(__uint_as_float(v[qq * N1 + j]), 0.f), sum);
+              for (int j = 0; j < N1 / 4; ++j) {
+                const float4 w = w4[(cc * 32 + qq * N1) / 4 + j];
+                sum = fmaf(w.x, fmaxf(__uint_as_float(v[qq * N1 + 4 * j]), 0.f), sum);
+                sum = fmaf(w.y, fmaxf(__uint_as_float(v[qq * N1 + 4 * j + 1]), 0.f), sum);
+                sum = fmaf(w.z, fmaxf(__uint_as_float(v[qq * N1 + 4 * j + 2]), 0.f), sum);
+                sum = fmaf(w.w, fmaxf(__uint_as_float(v[qq * N1 + 4 * j + 3]), 0.f), sum);
+              }
               const int i = cc * QPC + qq;
-              if (q0 + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? sum : -INFINITY;
+              if (q0 + half * QH + i < p.S1 && key < p.S2) out[static_cast<int64_t>(i) * p.S2 + key] = key < lim[i] ? sum : -INFINITY;
             }
           }
         }
@@ -219,15 +238,15 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
         mbar_arrive(&acc_empty[a]);
       } else if (key < p.S2) {  // tile entirely beyond every limit of this CTA
 #pragma unroll
-        for (int i = 0; i < QB; ++i)
-          if (q0 + i < p.S1) out[static_cast<int64_t>(i) * p.S2 + key] = -INFINITY;
+        for (int i = 0; i < QH; ++i)
+          if (q0 + half * QH + i < p.S1) out[static_cast<int64_t>(i) * p.S2 + key] = -INFINITY;
       }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // -------------------------------------------------------------------------------------------------
