@@ -10,9 +10,13 @@
 // one key per lane and all heads of a query in consecutive columns.  The ReLU, the per-head weight
 // and the sum over heads are then a per-thread reduction over columns, and a warp writes 32
 // consecutive keys of one query row (coalesced).  Two accumulators (2 x 256 TMEM columns) let the
-// reduction of tile i overlap the MMAs of tile i+1.
+// reduction of tile i overlap the MMAs of tile i+1.  Key tiles are dense (128 consecutive keys x 128 dims): one thread
+// fetches each with two TMA tile loads (64 dims x 128 keys, 128-byte swizzle) into a 3-stage ring; when no tensor
+// map could be made for k (unaligned pointer) four warps fetch the tiles with cp.async instead.
 //
 // Generic kernel (any D, any N1): CUDA-core fp32.
+#include <cuda.h>
+#include <string.h>
 #include <type_traits>
 
 #include "params.h"
@@ -50,7 +54,8 @@ constexpr uint32_t kTmemCols = 512;
 }  // namespace itc
 
 template <bool kBF16, int N1>
-__global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(const IndexerParams p) {
+__global__ void __launch_bounds__(itc::kThreads, 1)
+    indexer_scores_tc_kernel(const __grid_constant__ IndexerParams p, const __grid_constant__ CUtensorMap kmap, const int use_tma) {
   using namespace itc;
   constexpr int QB = kN / N1;  // queries per CTA
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
@@ -60,7 +65,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
   const uint32_t sK = sQ + kOffK;
   float* sW = reinterpret_cast<float*>(smem + kOffW);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
-  uint64_t* k_full = bars;          // [3] count 128
+  uint64_t* k_full = bars;          // [3] count 1 + 32768 transaction bytes (TMA) or count 128 (cp.async producers)
   uint64_t* k_empty = bars + 3;     // [3] count 1 (commit)
   uint64_t* acc_full = bars + 6;    // [2] count 1 (commit)
   uint64_t* acc_empty = bars + 8;   // [2] count 256
@@ -87,7 +92,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
   const int ntiles_all = p.fill_masked ? (p.S2 + kKeys - 1) / kKeys : ntiles_mma;
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) { mbar_init(&k_full[i], 128); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&k_full[i], use_tma ? 1 : 128); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpilogueWarps * 32); }
     mbar_init_fence();
   }
@@ -120,6 +125,21 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
     // ================================ key-tile producers ============================================
     const int pt = tid - (kMmaWarp + 1) * 32;
     const T* kbase = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(b) * p.S2 * kD;
+    if (use_tma) {
+      // one thread: k as a 2-D tensor [B * S2 keys, 128 dims]; keys past the row's limit (or past the batch entry: they
+      // belong to the next one) only produce scores that the reduce warps replace by -inf
+      if (pt == 0) {
+        prefetch_tensormap(&kmap);
+        for (int it = 0; it < ntiles_mma; ++it) {
+          const int s = it % kStages;
+          if (it >= kStages && !mbar_wait(&k_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
+          const uint32_t stage = sK + s * kKStageBytes, full = smem_u32(&k_full[s]);
+          mbar_arrive_expect_tx(&k_full[s], kKStageBytes);
+          tma_load_2d(stage, &kmap, full, 0, b * p.S2 + it * kKeys);
+          tma_load_2d(stage + kKeys * 128, &kmap, full, 64, b * p.S2 + it * kKeys);
+        }
+      }
+    } else
     for (int it = 0; it < ntiles_mma; ++it) {
       const int s = it % kStages;
       if (it >= kStages && !mbar_wait(&k_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
@@ -141,7 +161,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1) indexer_scores_tc_kernel(con
       }
     }
     cp_async_wait<0>();
-    if (ok && ntiles_mma > 0) {
+    if (!use_tma && ok && ntiles_mma > 0) {
       fence_proxy_async_smem();
       mbar_arrive(&k_full[(ntiles_mma - 1) % kStages]);
     }
@@ -285,6 +305,36 @@ bool indexer_tc_supported(const IndexerParams& p) {
   return p.D == itc::kD && (p.N1 == 64 || p.N1 == 32 || p.N1 == 16 || p.N1 == 8);
 }
 
+namespace {
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link against the driver library.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// k [B * S2, 128] as a tensor map with a box of 64 dims x 128 keys in the 128-byte swizzle; false when that is not
+// possible (then the kernel's cp.async producers fetch the tiles)
+bool make_k_map(const IndexerParams& p, bool bf16, CUtensorMap* map) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  const long long rows = static_cast<long long>(p.B) * p.S2;
+  if (!encode || (reinterpret_cast<uintptr_t>(p.k) & 15u) || rows <= 0 || rows > 0x7fffffffLL) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(itc::kD), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(itc::kD) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(itc::kKeys)}, estr[2] = {1, 1};
+  return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(p.k), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
 template <bool kBF16, int N1>
 static int launch_indexer_tc_n1(const IndexerParams& p, cudaStream_t stream) {
   auto kern = indexer_scores_tc_kernel<kBF16, N1>;
@@ -292,7 +342,10 @@ static int launch_indexer_tc_n1(const IndexerParams& p, cudaStream_t stream) {
   if (e != cudaSuccess) return static_cast<int>(e);
   constexpr int QB = itc::kN / N1;
   const int nqb = (p.S1 + QB - 1) / QB;
-  kern<<<p.B * nqb, itc::kThreads, itc::kSmemBytes, stream>>>(p);
+  alignas(64) CUtensorMap kmap;
+  memset(&kmap, 0, sizeof(kmap));
+  const int use_tma = make_k_map(p, kBF16, &kmap) ? 1 : 0;
+  kern<<<p.B * nqb, itc::kThreads, itc::kSmemBytes, stream>>>(p, kmap, use_tma);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -138,6 +138,17 @@ __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t clus
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// TMA tile load (no multicast): the box of a 2-D tensor map at element coordinates (x, y) lands at `smem_dst` in the
+// map's swizzle; its bytes are subtracted from the transaction count of `mbar` (this CTA).  x times the element size
+// must be a multiple of 16 bytes; rows beyond the tensor read as zeros.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tensor_map, uint32_t mbar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
+               "l"(tensor_map), "r"(x), "r"(y), "r"(mbar)
+               : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
+}
 // Local arrive (count 1) that also adds `tx_bytes` to the barrier's expected transaction count.
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t tx_bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(tx_bytes) : "memory");
