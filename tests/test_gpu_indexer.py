@@ -119,3 +119,25 @@ def test_tnd_layout_matches_bsnd():
                                      actual_seq_lengths_key=torch.tensor(kl), sparse_count=32)
     check_status()
     assert torch.equal(idx_t[:6], idx_b[0, :6]) and torch.equal(idx_t[6:], idx_b[1, :4])
+
+
+def test_tma_and_cp_async_key_tiles_agree(monkeypatch):
+    """The tensor-core score kernel fetches key tiles with TMA tile loads; its cp.async producers (used when no tensor
+    map can be made for k) must give bit-identical scores.  Two batch entries, so that a key tile of the first entry
+    reaches into the rows of the second one, and actual lengths shorter than the tensors."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator().manual_seed(5)
+    B, S1, S2, N1 = 2, 96, 1000, 64
+    q = torch.randn((B, S1, N1, 128), generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn((B, S2, 1, 128), generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn((B, S1, N1), generator=g) / 8).float().cuda()
+    a = dsa.indexer_scores_raw(q, k, w, sparse_mode=3)
+    check_status()
+    monkeypatch.setenv("DSA_INDEXER_NO_TMA", "1")
+    b = dsa.indexer_scores_raw(q, k, w, sparse_mode=3)
+    check_status()
+    assert torch.equal(torch.isfinite(a), torch.isfinite(b))
+    fin = torch.isfinite(a)
+    assert torch.equal(a[fin], b[fin])
+    ref = orc.indexer_scores(q.cpu(), k.cpu(), w.cpu(), sparse_mode=3)
+    _scores_close(a.cpu().numpy(), ref.numpy() if hasattr(ref, "numpy") else np.asarray(ref))

@@ -16,6 +16,7 @@
 //
 // Generic kernel (any D, any N1): CUDA-core fp32.
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 #include <type_traits>
 
@@ -344,7 +345,9 @@ static int launch_indexer_tc_n1(const IndexerParams& p, cudaStream_t stream) {
   const int nqb = (p.S1 + QB - 1) / QB;
   alignas(64) CUtensorMap kmap;
   memset(&kmap, 0, sizeof(kmap));
-  const int use_tma = make_k_map(p, kBF16, &kmap) ? 1 : 0;
+  // DSA_INDEXER_NO_TMA=1 in the environment forces the cp.async producers (used by the tests to cover that path)
+  const char* no_tma = getenv("DSA_INDEXER_NO_TMA");
+  const int use_tma = (!(no_tma && no_tma[0] == '1') && make_k_map(p, kBF16, &kmap)) ? 1 : 0;
   kern<<<p.B * nqb, itc::kThreads, itc::kSmemBytes, stream>>>(p, kmap, use_tma);
   return static_cast<int>(cudaGetLastError());
 }
