@@ -154,16 +154,16 @@ __global__ void __launch_bounds__(256) sparse_mla_bwd_kernel(const BwdParams bp)
 }
 
 // -------------------------------------------------------------------------------------------------
-// D = 576 / DV = 512: one CTA per (query, group of 32 heads), 288 threads
+// D = 576 / DV = 512: one CTA per (query, group of 32 heads), 256 threads
 // -------------------------------------------------------------------------------------------------
 // Per tile of 32 gathered KV rows:
 //   phase A (8 warps, 4 heads each): per (head, key) the two dot products q.k and dO.v over the lanes, P and dS from
 //            them, dQ += dS * k in registers; P and dS of the 32 x 32 (head, key) pairs go to shared memory;
-//   phase B (all threads): the tile's key gradient  dKV[j, :] = sum_h dS[h, j] q[h, :] + P[h, j] dO[h, :]  as a small
+//   phase B (all threads, 288 slots of 4 dims x 16 keys): the tile's key gradient  dKV[j, :] = sum_h dS[h, j] q[h, :] + P[h, j] dO[h, :]  as a small
 //            register-tiled matrix product (thread = 4 dims x 16 keys, loop over the 32 heads), then ONE vector atomic
 //            per (key, 4 dims) to global memory -- a quarter of the atomics of the generic kernel and none in shared memory.
 namespace bwd2 {
-constexpr int kBK = 32, kHG = 32, kThreads = 288, kD = 576, kDV = 512;
+constexpr int kBK = 32, kHG = 32, kThreads = 256, kD = 576, kDV = 512;  // 8 warps: two per scheduler, up to 255 registers
 constexpr size_t kOffK = 0;                                   // [32][576] T
 constexpr size_t kOffQ = kOffK + kBK * kD * 2;                // [32][576] T
 constexpr size_t kOffDO = kOffQ + kHG * kD * 2;               // [32][512] T
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(bwd2::kThreads, 1) sparse_mla_bwd_mla_kernel(c
     }
     __syncthreads();
     // ---- phase A ----
-    if (warp < 8) {
+    {
 #pragma unroll
       for (int hq = 0; hq < 4; ++hq) {
         const int hh = warp * 4 + hq;
@@ -292,40 +292,63 @@ __global__ void __launch_bounds__(bwd2::kThreads, 1) sparse_mla_bwd_mla_kernel(c
 #pragma unroll
         for (int i = 0; i < 8; ++i) g2[i] = pair_to_float2<T>(grow[i * 32 + lane]);
         const float delta = s_delta[hh], lse2 = s_lse2[hh];
-        for (int j = 0; j < kBK; ++j) {
-          float prob = 0.f, ds = 0.f;
-          if (s_valid[j]) {  // uniform over the warp
-            const uint32_t* krow = reinterpret_cast<const uint32_t*>(Ks + j * kD);
-            float2 k2[9];
-            float dot = 0.f, dp = 0.f;
+        // four keys at a time: their dot products, reductions and dQ updates are independent chains that overlap
+#pragma unroll 1
+        for (int j0 = 0; j0 < kBK; j0 += 4) {
+          float2 k2[4][9];
+          float dot[4], dp[4];
 #pragma unroll
-            for (int i = 0; i < 9; ++i) {
-              k2[i] = pair_to_float2<T>(krow[i * 32 + lane]);
-              dot = fmaf(q2[i].x, k2[i].x, fmaf(q2[i].y, k2[i].y, dot));
-            }
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint32_t* krow = reinterpret_cast<const uint32_t*>(Ks + (j0 + jj) * kD);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dp = fmaf(g2[i].x, k2[i].x, fmaf(g2[i].y, k2[i].y, dp));
+            for (int i = 0; i < 9; ++i) k2[jj][i] = pair_to_float2<T>(krow[i * 32 + lane]);
+          }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              dot += __shfl_xor_sync(0xffffffffu, dot, o);
-              dp += __shfl_xor_sync(0xffffffffu, dp, o);
-            }
-            prob = exp2f(dot * p.scale_log2 - lse2);
-            ds = prob * (dp - delta) * bp.sm_scale;
+          for (int jj = 0; jj < 4; ++jj) {
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 9; ++i) {
-              dq[hq][2 * i] = fmaf(ds, k2[i].x, dq[hq][2 * i]);
-              dq[hq][2 * i + 1] = fmaf(ds, k2[i].y, dq[hq][2 * i + 1]);
+            for (int i = 0; i < 9; ++i) { a0 = fmaf(q2[i].x, k2[jj][i].x, a0); a1 = fmaf(q2[i].y, k2[jj][i].y, a1); }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { b0 = fmaf(g2[i].x, k2[jj][i].x, b0); b1 = fmaf(g2[i].y, k2[jj][i].y, b1); }
+            dot[jj] = a0 + a1;
+            dp[jj] = b0 + b1;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              dot[jj] += __shfl_xor_sync(0xffffffffu, dot[jj], o);
+              dp[jj] += __shfl_xor_sync(0xffffffffu, dp[jj], o);
             }
           }
-          if (lane == 0) { DSs[hh * kBK + j] = ds; Ps[hh * kBK + j] = prob; }
+          float prob[4], ds[4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            // a key that does not take part was gathered as zeros: its probability must still be forced to zero
+            prob[jj] = s_valid[j0 + jj] ? exp2f(dot[jj] * p.scale_log2 - lse2) : 0.f;
+            ds[jj] = prob[jj] * (dp[jj] - delta) * bp.sm_scale;
+          }
+#pragma unroll
+          for (int i = 0; i < 9; ++i) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              dq[hq][2 * i] = fmaf(ds[jj], k2[jj][i].x, dq[hq][2 * i]);
+              dq[hq][2 * i + 1] = fmaf(ds[jj], k2[jj][i].y, dq[hq][2 * i + 1]);
+            }
+          }
+          if (lane < 4) {
+            const float dsl = lane == 0 ? ds[0] : lane == 1 ? ds[1] : lane == 2 ? ds[2] : ds[3];
+            const float pl = lane == 0 ? prob[0] : lane == 1 ? prob[1] : lane == 2 ? prob[2] : prob[3];
+            DSs[hh * kBK + j0 + lane] = dsl;
+            Ps[hh * kBK + j0 + lane] = pl;
+          }
         }
       }
     }
     __syncthreads();
-    // ---- phase B: thread = (4 dims, 16 keys) ----
-    {
-      const int dg = tid % 144, kh = tid / 144;
+    // ---- phase B: slot = (4 dims, 16 keys); 288 slots over 256 threads ----
+    for (int slot = tid; slot < 288; slot += kThreads) {
+      const int dg = slot % 144, kh = slot / 144;
       float acc[16][4];
 #pragma unroll
       for (int j = 0; j < 16; ++j)
