@@ -1,4 +1,4 @@
-// Sparse MLA backward (correctness-first CUDA-core kernel).
+// Sparse MLA backward (CUDA-core kernels).
 //
 // Given q, kv, indices, the forward's out / lse and the output gradient dO it produces
 //   dQ  [B, S, H, D]      (input dtype)
@@ -9,9 +9,9 @@
 // the saved LSE, fp32 atomic accumulation of the key gradient) is the one its dense backward uses
 // (examples_experiment/example_gqa_bwd/example_gqa_bwd.py:189-223, 312-556).
 //
-// One CTA per (query, group of 8 heads), one warp per head; a tile of 32 gathered KV rows sits in
-// shared memory next to an fp32 tile that collects the 8 heads' key gradients before they go to
-// global memory as one atomic add per element.
+// Two kernels.  Generic (any D <= 640, DV <= 512): one CTA per (query, group of 8 heads), one warp per head; a tile of
+// 32 gathered KV rows sits in shared memory next to an fp32 tile that collects the 8 heads' key gradients before
+// they go to global memory as one atomic add per element.  D = 576 / DV = 512: see sparse_mla_bwd_mla_kernel below.
 #include <type_traits>
 
 #include "params.h"
