@@ -253,9 +253,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       prefetch_q(item_of(k + 1));  // the next item's rows, while this item is being worked on
       for (int it = 0; it < nvt; ++it, ++g) {
         const int sb = g & 1;
-        uint32_t v[32];
+        uint32_t v[2][32];
         if (!__all_sync(0xffffffffu, mbar_wait<true>(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
         tc_fence_after();
+        // both column halves of the rows are read at once; the sends below then only wait for their buffers
+        tmem_ld32(tS + sb * kBK + lane_base, v[0]);
+        tmem_ld32(tS + sb * kBK + 32 + lane_base, v[1]);
+        tmem_wait_ld();
         // The receive buffer is handled in two column halves with their own barriers, so that the peer's first half
         // can be on its way while the second half of the previous tile is still being read there.
 #pragma unroll
@@ -266,12 +270,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           // this CTA's receive barrier is armed once per tile: its previous phase (tile g-1) must be complete first --
           // the peer's credit above says the peer read OUR data, not that ITS data has fully landed here
           if (g >= 1 && !__all_sync(0xffffffffu, mbar_wait<true>(&x_full[xb], (g + 1) & 1, p.status))) { ok = false; break; }
-          tmem_ld32(tS + sb * kBK + hf * 32 + lane_base, v);
-          tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            st_async_v4(peer_x + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + xb * 8, __uint_as_float(v[4 * j]),
-                        __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            st_async_v4(peer_x + (8 * hf + j) * (kM * 16) + r * 16, peer_x_full + xb * 8, __uint_as_float(v[hf][4 * j]),
+                        __uint_as_float(v[hf][4 * j + 1]), __uint_as_float(v[hf][4 * j + 2]), __uint_as_float(v[hf][4 * j + 3]));
           // Arm this CTA's receive barrier for the same rows and columns only now: its completion then tells the softmax
           // warp of this block three things at once -- the peer's partial scores have landed, this CTA's own QK MMAs of
           // the tile are complete (s_full was waited for above), and this warp has read its copy of these scores out
