@@ -118,6 +118,24 @@ int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, vo
                        const int32_t* kv_len_b, const int32_t* q_len_b, const int32_t* block_table, int32_t block_size,
                        int32_t max_blocks, int32_t impl, void* stream);
 
+/* The same forward with the keys of every query split over `nsplit` work units (tensor-core kernel only: D = 576,
+ * DV = 512): for calls with fewer (query, block of 128 heads) items than SM pairs -- decode with a handful of
+ * sequences per GPU -- where one unit per query would leave most of the GPU idle.  Each unit writes a normalised
+ * partial output and its log-sum-exp into `workspace` (fp32, size from dsa_sparse_mla_fwd_splitkv_workspace_bytes,
+ * 16-byte aligned, owned by the caller); a second kernel on the same stream combines them into out / lse.
+ * nsplit = 1 is dsa_sparse_mla_fwd with impl = DSA_IMPL_TENSOR_CORE; dsa_sparse_mla_fwd_splitkv_nsplit suggests a
+ * value for the current device (1 = do not split).  Queries that do not exist (q_len_b) get out = 0, lse = -inf.
+ * Replaces the same reference kernels as dsa_sparse_mla_fwd (their decode shape:
+ * bench_sfa/sparse_flash_attn_pa_no_cv_pipeline.py:384-419, T = 1). */
+int dsa_sparse_mla_fwd_splitkv_nsplit(int32_t B, int32_t S, int32_t H, int32_t topk);
+size_t dsa_sparse_mla_fwd_splitkv_workspace_bytes(int32_t B, int32_t S, int32_t H, int32_t DV, int32_t nsplit);
+int dsa_sparse_mla_fwd_splitkv(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B,
+                               int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale,
+                               int32_t q_start, int32_t causal, int32_t dtype, const int32_t* q_start_b,
+                               const int32_t* kv_len_b, const int32_t* q_len_b, const int32_t* block_table,
+                               int32_t block_size, int32_t max_blocks, int32_t nsplit, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
 /* Sparse MLA backward.  Inputs as the forward plus out / lse of the forward and d_out [B,S,H,DV];
  * outputs d_q [B,S,H,D] (dtype) and d_kv (fp32, same shape as kv, ACCUMULATED INTO: zero it first).
  * The reference has no counterpart kernel; the decomposition follows its dense backward

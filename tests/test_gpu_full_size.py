@@ -103,12 +103,17 @@ def test_decode_full_size():
         ro, rl = orc.sparse_mla_fwd(q[b:b + 1].cpu(), kv[b:b + 1].cpu(), idx[b:b + 1].cpu(), q_start_index_s=10 ** 9)
         assert_close_fp(out[b:b + 1].cpu(), ro, f"decode out {b}")
         assert_close_fp(lse[b:b + 1].cpu(), rl, f"decode lse {b}")
-    # sharded by batch (8 "ranks"): identical to the unsharded call
+    # sharded by batch (8 "ranks"): identical to the unsharded call with one work unit per query; with 8 sequences on a
+    # GPU the library splits every query's keys over several units, which changes the summation order only
     for rank in (0, 5):
         qs, kvs, ixs = dsa.shard_batch([q, kv, idx], rank, 8)
-        o, l = dsa.sparse_mla_fwd_raw(qs, kvs, ixs, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512)
         s, e = dsa.shard_range(B, rank, 8)
+        o, l = dsa.sparse_mla_fwd_raw(qs, kvs, ixs, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512, nsplit=1)
         assert torch.equal(o, out[s:e]) and torch.equal(l, lse[s:e])
+        o, l = dsa.sparse_mla_fwd_raw(qs, kvs, ixs, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512)
+        check_status()
+        assert_close_fp(o.cpu(), out[s:e].cpu(), f"split-KV decode out, shard {rank}")
+        assert_close_fp(l.cpu(), lse[s:e].cpu(), f"split-KV decode lse, shard {rank}")
 
 
 def test_backward_prefill_shape_properties():

@@ -183,3 +183,44 @@ def test_host_buffer_pipeline_matches_direct_call():
         assert torch.equal(out_h, ref_o.cpu()) and torch.equal(lse_h, ref_l.cpu())
     with pytest.raises(ValueError):
         pipe(q, kv.pin_memory(), idx.pin_memory(), out_h, lse_h)  # not pinned
+
+
+@pytest.mark.parametrize("nsplit", [2, 3, 5, 16])
+def test_split_kv_matches_unsplit_and_oracle(nsplit):
+    """Keys of a query split over several work units + combine: same result as one unit per query.  topk 320 = 5 tiles
+    of 64, so 2 and 3 give uneven shares, 5 one tile each, 16 leaves most shares without a tile; a short query (fewer
+    keys than tiles) and -1 padding are in the mix through the causal sampling of the first rows."""
+    q, kv, idx = orc.make_sparse_mla_inputs(2, 6, 400, 128, 320, seed=9)
+    idx[0, 0, 0, 40:] = -1  # one query with a single partly filled tile
+    one_o, one_l = _fwd(q, kv, idx, IMPL_TC, nsplit=1)
+    spl_o, spl_l = _fwd(q, kv, idx, IMPL_TC, nsplit=nsplit)
+    assert_close_fp(spl_o, one_o, "split vs unsplit out")
+    assert_close_fp(spl_l, one_l, "split vs unsplit lse")
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(spl_o, ref_o, "out vs oracle")
+    assert_close_fp(spl_l, ref_l, "lse vs oracle")
+
+
+def test_split_kv_is_chosen_for_a_few_sequences_and_handles_absent_queries():
+    """Decode of 4 sequences: the library splits on its own (fewer queries than SM pairs); per-sequence lengths, one
+    sequence without its query (q_len 0): out = 0 and lse = -inf there."""
+    import tilelang_ascend_b200 as dsa
+    from tilelang_ascend_b200 import _lib
+    B, S_kv, H, topk = 4, 2048, 128, 512
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn((B, 1, H, 576), generator=g).to(torch.bfloat16)
+    kv = torch.randn((B, S_kv, 1, 576), generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(S_kv, generator=g)[:topk] for _ in range(B)]).to(torch.int32).view(B, 1, 1, topk)
+    assert int(_lib.load().dsa_sparse_mla_fwd_splitkv_nsplit(B, 1, H, topk)) > 1
+    q_len = torch.tensor([1, 1, 0, 1], dtype=torch.int32)
+    kv_len = torch.tensor([S_kv, 1500, S_kv, S_kv], dtype=torch.int32)
+    out, lse = dsa.sparse_mla_fwd_raw(q.cuda(), kv.cuda(), idx.cuda(), sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512,
+                                      q_len_b=q_len.cuda(), kv_len_b=kv_len.cuda())
+    check_status()
+    one, one_l = dsa.sparse_mla_fwd_raw(q.cuda(), kv.cuda(), idx.cuda(), sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512,
+                                        q_len_b=q_len.cuda(), kv_len_b=kv_len.cuda(), nsplit=1)
+    check_status()
+    keep = [0, 1, 3]
+    assert_close_fp(out.cpu()[keep], one.cpu()[keep], "auto split vs unsplit out")
+    assert_close_fp(lse.cpu()[keep], one_l.cpu()[keep], "auto split vs unsplit lse")
+    assert torch.count_nonzero(out[2]).item() == 0 and torch.isinf(lse[2]).all() and (lse[2] < 0).all()

@@ -26,6 +26,12 @@ struct FwdParams {
   int block_size, max_blocks;
   float scale_log2;            // sm_scale * log2(e)
   int* status;                 // device status word (0 = ok)
+  // Split-KV (tensor-core kernel only): with nsplit > 1 every (query, head block) is handled by nsplit work units, each
+  // taking a contiguous share of the query's key tiles and writing a normalised partial result; a second kernel
+  // combines them.  part_out [nsplit, B*S, H, DV] fp32, part_lse [nsplit, B*S, H] fp32 (natural log, -inf = no key).
+  int nsplit;
+  float* part_out;
+  float* part_lse;
 };
 
 // Sparse MLA backward: the forward's fields (out / lse hold the forward results) plus gradients.

@@ -159,10 +159,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
   const uint32_t peer = rank ^ 1u;
   const int num_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
   const int head_blocks = (p.H + kM - 1) / kM;
-  const int num_items = p.B * p.S * head_blocks;
+  const int nsplit = p.nsplit > 1 ? p.nsplit : 1;
+  const int num_items = p.B * p.S * head_blocks * nsplit;  // work units: (query, head block, share of the key tiles)
   const int ntiles = (p.topk + kBK - 1) / kBK;
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
-  // k-th item of this cluster (late queries first), or -1
+  // k-th work unit of this cluster (late queries first), or -1; unit = (query, head block) * nsplit + share
   auto item_of = [&](int k) { const int it = num_items - 1 - cluster_id - k * num_clusters; return it; };
 
   // ---- setup ------------------------------------------------------------------------------------------
@@ -206,8 +207,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     const uint32_t peer_x = map_to_cta(sX, peer);
     const uint32_t peer_x_full = map_to_cta(smem_u32(x_full), peer);
     // pulls this thread's Q row of an item towards L2 (the CTA's 4 latent lines and its rope line)
-    auto prefetch_q = [&](int it_item) {
-      if (it_item < 0) return;
+    auto prefetch_q = [&](int it_unit) {
+      if (it_unit < 0) return;
+      const int it_item = it_unit / nsplit;
       const int nbt = it_item / head_blocks, nh = (it_item - nbt * head_blocks) * kM + r;
       if (nh >= p.H) return;
       const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * (kD * 2);
@@ -218,8 +220,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     if (run_all) prefetch_q(item_of(0));  // the first item's rows: behind the wait for its tile list
     int g = 0;
     for (int k = 0; run_all && ok; ++k) {
-      const int item = item_of(k);
-      if (item < 0) break;
+      const int unit = item_of(k);
+      if (unit < 0) break;
+      const int item = unit / nsplit;
       const int qp = k & 1;
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
       if (!__all_sync(0xffffffffu, mbar_wait<true>(&info_full[qp], (k >> 1) & 1, p.status))) { ok = false; break; }
@@ -294,8 +297,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
     int g = 0;
     for (int k = 0; run_all; ++k) {
-      const int item = item_of(k);
-      if (item < 0) break;
+      const int unit = item_of(k);
+      if (unit < 0) break;
+      const int item = unit / nsplit, share = unit - item * nsplit;
       const int qp = k & 1;
       const int bt = item / head_blocks;
       const RowCtx ctx = make_row_ctx(p, bt);
@@ -329,6 +333,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           const uint32_t bal = __ballot_sync(0xffffffffu, nonempty);
           if (nonempty) tile_list[qp * kMaxTiles + n + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(tile);
           n += __popc(bal);
+        }
+        if (nsplit > 1) {
+          // this unit's share of the list: entries [lo, hi) move to the front (in chunks of 32, reading before writing)
+          const int lo = static_cast<int>(static_cast<long long>(n) * share / nsplit);
+          const int hi = static_cast<int>(static_cast<long long>(n) * (share + 1) / nsplit);
+          __syncwarp();
+          for (int base = 0; base < hi - lo; base += 32) {
+            const int i = base + lane;
+            const uint16_t v = i < hi - lo ? tile_list[qp * kMaxTiles + lo + i] : 0;
+            __syncwarp();
+            if (i < hi - lo) tile_list[qp * kMaxTiles + i] = v;
+            __syncwarp();
+          }
+          n = hi - lo;
         }
         if (lane == 0) { info[qp * 2] = n; info[qp * 2 + 1] = ctx.active ? 1 : 0; }
         __syncwarp();
@@ -457,8 +475,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
     const uint32_t peer_x_empty = map_to_cta(smem_u32(x_empty), peer);
     int g = 0;
     for (int k = 0; run_all; ++k) {
-      const int item = item_of(k);
-      if (item < 0) break;
+      const int unit = item_of(k);
+      if (unit < 0) break;
+      const int item = unit / nsplit, share = unit - item * nsplit;
       const int qp = k & 1;
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status));
@@ -584,7 +603,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       }
       const int h = h0 + r;
       T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + rank * kHalfDV;
-      if (active && nvt == 0) {
+      // split-KV: this unit's normalised partial result and its log-sum-exp go to the workspace instead
+      const int64_t prow_index = (static_cast<int64_t>(share) * p.B * p.S + bt) * p.H + h;
+      float* part_row = nsplit > 1 ? p.part_out + prow_index * kDV + rank * kHalfDV : nullptr;
+      if (nsplit > 1 && nvt == 0) {
+        if (h < p.H) {  // nothing to add from this share (also for queries that do not exist: the combine step writes zeros)
+          for (int j = 32 * ch; j < 32 * ch + 32; ++j) reinterpret_cast<float4*>(part_row)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (rank == 0 && ch == 0) p.part_lse[prow_index] = -INFINITY;
+        }
+      } else if (active && nvt == 0) {
         if (h < p.H) {
           for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
           if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
@@ -599,7 +626,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         for (int cc = 4 * ch; cc < 4 * ch + 4; ++cc) {
           tmem_ld32(tO + lane_base + cc * 32, v);
           tmem_wait_ld();
-          if (ok && h < p.H) {
+          if (ok && h < p.H && nsplit > 1) {
+#pragma unroll
+            for (int gq = 0; gq < 8; ++gq)
+              reinterpret_cast<float4*>(part_row + cc * 32)[gq] =
+                  make_float4(__uint_as_float(v[4 * gq]) * inv_l, __uint_as_float(v[4 * gq + 1]) * inv_l, __uint_as_float(v[4 * gq + 2]) * inv_l,
+                              __uint_as_float(v[4 * gq + 3]) * inv_l);
+          } else if (ok && h < p.H) {
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
               uint4 w;
@@ -611,7 +644,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
             }
           }
         }
-        if (ok && rank == 0 && ch == 0 && p.lse && h < p.H) p.lse[static_cast<int64_t>(bt) * p.H + h] = m_used * 0.6931471805599453f + logf(l);
+        if (ok && rank == 0 && ch == 0 && h < p.H) {
+          const float lse_v = m_used * 0.6931471805599453f + logf(l);
+          if (nsplit > 1) p.part_lse[prow_index] = lse_v;
+          else if (p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = lse_v;
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -717,6 +754,32 @@ __global__ void __launch_bounds__(256) sparse_mla_fwd_generic_kernel(const FwdPa
 }
 
 // -------------------------------------------------------------------------------------------------
+// split-KV combine: out = sum_s w_s part_out[s],  w_s = exp(lse_s - lse),  lse = log sum_s exp(lse_s)
+// -------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) sparse_mla_fwd_combine_kernel(const float* __restrict__ part_out, const float* __restrict__ part_lse,
+                                                                     T* __restrict__ out, float* __restrict__ lse, int64_t rows, int nsplit, int dv) {
+  const int64_t row = blockIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_lse[s * rows + row]);
+  float wsum = 0.f;
+  for (int s = 0; s < nsplit; ++s) wsum += (m == -INFINITY) ? 0.f : expf(part_lse[s * rows + row] - m);
+  for (int c = threadIdx.x * 4; c < dv; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < nsplit; ++s) {
+      const float ls = part_lse[s * rows + row];
+      if (ls == -INFINITY) continue;
+      const float w = expf(ls - m) / wsum;
+      const float4 v = *reinterpret_cast<const float4*>(part_out + (s * rows + row) * dv + c);
+      acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+    T* o = out + row * dv + c;
+    o[0] = static_cast<T>(acc.x); o[1] = static_cast<T>(acc.y); o[2] = static_cast<T>(acc.z); o[3] = static_cast<T>(acc.w);
+  }
+  if (threadIdx.x == 0 && lse) lse[row] = (m == -INFINITY) ? -INFINITY : m + logf(wsum);
+}
+
+// -------------------------------------------------------------------------------------------------
 // host launchers (return a cudaError_t as int; 0 = launched)
 // -------------------------------------------------------------------------------------------------
 bool sparse_mla_fwd_tc_supported(const FwdParams& p) {
@@ -734,9 +797,30 @@ int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream)
   // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
   const long long items = static_cast<long long>(p.B) * p.S * ((p.H + tc::kM - 1) / tc::kM);
   long long clusters = sms / 2 > 0 ? sms / 2 : 1;
-  if (clusters > items) clusters = items;
+  const long long units = items * (p.nsplit > 1 ? p.nsplit : 1);
+  if (clusters > units) clusters = units;
   kern<<<dim3(static_cast<unsigned>(2 * clusters)), tc::kThreads, tc::kSmemBytes, stream>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess || p.nsplit <= 1) return static_cast<int>(e);
+  const int64_t rows = static_cast<int64_t>(p.B) * p.S * p.H;
+  if (bf16)
+    sparse_mla_fwd_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 128, 0, stream>>>(p.part_out, p.part_lse, reinterpret_cast<__nv_bfloat16*>(p.out),
+                                                                                                p.lse, rows, p.nsplit, p.DV);
+  else
+    sparse_mla_fwd_combine_kernel<__half><<<static_cast<unsigned>(rows), 128, 0, stream>>>(p.part_out, p.part_lse, reinterpret_cast<__half*>(p.out), p.lse,
+                                                                                         rows, p.nsplit, p.DV);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Number of shares that fills the GPU's cluster slots when there are fewer (query, head block) items than slots.
+int sparse_mla_fwd_auto_nsplit(const FwdParams& p, int sms) {
+  const long long items = static_cast<long long>(p.B) * p.S * ((p.H + tc::kM - 1) / tc::kM);
+  const long long clusters = sms / 2 > 0 ? sms / 2 : 1;
+  const int ntiles = (p.topk + tc::kBK - 1) / tc::kBK;
+  long long ns = clusters / (items > 0 ? items : 1);
+  if (ns > 16) ns = 16;
+  if (ns > ntiles / 2) ns = ntiles / 2;  // at least two tiles per share
+  return ns < 2 ? 1 : static_cast<int>(ns);
 }
 
 int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t stream) {

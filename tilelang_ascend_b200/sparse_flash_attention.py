@@ -24,9 +24,14 @@ def _next_pow2(x: int) -> int:
 
 def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal: bool, dv: int, out=None,
                        return_lse: bool = True, q_start_b=None, kv_len_b=None, q_len_b=None, block_table=None,
-                       block_size: int = 0, impl: int = _lib.IMPL_AUTO):
+                       block_size: int = 0, impl: int = _lib.IMPL_AUTO, nsplit=None):
     """One launch of the forward through the C ABI.  q [B,S,H,D], kv [B,S_kv,1,D] (or paged blocks),
-    indices [B,S,1,topk] int32.  Returns (out, lse-or-None)."""
+    indices [B,S,1,topk] int32.  Returns (out, lse-or-None).
+
+    nsplit: None = let the library decide whether the keys of every query are split over several work units (it does for
+    D=576 / dv=512 calls with fewer queries than SM pairs, e.g. decode of a few sequences); 1 = never; n > 1 = n shares.
+    The fp32 workspace of a split call is allocated here, as the reference's adapter allocates its kernels' workspaces
+    (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137)."""
     opt = [t for t in (q_start_b, kv_len_b, q_len_b, block_table) if t is not None]
     dev = check_inputs([q, kv, indices] + opt, [None, q.dtype, torch.int32] + [torch.int32] * len(opt),
                        ["q", "kv", "indices"] + ["int32 side input"] * len(opt))
@@ -48,11 +53,26 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
     if out is None:
         out = torch.empty((B, S, H, dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, S, H), dtype=torch.float32, device=dev) if return_lse else None
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().dsa_sparse_mla_fwd(
-            ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
-            1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
-            int(max_blocks), int(impl), current_stream(dev)))
+        tc_shape = D == 576 and dv == 512 and topk <= 8192 and impl != _lib.IMPL_GENERIC
+        if nsplit is None:
+            nsplit = int(lib.dsa_sparse_mla_fwd_splitkv_nsplit(B, S, H, topk)) if tc_shape else 1
+        nsplit = int(nsplit)
+        if nsplit > 1:
+            if not tc_shape:
+                raise ValueError("nsplit > 1 needs D = 576, dv = 512, topk <= 8192 and the tensor-core kernel")
+            nbytes = int(lib.dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, dv, nsplit))
+            workspace = torch.empty((nbytes // 4,), dtype=torch.float32, device=dev)
+            _lib.check(lib.dsa_sparse_mla_fwd_splitkv(
+                ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
+                1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
+                int(max_blocks), nsplit, ptr(workspace), nbytes, current_stream(dev)))
+        else:
+            _lib.check(lib.dsa_sparse_mla_fwd(
+                ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
+                1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
+                int(max_blocks), int(impl), current_stream(dev)))
     return out, lse
 
 
