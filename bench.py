@@ -151,6 +151,10 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     t_dec = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd, kvd, idxd, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=20)
     dec_bytes = B * (topk * 1152 + H * 576 * 2 + H * 512 * 2 + topk * 4)
     dec_gbs = dec_bytes / (t_dec * 1e-3) / 1e9
+    # one GPU's share of the same decode case sharded over 8 GPUs: 8 sequences, keys of every query split over work units
+    B8 = 8
+    t_dec8 = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd[:B8], kvd[:B8], idxd[:B8], sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=20)
+    t_dec8_one = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd[:B8], kvd[:B8], idxd[:B8], sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512, nsplit=1), reps=20)
     del qd, kvd, idxd
     # backward at the prefill shape (last S_b queries of the workload; dKV accumulated in fp32)
     S_b = 256 if small else WORKLOAD["S"]
@@ -174,6 +178,8 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
         "decode": {"us": t_dec * 1e3, "tokens_per_s": B / (t_dec * 1e-3), "algorithmic_gb_per_s": dec_gbs,
                    "frac_of_hbm_peak": dec_gbs / peaks["hbm_gbs"], "algorithmic_bytes": dec_bytes,
                    "workload": f"B={B} x 1 token, S_kv=32768, H=128, topk=2048 (KV cache {B * S_kv * 1152 / 1e9:.1f} GB, larger than L2)"},
+        "decode_8_sequences": {"us": t_dec8 * 1e3, "us_one_unit_per_query": t_dec8_one * 1e3, "tokens_per_s": B8 / (t_dec8 * 1e-3),
+                               "workload": "8 of those sequences (one GPU's share at 8 GPUs), split-KV chosen by the library"},
     }
 
 
