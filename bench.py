@@ -30,8 +30,8 @@ sys.path.insert(0, ROOT)
 WORKLOAD = dict(B=1, S=4096, S_kv=4096, H=128, D=576, DV=512, topk=2048)
 FLOP_PER_PAIR_HEAD = 2 * 576 + 2 * 512  # QK^T over 576 dims + PV over 512 dims
 METRIC, UNIT = "dsa_prefill_tokens_per_s", "tokens/s"
-# DRAM bytes per query of the forward kernel: (96 930 304 read + 36 243 456 written) / 592 queries, one ncu capture
-DRAM_BYTES_PER_QUERY = (96930304 + 36243456) / 592
+# DRAM bytes per query of the forward kernel: (96 945 664 read + 33 952 256 written) / 592 queries, one ncu capture
+DRAM_BYTES_PER_QUERY = (96945664 + 33952256) / 592
 
 
 def valid_pairs(S: int, S_kv: int, topk: int) -> int:
@@ -243,8 +243,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="prefill", choices=["prefill", "others"],
-                    help="profiling aid: 'others' runs only the indexer / top-k / decode measurements and prints them")
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others"],
+                    help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="queries the CPU baseline / parity sample covers")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
@@ -360,7 +361,7 @@ def main() -> None:
     }
 
     # ---- the rest of the path on its BASELINE shapes (N=1 only; reported beside the headline, not part of it) ----
-    if rank == 0 and world == 1 and not args.queries:
+    if rank == 0 and world == 1 and not args.queries and args.stage == "all":
         line["other_stages"] = measure_other_stages(dev, peaks)
 
     # ---- CPU baseline (rank 0, N=1 only): the oracle on a bounded sample; doubles as a parity check -----
