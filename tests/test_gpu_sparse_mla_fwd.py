@@ -224,3 +224,28 @@ def test_split_kv_is_chosen_for_a_few_sequences_and_handles_absent_queries():
     assert_close_fp(out.cpu()[keep], one.cpu()[keep], "auto split vs unsplit out")
     assert_close_fp(lse.cpu()[keep], one_l.cpu()[keep], "auto split vs unsplit lse")
     assert torch.count_nonzero(out[2]).item() == 0 and torch.isinf(lse[2]).all() and (lse[2] < 0).all()
+
+
+def test_split_kv_fp16_paged():
+    """Split-KV through a block table and in float16: same answer as one unit per query on the same paged cache."""
+    import tilelang_ascend_b200 as dsa
+    B, S_kv, H, topk, bs = 3, 1024, 128, 256, 64
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn((B, 1, H, 576), generator=g).to(torch.float16)
+    kv = torch.randn((B, S_kv, 1, 576), generator=g).to(torch.float16)
+    idx = torch.stack([torch.randperm(S_kv, generator=g)[:topk] for _ in range(B)]).to(torch.int32).view(B, 1, 1, topk)
+    nblk = S_kv // bs
+    table = torch.randperm(B * nblk, generator=g).view(B, nblk).to(torch.int32)
+    paged = torch.zeros((B * nblk, bs, 1, 576), dtype=kv.dtype)
+    for b in range(B):
+        for j in range(nblk):
+            paged[table[b, j]] = kv[b, j * bs:(j + 1) * bs]
+    kw = dict(sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512, block_table=table.cuda(), block_size=bs)
+    one, one_l = dsa.sparse_mla_fwd_raw(q.cuda(), paged.cuda(), idx.cuda(), nsplit=1, **kw)
+    spl, spl_l = dsa.sparse_mla_fwd_raw(q.cuda(), paged.cuda(), idx.cuda(), nsplit=2, **kw)
+    check_status()
+    assert_close_fp(spl.cpu(), one.cpu(), "paged fp16 split vs unsplit out")
+    assert_close_fp(spl_l.cpu(), one_l.cpu(), "paged fp16 split vs unsplit lse")
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx, q_start_index_s=10 ** 9)
+    assert_close_fp(spl.cpu(), ref_o, "out vs oracle")
+    assert_close_fp(spl_l.cpu(), ref_l, "lse vs oracle")

@@ -24,7 +24,7 @@ def test_fixture_from_reference_topk(golden):
 
 
 @pytest.mark.parametrize("B,N,K", [(64, 4096, 2048), (1024, 1024, 128), (7, 8192, 2048), (3, 1000, 1000), (5, 33, 1),
-                                   (2, 32768, 2048), (4, 5000, 4096)])
+                                   (2, 32768, 2048), (4, 5000, 4096), (3, 8192, 8192), (3, 500, 64), (3, 500, 65), (2, 3000, 2049)])
 def test_random_rows_match_oracle(B, N, K):
     rng = np.random.default_rng(B * 131 + N)
     x = rng.standard_normal((B, N)).astype(np.float32)

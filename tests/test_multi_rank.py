@@ -53,3 +53,44 @@ def test_two_rank_query_sharding_reassembles():
             p.join(120)
             assert p.exitcode == 0
         assert ret.get("ok") is True
+
+
+def _bwd_worker(rank: int, world: int, port: int, ret):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import tilelang_ascend_b200 as dsa
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    S, S_kv = 9, 48
+    q, kv, idx = orc.make_sparse_mla_inputs(1, S, S_kv, 4, 16, seed=1)
+    d_out = torch.randn((1, S, 4, 512), generator=torch.Generator().manual_seed(2))
+    qs, ix, q_start = dsa.shard_queries(q, idx, rank, world, s_kv=S_kv)
+    s, e = dsa.shard_range(S, rank, world)
+
+    def oracle_bwd(q_, kv_, idx_, out_, lse_, d_out_, *, sm_scale, q_start, causal):  # stands in for the device kernel
+        return orc.sparse_mla_bwd(q_, kv_, idx_, d_out_, q_start_index_s=q_start, sm_scale=sm_scale)
+
+    d_q, d_kv = dsa.sparse_mla_bwd_sharded(qs, kv, ix, None, None, d_out[:, s:e].contiguous(), sm_scale=576 ** -0.5,
+                                           q_start_index_s=q_start, bwd=oracle_bwd)
+    ref_dq, ref_dkv = orc.sparse_mla_bwd(q, kv, idx, d_out)
+    ok = bool(torch.allclose(d_q, ref_dq[:, s:e], atol=1e-5)) and bool(torch.allclose(d_kv, ref_dkv, atol=1e-4))
+    flag = torch.tensor([1.0 if ok else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ret["ok"] = float(flag) == 1.0
+    dist.destroy_process_group()
+
+
+def test_two_rank_backward_sums_key_gradient():
+    """dQ shards by query; dKV needs the one all-reduce of the path: every rank ends with the full key gradient."""
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as m:
+        ret = m.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_bwd_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(180)
+            assert p.exitcode == 0
+        assert ret.get("ok") is True
