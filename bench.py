@@ -156,6 +156,25 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     t_dec8 = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd[:B8], kvd[:B8], idxd[:B8], sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=20)
     t_dec8_one = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd[:B8], kvd[:B8], idxd[:B8], sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512, nsplit=1), reps=20)
     del qd, kvd, idxd
+    # the whole pipeline on the prefill shape: indexer scores -> top-2048 -> sparse MLA forward on the SELECTED indices,
+    # three library calls back to back on one stream (S_q = S_kv = 4096; index heads 64 x 128 as in the indexer case)
+    Sp = 1024 if small else WORKLOAD["S"]
+    S_kvp = WORKLOAD["S_kv"]
+    qi = torch.randn((1, Sp, 64, 128), generator=g, device=dev).to(torch.bfloat16)
+    ki = torch.randn((1, S_kvp, 1, 128), generator=g, device=dev).to(torch.bfloat16)
+    wi = (torch.randn((1, Sp, 64), generator=g, device=dev) / 8).float()
+    qm = torch.randn((1, Sp, WORKLOAD["H"], WORKLOAD["D"]), generator=g, device=dev).to(torch.bfloat16)
+    kvm = torch.randn((1, S_kvp, 1, WORKLOAD["D"]), generator=g, device=dev).to(torch.bfloat16)
+
+    def pipeline():
+        sel, _ = dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=WORKLOAD["topk"], sparse_mode=3)
+        return dsa.sparse_mla_fwd_raw(qm, kvm, sel.view(1, Sp, 1, WORKLOAD["topk"]), sm_scale=WORKLOAD["D"] ** -0.5, q_start=S_kvp - Sp,
+                                      causal=True, dv=WORKLOAD["DV"])
+    t_pipe = _time_ms(pipeline)
+    pp = np.arange(Sp, dtype=np.int64) + (S_kvp - Sp) + 1                       # candidates per query (causal)
+    pipe_flop = int(pp.sum()) * 64 * 256 + int(np.minimum(pp, WORKLOAD["topk"]).sum()) * WORKLOAD["H"] * FLOP_PER_PAIR_HEAD
+    pipe_tflops = pipe_flop / (t_pipe * 1e-3) / 1e12
+    del qi, ki, wi, qm, kvm
     # backward at the prefill shape (last S_b queries of the workload; dKV accumulated in fp32)
     S_b = 256 if small else WORKLOAD["S"]
     saved = WORKLOAD["S"]
@@ -172,6 +191,8 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     return {
         "backward": {"ms": t_bwd, "tokens_per_s": S_b / (t_bwd * 1e-3), "tflops": bwd_tflops, "frac_of_bf16_peak": bwd_tflops / peaks["bf16_tflops"],
                      "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (CUDA-core kernel)"},
+        "pipeline": {"ms": t_pipe, "tokens_per_s": Sp / (t_pipe * 1e-3), "tflops": pipe_tflops, "frac_of_bf16_peak": pipe_tflops / peaks["bf16_tflops"],
+                     "workload": f"indexer (64 x 128) -> top-2048 -> sparse MLA forward on the selected indices, S_q={Sp}, S_kv={S_kvp}, one stream"},
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
                            "workload": f"S_q={S1} S_kv=8192 64 heads x 128, causal"},
         "indexer_plus_topk": {"ms": t_all, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
