@@ -56,6 +56,32 @@ __device__ __forceinline__ int64_t kv_row(const FwdParams& p, int b, int idx) {
   return static_cast<int64_t>(b) * p.S_kv + idx;
 }
 
+// Packed pairs of fp32 (one instruction for two values) and the three-input maximum of sm_100.
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool kBF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (kBF16) {
@@ -516,20 +542,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         if (lane == 0) mbar_arrive(&s_free[sb]);  // the QK^T of tile g+2 may overwrite the buffer
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          sc[4 * j] = __float_as_uint(__uint_as_float(sc[4 * j]) + xr[j].x);
-          sc[4 * j + 1] = __float_as_uint(__uint_as_float(sc[4 * j + 1]) + xr[j].y);
-          sc[4 * j + 2] = __float_as_uint(__uint_as_float(sc[4 * j + 2]) + xr[j].z);
-          sc[4 * j + 3] = __float_as_uint(__uint_as_float(sc[4 * j + 3]) + xr[j].w);
+          const float2 a = fadd2(make_float2(__uint_as_float(sc[4 * j]), __uint_as_float(sc[4 * j + 1])), make_float2(xr[j].x, xr[j].y));
+          const float2 b = fadd2(make_float2(__uint_as_float(sc[4 * j + 2]), __uint_as_float(sc[4 * j + 3])), make_float2(xr[j].z, xr[j].w));
+          sc[4 * j] = __float_as_uint(a.x); sc[4 * j + 1] = __float_as_uint(a.y);
+          sc[4 * j + 2] = __float_as_uint(b.x); sc[4 * j + 3] = __float_as_uint(b.y);
         }
         const bool full = mask == 0xffffffffu;
         float mx;
         if (full) {
           float m4[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(sc[j]), __uint_as_float(sc[j + 4]));
+          for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1]));
 #pragma unroll
-          for (int j = 8; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(sc[j]));
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          for (int j = 4; j < 16; ++j) m4[j & 3] = fmax3(m4[j & 3], __uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1]));
+          mx = fmaxf(fmax3(m4[0], m4[1], m4[2]), m4[3]);
         } else {
           mx = -INFINITY;
 #pragma unroll
@@ -545,13 +571,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
         const float m_loc = mx * p.scale_log2;                      // -inf when no key of this half takes part
         const float neg_loc = (mx == -INFINITY) ? 0.f : -m_loc;
         float pe[32];
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg_loc, neg_loc);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float e = exp2f(fmaf(__uint_as_float(sc[j]), p.scale_log2, neg_loc));
-          if (!full) e = ((mask >> j) & 1u) ? e : 0.f;
-          pe[j] = e;
-          sum4[j & 3] += e;
+        for (int j = 0; j < 16; ++j) {
+          const float2 x = ffma2(make_float2(__uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1])), scale2, neg2);
+          float2 e = make_float2(exp2f(x.x), exp2f(x.y));
+          if (!full) {
+            e.x = ((mask >> (2 * j)) & 1u) ? e.x : 0.f;
+            e.y = ((mask >> (2 * j + 1)) & 1u) ? e.y : 0.f;
+          }
+          pe[2 * j] = e.x; pe[2 * j + 1] = e.y;
+          sum2[j & 1] = fadd2(sum2[j & 1], e);
         }
         named_bar_sync(1 + q4, 64);
         mx = fmaxf(slot[r], slot[128 + r]) * p.scale_log2;
@@ -580,10 +611,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           tc_fence_before();
         }
         const float corr = exp2f(m_loc - m_used);                  // <= 2^8; 0 for a half without keys
-        l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * corr;
+        l = l * factor + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) * corr;
         uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = pack2<kBF16>(pe[2 * j] * corr, pe[2 * j + 1] * corr);
+        for (int j = 0; j < 16; ++j) {
+          const float2 v = fmul2(make_float2(pe[2 * j], pe[2 * j + 1]), make_float2(corr, corr));
+          pk[j] = pack2<kBF16>(v.x, v.y);
+        }
         // P goes to shared memory as the K-major A operand of the PV MMAs: row r, keys 32 ch .. 32 ch + 31 = four 16-byte
         // units.  The buffer was last read by the PV MMAs of tile g-2.
         if (g >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((g >> 1) + 1) & 1, p.status));
