@@ -146,6 +146,20 @@ int dsa_sparse_mla_bwd(const void* q, const void* kv, const int32_t* indices, co
                        int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
                        const int32_t* block_table, int32_t block_size, int32_t max_blocks, void* stream);
 
+/* Sparse MLA backward on the tensor cores (D = 576, DV = 512, topk <= 8192): same arguments and results as
+ * dsa_sparse_mla_bwd, plus a caller-owned workspace (256-byte aligned).  The work is done in passes over consecutive
+ * queries; a pass keeps P and dS of its queries in the workspace (dsa_sparse_mla_bwd_tc_workspace_bytes(B, S, H, topk, n)
+ * bytes hold n queries per pass; n <= 0 or n >= B * S = all queries in one pass).  queries_per_pass <= 0 lets the
+ * library use as many as the workspace holds.  d_kv is accumulated into with fp32 atomics: zero it first.
+ * No counterpart in the reference (see dsa_sparse_mla_bwd). */
+size_t dsa_sparse_mla_bwd_tc_workspace_bytes(int32_t B, int32_t S, int32_t H, int32_t topk, int32_t queries_per_pass);
+int dsa_sparse_mla_bwd_tc(const void* q, const void* kv, const int32_t* indices, const void* out, const float* lse,
+                          const void* d_out, void* d_q, float* d_kv, int32_t B, int32_t S, int32_t S_kv, int32_t H,
+                          int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start, int32_t causal,
+                          int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                          const int32_t* block_table, int32_t block_size, int32_t max_blocks, void* workspace,
+                          size_t workspace_bytes, int32_t queries_per_pass, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -118,8 +118,8 @@ def test_decode_full_size():
 
 def test_backward_prefill_shape_properties():
     import tilelang_ascend_b200 as dsa
-    # the prefill shape in every dimension but the number of queries (the CUDA-core backward is correctness-first)
-    S, S_kv, H, topk = 256, 4096, 128, 2048
+    # the prefill shape of the backward configuration (tensor-core kernels)
+    S, S_kv, H, topk = 4096, 4096, 128, 2048
     g = torch.Generator(device=DEV).manual_seed(0)
     q = torch.randn((1, S, H, 576), generator=g, device=DEV).to(torch.bfloat16)
     kv = torch.randn((1, S_kv, 1, 576), generator=g, device=DEV).to(torch.bfloat16)
@@ -130,18 +130,27 @@ def test_backward_prefill_shape_properties():
     d_q, d_kv = dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=qs, causal=True)
     check_status()
     # dQ of a query depends on that query only: oracle on two sampled queries
-    for r in (0, 255):
+    for r in (0, 1000, S - 1):
         ref_dq, _ = orc.sparse_mla_bwd(q[:, r:r + 1].cpu(), kv.cpu(), idx[:, r:r + 1].cpu(), d_out[:, r:r + 1].cpu(), q_start_index_s=qs + r)
         assert_close_fp(d_q[:, r:r + 1].cpu(), ref_dq, f"dQ row {r}")
     # dKV is additive over queries: the two halves sum to the whole (fp32 atomics: order-dependent rounding only)
     halves = []
-    for sl, start in ((slice(0, 128), qs), (slice(128, 256), qs + 128)):
+    for sl, start in ((slice(0, S // 2), qs), (slice(S // 2, S), qs + S // 2)):
         _, dk = dsa.sparse_mla_bwd_raw(q[:, sl].contiguous(), kv, idx[:, sl].contiguous(), out[:, sl].contiguous(), lse[:, sl].contiguous(),
                                        d_out[:, sl].contiguous(), sm_scale=scale, q_start=start, causal=True)
         halves.append(dk)
-    torch.testing.assert_close(halves[0] + halves[1], d_kv, rtol=1e-3, atol=1e-2)
-    # and the oracle on a small query block pins its values
-    _, ref_dkv = orc.sparse_mla_bwd(q[:, :4].cpu(), kv.cpu(), idx[:, :4].cpu(), d_out[:, :4].cpu(), q_start_index_s=qs)
-    _, dk4 = dsa.sparse_mla_bwd_raw(q[:, :4].contiguous(), kv, idx[:, :4].contiguous(), out[:, :4].contiguous(), lse[:, :4].contiguous(),
-                                    d_out[:, :4].contiguous(), sm_scale=scale, q_start=qs, causal=True)
+    torch.testing.assert_close(halves[0] + halves[1], d_kv, rtol=1e-3, atol=5e-2)
+    # and the oracle on a small query block (the last four queries: 2048 keys each) pins its values
+    sl = slice(S - 4, S)
+    _, ref_dkv = orc.sparse_mla_bwd(q[:, sl].cpu(), kv.cpu(), idx[:, sl].cpu(), d_out[:, sl].cpu(), q_start_index_s=qs + S - 4)
+    _, dk4 = dsa.sparse_mla_bwd_raw(q[:, sl].contiguous(), kv, idx[:, sl].contiguous(), out[:, sl].contiguous(), lse[:, sl].contiguous(),
+                                    d_out[:, sl].contiguous(), sm_scale=scale, q_start=qs + S - 4, causal=True)
     assert_close_fp(dk4.cpu(), ref_dkv, "dKV of 4 queries", atol=1e-1)
+    # the tensor-core and the CUDA-core kernels agree on a block of queries
+    sl = slice(2000, 2064)
+    args = (q[:, sl].contiguous(), kv, idx[:, sl].contiguous(), out[:, sl].contiguous(), lse[:, sl].contiguous(), d_out[:, sl].contiguous())
+    dq_t, dk_t = dsa.sparse_mla_bwd_raw(*args, sm_scale=scale, q_start=qs + 2000, causal=True, impl="tensor_core")
+    dq_c, dk_c = dsa.sparse_mla_bwd_raw(*args, sm_scale=scale, q_start=qs + 2000, causal=True, impl="cuda_core")
+    check_status()
+    assert_close_fp(dq_t.float().cpu(), dq_c.float().cpu(), "dQ tensor-core vs CUDA-core")
+    assert_close_fp(dk_t.cpu(), dk_c.cpu(), "dKV tensor-core vs CUDA-core", atol=5e-2)

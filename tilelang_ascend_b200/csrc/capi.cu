@@ -22,6 +22,9 @@ bool indexer_tc_supported(const IndexerParams& p);
 int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_sparse_mla_bwd(const BwdParams& bp, bool bf16, cudaStream_t stream);
+bool sparse_mla_bwd_tc_supported(const FwdParams& p);
+size_t sparse_mla_bwd_tc_bytes_per_query(int H, int topk);
+int launch_sparse_mla_bwd_tc(const BwdParams& bp, bool bf16, void* workspace, size_t workspace_bytes, int queries_per_pass, cudaStream_t stream);
 }  // namespace dsa
 
 namespace {
@@ -251,6 +254,35 @@ int dsa_sparse_mla_bwd(const void* q, const void* kv, const int32_t* indices, co
   bp.d_out = d_out; bp.d_q = d_q; bp.d_kv = d_kv; bp.sm_scale = sm_scale;
   int err = dsa::launch_sparse_mla_bwd(bp, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("sparse_mla_bwd launch", err) : 0;
+}
+
+size_t dsa_sparse_mla_bwd_tc_workspace_bytes(int32_t B, int32_t S, int32_t H, int32_t topk, int32_t queries_per_pass) {
+  if (B <= 0 || S <= 0 || H <= 0 || topk <= 0) return 0;
+  size_t nq = static_cast<size_t>(B) * S;
+  if (queries_per_pass > 0 && static_cast<size_t>(queries_per_pass) < nq) nq = queries_per_pass;
+  return nq * dsa::sparse_mla_bwd_tc_bytes_per_query(H, topk);
+}
+
+int dsa_sparse_mla_bwd_tc(const void* q, const void* kv, const int32_t* indices, const void* out, const float* lse, const void* d_out,
+                          void* d_q, float* d_kv, int32_t B, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk,
+                          float sm_scale, int32_t q_start, int32_t causal, int32_t dtype, const int32_t* q_start_b,
+                          const int32_t* kv_len_b, const int32_t* q_len_b, const int32_t* block_table, int32_t block_size,
+                          int32_t max_blocks, void* workspace, size_t workspace_bytes, int32_t queries_per_pass, void* stream) {
+  if (!lse || !d_out || !d_q || !d_kv) return fail("null tensor pointer");
+  dsa::BwdParams bp;
+  if (fill_fwd_params(&bp.f, q, kv, indices, const_cast<void*>(out), const_cast<float*>(lse), B, S, S_kv, H, D, DV, topk, sm_scale,
+                      q_start, causal, dtype, q_start_b, kv_len_b, q_len_b, block_table, block_size, max_blocks))
+    return 1;
+  if (!dsa::sparse_mla_bwd_tc_supported(bp.f)) return fail("the tensor-core backward needs D = 576, DV = 512 and topk <= 8192");
+  const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv) | reinterpret_cast<uintptr_t>(out) |
+                        reinterpret_cast<uintptr_t>(d_out) | reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_kv);
+  if (all & 15u) return fail("q, kv, out, d_out, d_q and d_kv must be 16-byte aligned");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return fail("workspace must be non-null and 256-byte aligned");
+  if (workspace_bytes < dsa::sparse_mla_bwd_tc_bytes_per_query(H, topk))
+    return fail("workspace too small: it must hold at least one query (see dsa_sparse_mla_bwd_tc_workspace_bytes)");
+  bp.d_out = d_out; bp.d_q = d_q; bp.d_kv = d_kv; bp.sm_scale = sm_scale;
+  int err = dsa::launch_sparse_mla_bwd_tc(bp, dtype == DSA_DTYPE_BF16, workspace, workspace_bytes, queries_per_pass, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sparse_mla_bwd_tc launch", err) : 0;
 }
 
 }  // extern "C"

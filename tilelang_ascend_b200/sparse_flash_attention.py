@@ -76,19 +76,44 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
     return out, lse
 
 
-def sparse_mla_bwd_raw(q, kv, indices, out, lse, d_out, *, sm_scale: float, q_start: int, causal: bool):
-    """dQ (input dtype) and dKV (fp32) of the forward; no reference counterpart (see the C header)."""
+# queries whose P / dS tiles one pass of the tensor-core backward keeps in its workspace (1 MiB each at H = 128, topk = 2048)
+BWD_TC_QUERIES_PER_PASS = 296
+
+
+def sparse_mla_bwd_raw(q, kv, indices, out, lse, d_out, *, sm_scale: float, q_start: int, causal: bool, impl: str = "auto",
+                       queries_per_pass: int | None = None):
+    """dQ (input dtype) and dKV (fp32) of the forward; no reference counterpart (see the C header).
+
+    ``impl``: "auto" = the tensor-core kernels when D = 576 / DV = 512 / topk <= 8192, else the CUDA-core kernel;
+    "tensor_core" / "cuda_core" force one.  The tensor-core path works in passes of ``queries_per_pass`` queries and
+    allocates its workspace (P and dS of one pass) here, as the reference's adapter does for its kernels' workspaces."""
     dev = check_inputs([q, kv, indices, out, lse, d_out], [None, q.dtype, torch.int32, q.dtype, torch.float32, q.dtype],
                        ["q", "kv", "indices", "out", "lse", "d_out"])
     B, S, H, D = q.shape
     S_kv, dv, topk = kv.shape[1], out.shape[3], indices.shape[3]
+    if impl not in ("auto", "tensor_core", "cuda_core"):
+        raise ValueError(f"unknown impl {impl!r}")
+    tc_ok = D == 576 and dv == 512 and topk <= 8192
+    if impl == "tensor_core" and not tc_ok:
+        raise ValueError("the tensor-core backward needs D = 576, DV = 512 and topk <= 8192")
+    use_tc = tc_ok and impl != "cuda_core"
     d_q = torch.empty_like(q)
     d_kv = torch.zeros(kv.shape, dtype=torch.float32, device=dev)
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().dsa_sparse_mla_bwd(
-            ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), ptr(d_out), ptr(d_q), ptr(d_kv), B, S, S_kv, H, D, dv, topk,
-            float(sm_scale), int(q_start), 1 if causal else 0, dtype_code(q.dtype), None, None, None, None, 0, 0,
-            current_stream(dev)))
+        if use_tc:
+            qpp = min(B * S, int(queries_per_pass) if queries_per_pass else BWD_TC_QUERIES_PER_PASS)
+            nbytes = int(lib.dsa_sparse_mla_bwd_tc_workspace_bytes(B, S, H, topk, qpp))
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            _lib.check(lib.dsa_sparse_mla_bwd_tc(
+                ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), ptr(d_out), ptr(d_q), ptr(d_kv), B, S, S_kv, H, D, dv, topk,
+                float(sm_scale), int(q_start), 1 if causal else 0, dtype_code(q.dtype), None, None, None, None, 0, 0,
+                ptr(workspace), nbytes, qpp, current_stream(dev)))
+        else:
+            _lib.check(lib.dsa_sparse_mla_bwd(
+                ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), ptr(d_out), ptr(d_q), ptr(d_kv), B, S, S_kv, H, D, dv, topk,
+                float(sm_scale), int(q_start), 1 if causal else 0, dtype_code(q.dtype), None, None, None, None, 0, 0,
+                current_stream(dev)))
     return d_q, d_kv
 
 
