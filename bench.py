@@ -183,14 +183,14 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     scale, q0 = WORKLOAD["D"] ** -0.5, WORKLOAD["S_kv"] - S_b
     out, lse = dsa.sparse_mla_fwd_raw(q, kv, idx, sm_scale=scale, q_start=q0, causal=True, dv=WORKLOAD["DV"], return_lse=True)
     d_out = torch.randn(out.shape, generator=g, device=dev).to(torch.bfloat16)
-    t_bwd = _time_ms(lambda: dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=q0, causal=True), reps=2, warm=1)
+    t_bwd = _time_ms(lambda: dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=q0, causal=True), reps=10, warm=3)
     bwd_pairs = int((idx >= 0).sum().item())
     bwd_tflops = bwd_pairs * WORKLOAD["H"] * 5504 / (t_bwd * 1e-3) / 1e12
     del q, kv, idx, out, lse, d_out
     assert dsa.kernel_status() == 0
     return {
         "backward": {"ms": t_bwd, "tokens_per_s": S_b / (t_bwd * 1e-3), "tflops": bwd_tflops, "frac_of_bf16_peak": bwd_tflops / peaks["bf16_tflops"],
-                     "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (CUDA-core kernel)"},
+                     "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (tensor-core kernels, workspace and dKV zeroing inside the timed call)"},
         "pipeline": {"ms": t_pipe, "tokens_per_s": Sp / (t_pipe * 1e-3), "tflops": pipe_tflops, "frac_of_bf16_peak": pipe_tflops / peaks["bf16_tflops"],
                      "workload": f"indexer (64 x 128) -> top-2048 -> sparse MLA forward on the selected indices, S_q={Sp}, S_kv={S_kvp}, one stream"},
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
