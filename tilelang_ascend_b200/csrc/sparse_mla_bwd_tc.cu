@@ -293,6 +293,12 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
       if (mask == 0ull) continue;
       const int sb = g & 1;
       uint32_t sc[64];
+      const uint8_t* p_tile = ps.p_ws + (tile0 + tile) * kTileBytes;
+      uint4 pv[8];  // MODE 1: this row's P values of the tile, requested before the wait so that their latency hides behind it
+      if (MODE == 1) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) pv[u] = *reinterpret_cast<const uint4*>(p_tile + sw128_offset(r, u));
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
       tmem_ld32(tS + sb * kBK + lane_base, sc);
@@ -302,7 +308,6 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[sb]);
       uint8_t* out_tile = (MODE == 0 ? ps.p_ws : ps.ds_ws) + (tile0 + tile) * kTileBytes;
-      const uint8_t* p_tile = ps.p_ws + (tile0 + tile) * kTileBytes;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {  // 16-byte unit u = keys 8u .. 8u + 7 of this row
         const uint32_t off = sw128_offset(r, u);
@@ -318,8 +323,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
             w[j] = pack2<kBF16>(e0, e1);
           }
         } else {
-          const uint4 pv = *reinterpret_cast<const uint4*>(p_tile + off);
-          const uint32_t pw4[4] = {pv.x, pv.y, pv.z, pv.w};
+          const uint32_t pw4[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int k0 = 8 * u + 2 * j;
@@ -499,7 +503,9 @@ constexpr uint32_t kOffQ = kStages * kPairBytes;                // 98304
 constexpr uint32_t kOffDO = kOffQ + kOperandBytes;              // 147456
 constexpr uint32_t kOffBar = kOffDO + kOperandBytes;            // 196608
 constexpr uint32_t kOffMask = kOffBar + 128;
-constexpr uint32_t kSmemBytes = kOffMask + kMaxTiles * 8 + 1024;
+constexpr uint32_t kOffXpose = kOffMask + kMaxTiles * 8;        // per epilogue warp: [32 keys x 32 dims] fp32 + 32 row numbers
+constexpr uint32_t kXposeBytes = 32 * 128 + 128;
+constexpr uint32_t kSmemBytes = kOffXpose + 4 * kXposeBytes + 1024;
 constexpr uint32_t kTmemCols = 512;                             // two accumulators of 192 columns
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 }  // namespace dkv
@@ -627,6 +633,9 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
       mbar_arrive(b_ready);
     }
     const int32_t* idx_row = p.indices + static_cast<int64_t>(bt) * p.topk;
+    uint8_t* xbuf_ptr = smem + kOffXpose + warp * kXposeBytes;
+    const uint32_t xbuf = smem_u32(xbuf_ptr);
+    int* xrows = reinterpret_cast<int*>(xbuf_ptr + 32 * 128);
     int g = 0;
     for (int tp = 0; run && ok && tp < npairs; ++tp) {
       const unsigned long long m0 = smask[2 * tp], m1 = smask[2 * tp + 1];
@@ -634,7 +643,9 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
       const int ab = g & 1;
       const bool valid = ((r < 64 ? m0 >> r : m1 >> (r - 64)) & 1ull) != 0ull;
       const int idx = valid ? __ldg(idx_row + tp * 128 + r) : 0;
-      float* dst = bp.d_kv + (valid ? kv_row_of(p, b, idx) : 0) * kD + part * kDimsPerCta;
+      // row number inside dKV of this thread's key (-1: takes no part), shared with the warp for the transposed atomics
+      __syncwarp();
+      xrows[lane] = valid ? static_cast<int>(kv_row_of(p, b, idx)) : -1;
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[ab], (g >> 1) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
@@ -642,11 +653,21 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
         uint32_t v[32];
         tmem_ld32(tAcc + ab * kDimsPerCta + lane_base + cc * 32, v);
         tmem_wait_ld();
-        if (valid) {
+        // The warp holds [32 keys x 32 dims] with one key per lane.  Through shared memory (16-byte units XOR-swizzled by the
+        // row, conflict-free both ways) it is turned so that 8 consecutive lanes cover the 128 contiguous bytes of ONE key:
+        // an atomic instruction then touches 4 full lines instead of 32 half-used sectors.
+        __syncwarp();
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            atomicAdd(reinterpret_cast<float4*>(dst + cc * 32) + q4,
-                      make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]), __uint_as_float(v[4 * q4 + 3])));
+        for (int j = 0; j < 8; ++j)
+          st_shared_v4(xbuf + lane * 128 + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int key = i * 4 + (lane >> 3);
+          const int row = xrows[key];
+          const float4 val = *reinterpret_cast<const float4*>(xbuf_ptr + key * 128 + (((lane & 7) ^ (key & 7)) << 4));
+          if (row >= 0)
+            atomicAdd(reinterpret_cast<float4*>(bp.d_kv + static_cast<int64_t>(row) * kD + part * kDimsPerCta + cc * 32) + (lane & 7), val);
         }
       }
       tc_fence_before();
