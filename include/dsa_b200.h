@@ -160,6 +160,16 @@ int dsa_sparse_mla_bwd_tc(const void* q, const void* kv, const int32_t* indices,
                           const int32_t* block_table, int32_t block_size, int32_t max_blocks, void* workspace,
                           size_t workspace_bytes, int32_t queries_per_pass, void* stream);
 
+/* Merges one or two partial attention results over disjoint key sets with a per-head sink logit:
+ * lse = log(exp(lse_a) + exp(lse_b) + exp(sinks[h])), out = exp(lse_a - lse) out_a + exp(lse_b - lse) out_b.
+ * out_a / out_b / out [rows, DV] (dtype), lse_a / lse_b / lse [rows] fp32 with rows = tokens * H (head fastest), sinks [H]
+ * fp32 or NULL (no sink); out_b / lse_b may be NULL (one partial); lse may be NULL; out may alias out_a.
+ * Together with two dsa_sparse_mla_fwd calls (sliding window of the original cache; selected compressed tokens) this replaces
+ * the kernel of sparse_flash_mla (examples/deepseek_v4/sparse_flash_mla/sparse_flash_mla_kernel.py; sink and LSE handling
+ * :1053-1064, golden sparse_flash_mla_golden.py:121-153). */
+int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, const float* lse_b, const float* sinks,
+                     void* out, float* lse, int64_t rows, int32_t H, int32_t DV, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -268,6 +268,65 @@ def mla_decode(q: torch.Tensor, q_pe: torch.Tensor, kv: torch.Tensor, k_pe: torc
 
 
 # ---------------------------------------------------------------------------
+# DeepSeek-V4 sparse_flash_mla: sliding window + compressed tokens + sink
+# ---------------------------------------------------------------------------
+def sparse_flash_mla_v4(
+    q: torch.Tensor,                      # [B, S, N1, D]
+    ori_k: torch.Tensor,                  # [B, S_kv, D]   original cache (K = V, one KV head)
+    sinks: torch.Tensor,                  # [N1]
+    *,
+    act_q_lens,
+    act_kv_lens,
+    softmax_scale: float,
+    cmp_k: Optional[torch.Tensor] = None,             # [B, S_cmp, D] compressed cache
+    cmp_sparse_indices: Optional[torch.Tensor] = None,  # [B, S, K] int, -1 ends a list; None = all tokens below the threshold
+    cmp_ratio: Optional[int] = None,
+    ori_win_left: int = 127,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """out [B,S,N1,D] (input dtype) and lse [B,S,N1] fp32 (natural log, sink included); rows s >= act_q stay zero.
+
+    Follows sparse_flash_mla_golden_bnsd
+    (examples/deepseek_v4/sparse_flash_mla/sparse_flash_mla_golden.py:56-153): token s of sequence b sits at
+    p = act_kv - act_q + s (:97); window keys [max(p - win, 0), p] (:100-102); compressed keys: the listed tokens, the
+    list cut at min(K, threshold) entries and at the first -1, entries >= min(threshold, floor(act_kv / ratio)) skipped,
+    threshold = floor((p + 1) / ratio) (_gather_cmp_kv_tokens :16-53; dense variant :116-118); the softmax starts from
+    row_max = sink, row_sum = 1 (:121-122), i.e. the sink adds exp(sink) to the denominator and nothing to the
+    numerator; lse = max + log(sum) (:149).  The golden rounds P to the input dtype before P.V (:143); this restatement
+    keeps fp32 (difference far below the comparison tolerance)."""
+    B, S, N1, D = q.shape
+    out = torch.zeros((B, S, N1, D), dtype=torch.float32)
+    lse = torch.zeros((B, S, N1), dtype=torch.float32)
+    sk = sinks.to(torch.float32)
+    for b in range(B):
+        aq, akv = int(act_q_lens[b]), int(act_kv_lens[b])
+        for s in range(aq):
+            p = akv - aq + s
+            keys = [ori_k[b, max(p - ori_win_left, 0): p + 1].to(torch.float32)]
+            if cmp_k is not None:
+                threshold = (p + 1) // cmp_ratio
+                if cmp_sparse_indices is None:
+                    keys.append(cmp_k[b, : max(threshold, 0)].to(torch.float32))
+                else:
+                    cmp_len = akv // cmp_ratio
+                    picked = []
+                    for i in range(min(cmp_sparse_indices.shape[-1], max(threshold, 0))):
+                        t = int(cmp_sparse_indices[b, s, i])
+                        if t == -1:
+                            break
+                        if 0 <= t < min(threshold, cmp_len):
+                            picked.append(t)
+                    keys.append(cmp_k[b, picked].to(torch.float32) if picked else cmp_k.new_zeros((0, D), dtype=torch.float32))
+            kk = torch.cat(keys, dim=0)                                     # [n, D]
+            sc = q[b, s].to(torch.float32) @ kk.T * softmax_scale           # [N1, n]
+            m = torch.maximum(sc.amax(dim=1), sk) if kk.shape[0] else sk.clone()
+            e = torch.exp(sc - m[:, None])
+            den = e.sum(dim=1) + torch.exp(sk - m)
+            out[b, s] = (e @ kk) / den[:, None]
+            lse[b, s] = m + torch.log(den)
+    return out.to(q.dtype), lse
+
+
+# ---------------------------------------------------------------------------
 # seeded synthetic inputs of the benchmark configurations
 # ---------------------------------------------------------------------------
 def make_sparse_mla_inputs(B: int, S: int, S_kv: int, H: int, topk: int, *, D: int = 576, seed: int = 0,

@@ -131,6 +131,29 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "lse_window.npz"), q=bits(qb), k=bits(kb), win=np.int64(win),
                         out=bits(o), lse=lse.numpy())
 
+    # ---- V4 sparse_flash_mla: window + selected / all compressed tokens + sinks ------------------
+    g = torch.Generator().manual_seed(9)
+    B, N1, S1, S2, D, K, ratio, win = 2, 8, 6, 41, 64, 8, 4, 7
+    qb = torch.randn((B, N1, S1, D), generator=g).to(torch.bfloat16)
+    kb = torch.randn((B, 1, S2, D), generator=g).to(torch.bfloat16)
+    cb = torch.randn((B, 1, S2 // ratio, D), generator=g).to(torch.bfloat16)
+    sinks = torch.randn((N1,), generator=g)
+    act_q, act_kv = [6, 4], [41, 30]
+    rng = np.random.default_rng(4)
+    ci = np.full((B, S1, 1, K), -1, dtype=np.int32)
+    for b in range(B):
+        for s_ in range(act_q[b]):
+            n = rng.integers(0, K + 1)
+            ci[b, s_, 0, :n] = rng.integers(0, S2 // ratio, size=n)   # includes entries at / above the threshold and repeats
+    o3, l3 = v4(qb, kb, sinks, act_q_lens=act_q, act_kv_lens=act_kv, softmax_scale=D ** -0.5, cmp_k_bnsd=cb,
+                cmp_sparse_indices=torch.from_numpy(ci), cmp_ratio=ratio, ori_win_left=win, return_lse=True)
+    o2, l2 = v4(qb, kb, sinks, act_q_lens=act_q, act_kv_lens=act_kv, softmax_scale=D ** -0.5, cmp_k_bnsd=cb,
+                cmp_ratio=ratio, ori_win_left=win, return_lse=True)
+    o1, l1 = v4(qb, kb, sinks, act_q_lens=act_q, act_kv_lens=act_kv, softmax_scale=D ** -0.5, ori_win_left=win, return_lse=True)
+    np.savez_compressed(os.path.join(HERE, "sparse_flash_mla_v4.npz"), q=bits(qb), k=bits(kb), c=bits(cb), sinks=sinks.numpy(),
+                        act_q=np.array(act_q), act_kv=np.array(act_kv), ci=ci, ratio=np.int64(ratio), win=np.int64(win),
+                        out3=bits(o3), lse3=l3.numpy(), out2=bits(o2), lse2=l2.numpy(), out1=bits(o1), lse1=l1.numpy())
+
     # ---- lightning indexer, production golden ---------------------------------------------------
     env = load_functions(os.path.join(ref, "examples/deepseek_v4/lightning_indexer.py"),
                          ["_NEG_INF", "cpu_lightning_indexer"])

@@ -56,6 +56,22 @@ def test_lse_definition_matches_reference(golden):
     torch.testing.assert_close(out, ref, rtol=2e-2, atol=2e-2)
 
 
+def test_sparse_flash_mla_v4_matches_reference_golden(golden):
+    """Window + compressed tokens + sinks: the three scenarios of the reference's V4 golden (selected tokens, all tokens
+    below the threshold, window only)."""
+    g = golden("sparse_flash_mla_v4.npz")
+    q, k, c = from_bits(g["q"]), from_bits(g["k"]), from_bits(g["c"])      # [B,N1,S1,D], [B,1,S2,D], [B,1,Sc,D]
+    sinks = torch.from_numpy(g["sinks"])
+    common = dict(act_q_lens=g["act_q"], act_kv_lens=g["act_kv"], softmax_scale=q.shape[-1] ** -0.5, ori_win_left=int(g["win"]))
+    qs, ks, cs = q.permute(0, 2, 1, 3).contiguous(), k[:, 0], c[:, 0]
+    ci = torch.from_numpy(g["ci"])[:, :, 0, :]
+    for tag, kw in (("3", dict(cmp_k=cs, cmp_sparse_indices=ci, cmp_ratio=int(g["ratio"]))),
+                    ("2", dict(cmp_k=cs, cmp_ratio=int(g["ratio"]))), ("1", {})):
+        out, lse = orc.sparse_flash_mla_v4(qs, ks, sinks, **common, **kw)
+        np.testing.assert_allclose(lse.permute(0, 2, 1).numpy(), g["lse" + tag], rtol=1e-5, atol=1e-5, err_msg=tag)
+        torch.testing.assert_close(out.float().permute(0, 2, 1, 3), from_bits(g["out" + tag]).float(), rtol=2e-2, atol=2e-2, msg=tag)
+
+
 def test_lightning_indexer_matches_reference_golden(golden):
     g = golden("lightning_indexer.npz")
     for tag in ("causal", "full", "ties"):

@@ -8,12 +8,13 @@ from .lightning_indexer import indexer, indexer_scores_raw, lightning_indexer, l
 from .sharding import shard_batch, shard_queries, shard_range, all_reduce_key_gradient, sparse_mla_bwd_sharded
 from .sparse_flash_attention import (sparse_attention_fwd, sparse_attn_tilelang, sparse_mla, sparse_mla_bwd_raw,
                                      sparse_mla_fwd_raw)
+from .sparse_flash_mla import sink_combine_raw, sparse_flash_mla
 from .topk_selector import simple_topk_selector, topk_select_raw
 
 kernel_status = _lib.kernel_status
 
 __all__ = [
     "indexer", "lightning_indexer", "simple_topk_selector", "sparse_attention_fwd", "sparse_attn_tilelang", "mla_decode",
-    "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
+    "sparse_flash_mla", "sink_combine_raw", "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
     "topk_select_raw", "HostPipelinedForward", "shard_range", "shard_queries", "shard_batch", "all_reduce_key_gradient", "sparse_mla_bwd_sharded", "kernel_status",
 ]

@@ -22,6 +22,8 @@ bool indexer_tc_supported(const IndexerParams& p);
 int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_sparse_mla_bwd(const BwdParams& bp, bool bf16, cudaStream_t stream);
+int launch_sink_combine(const void* out_a, const float* lse_a, const void* out_b, const float* lse_b, const float* sinks, void* out, float* lse,
+                        int64_t rows, int H, int DV, bool bf16, cudaStream_t stream);
 bool sparse_mla_bwd_tc_supported(const FwdParams& p);
 size_t sparse_mla_bwd_tc_bytes_per_query(int H, int topk);
 int launch_sparse_mla_bwd_tc(const BwdParams& bp, bool bf16, void* workspace, size_t workspace_bytes, int queries_per_pass, cudaStream_t stream);
@@ -283,6 +285,16 @@ int dsa_sparse_mla_bwd_tc(const void* q, const void* kv, const int32_t* indices,
   bp.d_out = d_out; bp.d_q = d_q; bp.d_kv = d_kv; bp.sm_scale = sm_scale;
   int err = dsa::launch_sparse_mla_bwd_tc(bp, dtype == DSA_DTYPE_BF16, workspace, workspace_bytes, queries_per_pass, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("sparse_mla_bwd_tc launch", err) : 0;
+}
+
+int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, const float* lse_b, const float* sinks, void* out, float* lse,
+                     int64_t rows, int32_t H, int32_t DV, int32_t dtype, void* stream) {
+  if (!out_a || !lse_a || !out) return fail("null tensor pointer");
+  if ((out_b == nullptr) != (lse_b == nullptr)) return fail("out_b and lse_b must both be given or both be null");
+  if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
+  if (rows <= 0 || H <= 0 || DV <= 0 || rows % H != 0) return fail("rows must be a positive multiple of H; DV positive");
+  int err = dsa::launch_sink_combine(out_a, lse_a, out_b, lse_b, sinks, out, lse, rows, H, DV, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sink_combine launch", err) : 0;
 }
 
 }  // extern "C"

@@ -503,16 +503,19 @@ constexpr uint32_t kOffQ = kStages * kPairBytes;                // 98304
 constexpr uint32_t kOffDO = kOffQ + kOperandBytes;              // 147456
 constexpr uint32_t kOffBar = kOffDO + kOperandBytes;            // 196608
 constexpr uint32_t kOffMask = kOffBar + 128;
-constexpr uint32_t kOffXpose = kOffMask + kMaxTiles * 8;        // per epilogue warp: [32 keys x 32 dims] fp32 + 32 row numbers
-constexpr uint32_t kXposeBytes = 32 * 128 + 128;
-constexpr uint32_t kSmemBytes = kOffXpose + 4 * kXposeBytes + 1024;
+constexpr uint32_t kOffXpose = kOffMask + kMaxTiles * 8;        // per epilogue warp: [32 keys x 16 dims] fp32 + 32 row numbers
+constexpr uint32_t kXposeBytes = 32 * 64 + 128;
+constexpr int kEpilogueWarps = 8;                               // warp w: tensor-memory lanes 32 (w & 3) .., columns 96 (w >> 2) .. + 95
+constexpr int kLoadWarp = 8, kIssueWarp = 9;
+constexpr int kThreadsDkv = 320;
+constexpr uint32_t kSmemBytes = kOffXpose + kEpilogueWarps * kXposeBytes + 1024;
 constexpr uint32_t kTmemCols = 512;                             // two accumulators of 192 columns
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 }  // namespace dkv
 }  // namespace bwdtc
 
 template <bool kBF16>
-__global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(const BwdParams bp, const bwdtc::Pass ps) {
+__global__ void __launch_bounds__(bwdtc::dkv::kThreadsDkv, 1) sparse_mla_bwd_dkv_kernel(const BwdParams bp, const bwdtc::Pass ps) {
   using namespace bwdtc;
   using namespace bwdtc::dkv;
   const FwdParams& p = bp.f;
@@ -524,7 +527,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
   uint64_t* full = bars;           // [3] count 1 + 32768 transaction bytes: a dS or P pair of tiles landed
   uint64_t* empty = bars + 3;      // [3] count 1: commit after the MMAs that read the stage
   uint64_t* acc_full = bars + 6;   // [2] count 1: commit after the MMAs of a key pair
-  uint64_t* acc_free = bars + 8;   // [2] count 4: the epilogue warps have read the accumulator
+  uint64_t* acc_free = bars + 8;   // [2] count 8: the epilogue warps have read the accumulator
   uint64_t* b_ready = bars + 10;   // count 128: Q / dO columns are in shared memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   unsigned long long* smask = reinterpret_cast<unsigned long long*>(smem + kOffMask);
@@ -541,12 +544,12 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], kEpilogueWarps); }
     mbar_init(b_ready, 128);
     mbar_init_fence();
   }
-  for (int i = tid; i < ps.ntiles2; i += kThreads) smask[i] = i < ps.ntiles ? ps.masks[static_cast<int64_t>(ql) * ps.ntiles2 + i] : 0ull;
-  if (warp == kMmaWarp) {
+  for (int i = tid; i < ps.ntiles2; i += kThreadsDkv) smask[i] = i < ps.ntiles ? ps.masks[static_cast<int64_t>(ql) * ps.ntiles2 + i] : 0ull;
+  if (warp == kIssueWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -557,7 +560,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
   const bool run = *reinterpret_cast<volatile int*>(p.status) == kStatusOk;
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == kLoadWarp) {
     // ================================ tile loads ====================================================
     // per key pair two loads into consecutive slots of the ring: dS (tiles 2 tp, 2 tp + 1), then P
     if (lane == 0 && run) {
@@ -573,7 +576,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
         }
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kIssueWarp) {
     // ================================ MMA issuer ====================================================
     // acc[128 keys x 192 dims] = dS^T[128 keys x 128 heads] . Q[128 heads x 192 dims] + P^T . dO[128 heads x its dims]:
     // both operands MN-major (contraction over heads = rows of the shared-memory images), 16 heads = 2048 bytes per step.
@@ -607,13 +610,15 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
         ++g;
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < kEpilogueWarps) {
     // ================================ operand columns + epilogue ====================================
-    // thread r first copies head row r's 192 Q dims and its dO dims into the [128 heads x 128 B] chunk images, then
-    // owns key r of every pair: tensor-memory lane r holds that key's 192 gradient values.
-    const int r = warp * 32 + lane, h = h0 + r;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    {
+    // thread r of the first four warps copies head row r's 192 Q dims and its dO dims into the [128 heads x 128 B] chunk
+    // images.  Then thread (r, half) owns key r of every pair: tensor-memory lane r holds that key's 192 gradient values,
+    // of which this thread takes columns [96 half, 96 half + 96).
+    const int q4 = warp & 3, half = warp >> 2;
+    const int r = q4 * 32 + lane, h = h0 + r;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    if (half == 0) {
       const bool row_ok = h < p.H;
       const int64_t hrow = static_cast<int64_t>(bt) * p.H + (row_ok ? h : 0);
       const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + hrow * (kD * 2) + part * (kDimsPerCta * 2);
@@ -635,7 +640,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
     const int32_t* idx_row = p.indices + static_cast<int64_t>(bt) * p.topk;
     uint8_t* xbuf_ptr = smem + kOffXpose + warp * kXposeBytes;
     const uint32_t xbuf = smem_u32(xbuf_ptr);
-    int* xrows = reinterpret_cast<int*>(xbuf_ptr + 32 * 128);
+    int* xrows = reinterpret_cast<int*>(xbuf_ptr + 32 * 64);
     int g = 0;
     for (int tp = 0; run && ok && tp < npairs; ++tp) {
       const unsigned long long m0 = smask[2 * tp], m1 = smask[2 * tp + 1];
@@ -649,26 +654,30 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[ab], (g >> 1) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int cc = 0; cc < kDimsPerCta / 32; ++cc) {
-        uint32_t v[32];
-        tmem_ld32(tAcc + ab * kDimsPerCta + lane_base + cc * 32, v);
+      for (int cc = 6 * half; cc < 6 * half + 6; ++cc) {  // chunks of 16 columns
+        uint32_t v[16];
+        tmem_ld16(tAcc + ab * kDimsPerCta + lane_base + cc * 16, v);
         tmem_wait_ld();
-        // The warp holds [32 keys x 32 dims] with one key per lane.  Through shared memory (16-byte units XOR-swizzled by the
-        // row, conflict-free both ways) it is turned so that 8 consecutive lanes cover the 128 contiguous bytes of ONE key:
-        // an atomic instruction then touches 4 full lines instead of 32 half-used sectors.
+        // The warp holds [32 keys x 16 dims] with one key per lane.  Through shared memory (16-byte units XOR-swizzled by the
+        // row, conflict-free both ways) it is turned so that 4 consecutive lanes cover the 64 contiguous bytes of ONE key:
+        // an atomic instruction then touches 16 full sectors instead of 32 half-used ones.
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          st_shared_v4(xbuf + lane * 128 + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        for (int j = 0; j < 4; ++j)
+          st_shared_v4(xbuf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         __syncwarp();
+        float4 val[4];
+        int rows4[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int key = i * 4 + (lane >> 3);
-          const int row = xrows[key];
-          const float4 val = *reinterpret_cast<const float4*>(xbuf_ptr + key * 128 + (((lane & 7) ^ (key & 7)) << 4));
-          if (row >= 0)
-            atomicAdd(reinterpret_cast<float4*>(bp.d_kv + static_cast<int64_t>(row) * kD + part * kDimsPerCta + cc * 32) + (lane & 7), val);
+        for (int i = 0; i < 4; ++i) {
+          const int key = i * 8 + (lane >> 2);
+          rows4[i] = xrows[key];
+          val[i] = *reinterpret_cast<const float4*>(xbuf_ptr + key * 64 + (((lane & 3) ^ ((key >> 1) & 3)) << 4));
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (rows4[i] >= 0)
+            atomicAdd(reinterpret_cast<float4*>(bp.d_kv + static_cast<int64_t>(rows4[i]) * kD + part * kDimsPerCta + cc * 16) + (lane & 3), val[i]);
       }
       tc_fence_before();
       __syncwarp();
@@ -678,7 +687,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_dkv_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) tmem_dealloc(tAcc, kTmemCols);
+  if (warp == kIssueWarp) tmem_dealloc(tAcc, kTmemCols);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -721,7 +730,7 @@ int run_bwd_tc_passes(const BwdParams& bp, bwdtc::Pass ps, int nq_max, cudaStrea
     k_p<<<items, kThreads, ScoresCfg<0>::kSmemBytes, stream>>>(bp, ps);
     k_ds<<<items, kThreads, ScoresCfg<1>::kSmemBytes, stream>>>(bp, ps);
     k_dq<<<items * kDimSplits, kThreads, dq::kSmemBytes, stream>>>(bp, ps);
-    k_dkv<<<items * kDimSplits, kThreads, dkv::kSmemBytes, stream>>>(bp, ps);
+    k_dkv<<<items * kDimSplits, dkv::kThreadsDkv, dkv::kSmemBytes, stream>>>(bp, ps);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   return 0;
