@@ -653,35 +653,41 @@ __global__ void __launch_bounds__(bwdtc::dkv::kThreadsDkv, 1) sparse_mla_bwd_dkv
       xrows[lane] = valid ? static_cast<int>(kv_row_of(p, b, idx)) : -1;
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[ab], (g >> 1) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int cc = 6 * half; cc < 6 * half + 6; ++cc) {  // chunks of 16 columns
-        uint32_t v[16];
-        tmem_ld16(tAcc + ab * kDimsPerCta + lane_base + cc * 16, v);
-        tmem_wait_ld();
+      // this thread's 96 columns leave tensor memory at once, so that the accumulator goes back to the MMA issuer before
+      // the (slow) atomics start
+      uint32_t v[96];
+#pragma unroll
+      for (int c3 = 0; c3 < 3; ++c3) tmem_ld32(tAcc + ab * kDimsPerCta + lane_base + half * 96 + c3 * 32, v + 32 * c3);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_free[ab]);
+      int rows4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rows4[i] = xrows[i * 8 + (lane >> 2)];
+#pragma unroll
+      for (int cc = 0; cc < 6; ++cc) {  // chunks of 16 columns
         // The warp holds [32 keys x 16 dims] with one key per lane.  Through shared memory (16-byte units XOR-swizzled by the
         // row, conflict-free both ways) it is turned so that 4 consecutive lanes cover the 64 contiguous bytes of ONE key:
         // an atomic instruction then touches 16 full sectors instead of 32 half-used ones.
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          st_shared_v4(xbuf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          st_shared_v4(xbuf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), v[16 * cc + 4 * j], v[16 * cc + 4 * j + 1], v[16 * cc + 4 * j + 2],
+                       v[16 * cc + 4 * j + 3]);
         __syncwarp();
         float4 val[4];
-        int rows4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int key = i * 8 + (lane >> 2);
-          rows4[i] = xrows[key];
           val[i] = *reinterpret_cast<const float4*>(xbuf_ptr + key * 64 + (((lane & 3) ^ ((key >> 1) & 3)) << 4));
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           if (rows4[i] >= 0)
-            atomicAdd(reinterpret_cast<float4*>(bp.d_kv + static_cast<int64_t>(rows4[i]) * kD + part * kDimsPerCta + cc * 16) + (lane & 3), val[i]);
+            atomicAdd(reinterpret_cast<float4*>(bp.d_kv + static_cast<int64_t>(rows4[i]) * kD + part * kDimsPerCta + half * 96 + cc * 16) + (lane & 3),
+                      val[i]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_free[ab]);
       ++g;
     }
   }
