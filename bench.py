@@ -130,6 +130,25 @@ def _time_ms(fn, reps: int = 10, warm: int = 3) -> float:
     return e0.elapsed_time(e1) / reps
 
 
+def measure_backward(dev, peaks, S_b: int, reps: int = 10, warm: int = 3) -> dict:
+    """Sparse MLA backward over the last S_b queries of the prefill shape (dKV accumulated in fp32)."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator(device=dev).manual_seed(13)
+    saved = WORKLOAD["S"]
+    q, kv, idx = make_inputs_cuda(11, dev)
+    q, idx = q[:, saved - S_b:].contiguous(), idx[:, saved - S_b:].contiguous()
+    scale, q0 = WORKLOAD["D"] ** -0.5, WORKLOAD["S_kv"] - S_b
+    out, lse = dsa.sparse_mla_fwd_raw(q, kv, idx, sm_scale=scale, q_start=q0, causal=True, dv=WORKLOAD["DV"], return_lse=True)
+    d_out = torch.randn(out.shape, generator=g, device=dev).to(torch.bfloat16)
+    t_bwd = _time_ms(lambda: dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=q0, causal=True), reps=reps, warm=warm)
+    bwd_pairs = int((idx >= 0).sum().item())
+    bwd_tflops = bwd_pairs * WORKLOAD["H"] * 5504 / (t_bwd * 1e-3) / 1e12
+    assert dsa.kernel_status() == 0
+    return {"ms": t_bwd, "tokens_per_s": S_b / (t_bwd * 1e-3), "tflops": bwd_tflops, "frac_of_bf16_peak": bwd_tflops / peaks["bf16_tflops"],
+            "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (tensor-core kernels, workspace "
+                        "allocation and dKV zeroing inside the timed call)"}
+
+
 def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU.
     small: the last 1024 queries / 16 sequences only (for profiler captures)."""
@@ -175,22 +194,10 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     pipe_flop = int(pp.sum()) * 64 * 256 + int(np.minimum(pp, WORKLOAD["topk"]).sum()) * WORKLOAD["H"] * FLOP_PER_PAIR_HEAD
     pipe_tflops = pipe_flop / (t_pipe * 1e-3) / 1e12
     del qi, ki, wi, qm, kvm
-    # backward at the prefill shape (last S_b queries of the workload; dKV accumulated in fp32)
-    S_b = 256 if small else WORKLOAD["S"]
-    saved = WORKLOAD["S"]
-    q, kv, idx = make_inputs_cuda(11, dev)
-    q, idx = q[:, saved - S_b:].contiguous(), idx[:, saved - S_b:].contiguous()
-    scale, q0 = WORKLOAD["D"] ** -0.5, WORKLOAD["S_kv"] - S_b
-    out, lse = dsa.sparse_mla_fwd_raw(q, kv, idx, sm_scale=scale, q_start=q0, causal=True, dv=WORKLOAD["DV"], return_lse=True)
-    d_out = torch.randn(out.shape, generator=g, device=dev).to(torch.bfloat16)
-    t_bwd = _time_ms(lambda: dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, d_out, sm_scale=scale, q_start=q0, causal=True), reps=10, warm=3)
-    bwd_pairs = int((idx >= 0).sum().item())
-    bwd_tflops = bwd_pairs * WORKLOAD["H"] * 5504 / (t_bwd * 1e-3) / 1e12
-    del q, kv, idx, out, lse, d_out
+    backward = measure_backward(dev, peaks, 256 if small else WORKLOAD["S"])
     assert dsa.kernel_status() == 0
     return {
-        "backward": {"ms": t_bwd, "tokens_per_s": S_b / (t_bwd * 1e-3), "tflops": bwd_tflops, "frac_of_bf16_peak": bwd_tflops / peaks["bf16_tflops"],
-                     "workload": f"sparse MLA backward, last {S_b} queries of the prefill shape, dQ bf16 + dKV fp32 (tensor-core kernels, workspace and dKV zeroing inside the timed call)"},
+        "backward": backward,
         "pipeline": {"ms": t_pipe, "tokens_per_s": Sp / (t_pipe * 1e-3), "tflops": pipe_tflops, "frac_of_bf16_peak": pipe_tflops / peaks["bf16_tflops"],
                      "workload": f"indexer (64 x 128) -> top-2048 -> sparse MLA forward on the selected indices, S_q={Sp}, S_kv={S_kvp}, one stream"},
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
@@ -264,9 +271,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others"],
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward"],
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
-                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements")
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls)")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="queries the CPU baseline / parity sample covers")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
@@ -296,6 +303,10 @@ def main() -> None:
 
     w = WORKLOAD
     peaks = load_peaks()
+    if args.stage == "backward":
+        if rank == 0:
+            print(json.dumps({"backward": measure_backward(dev, peaks, w["S"], reps=1, warm=1)}), flush=True)
+        return
     if args.stage == "others":
         if rank == 0:
             print(json.dumps({"other_stages": measure_other_stages(dev, peaks, small=bool(args.queries))}), flush=True)

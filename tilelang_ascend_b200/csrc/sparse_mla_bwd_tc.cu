@@ -36,6 +36,9 @@ constexpr uint32_t kChunkBytes = kBK * 128;    // 64 keys x 64 dims, 128-byte sw
 constexpr uint32_t kTileBytes = kM * 128;      // one P / dS tile: 128 heads x 64 keys
 constexpr int kThreads = 288;                  // warps 0-3 epilogue, 4-7 gather / loads, 8 MMA issuer
 constexpr int kMmaWarp = 8;
+// Index lists of up to this many entries are copied to shared memory when a CTA starts (one memory latency for the whole
+// list); longer lists are read from global memory tile by tile, one exposed latency per tile.
+constexpr int kIdxInSmem = 2048;
 
 // Workspace of one pass, carved by the host launcher.
 struct Pass {
@@ -159,8 +162,14 @@ struct ScoresCfg {
   static constexpr uint32_t kStageBytes = kChunks * kChunkBytes;
   static constexpr uint32_t kOffBar = kStages * kStageBytes;
   static constexpr uint32_t kOffMask = kOffBar + 256;
-  static constexpr uint32_t kSmemBytes = kOffMask + kMaxTiles * 8 + 1024;  // + slack to align the base to 1024 B
-  static constexpr uint32_t kColA = 0, kColS = 288;          // A operand: up to 288 columns (576 dims), then two score buffers
+  static constexpr uint32_t kOffIdx = kOffMask + kMaxTiles * 8;             // the query's index list (when it has at most kIdxInSmem entries)
+  static constexpr uint32_t kSmemBytes = kOffIdx + kIdxInSmem * 4 + 1024;   // + slack to align the base to 1024 B
+  // Tensor memory: the A operand (288 or 256 columns), then a ring of score buffers of 64 columns.  The hand-over of a
+  // buffer (commit -> epilogue wakes -> tensor-memory load -> "free" arrive -> issuer wakes) takes longer than the MMAs of a
+  // tile, so two buffers leave the tensor pipe idle most of the time; three (four) cover it.
+  static constexpr int kSBufs = MODE == 0 ? 3 : 4;
+  static constexpr uint32_t kColA = 0, kColS = MODE == 0 ? 288 : 256;
+  static_assert(kColS + kSBufs * kBK <= 512, "tensor memory columns");
   static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 };
 }  // namespace bwdtc
@@ -177,10 +186,11 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   uint64_t* kv_full = bars;        // [3] count 128: cp.async completion of the gather threads
   uint64_t* kv_empty = bars + 3;   // [3] count 1: commit after the MMAs that read the stage
-  uint64_t* s_full = bars + 6;     // [2] count 1: commit after the MMAs of a tile
-  uint64_t* s_free = bars + 8;     // [2] count 4: the epilogue warps have read the buffer out of tensor memory
-  uint64_t* a_ready = bars + 10;   // count 4: the A operand is in tensor memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* s_full = bars + 6;     // [kSBufs] count 1: commit after the MMAs of a tile
+  uint64_t* s_free = bars + 10;    // [kSBufs] count 4: the epilogue warps have read the buffer out of tensor memory
+  uint64_t* a_ready = bars + 14;   // count 4: the A operand is in tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  constexpr int kSBufs = Cfg::kSBufs;
   unsigned long long* smask = reinterpret_cast<unsigned long long*>(smem + Cfg::kOffMask);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -190,11 +200,15 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&kv_full[i], 128); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
+    for (int i = 0; i < kSBufs; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); }
     mbar_init(a_ready, 4);
     mbar_init_fence();
   }
   for (int i = tid; i < ps.ntiles; i += kThreads) smask[i] = ps.masks[static_cast<int64_t>(ql) * ps.ntiles2 + i];
+  int32_t* sidx = reinterpret_cast<int32_t*>(smem + Cfg::kOffIdx);
+  const bool idx_in_smem = p.topk <= kIdxInSmem;
+  if (idx_in_smem)
+    for (int i = tid; i < p.topk; i += kThreads) sidx[i] = __ldg(p.indices + static_cast<int64_t>(bt) * p.topk + i);
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -219,12 +233,12 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
       const int s = g % kStages;
       const int key = pw * 16 + (lane & 15);
       const bool valid = (mask >> key) & 1ull;
-      const int my_idx = valid ? __ldg(idx_row + tile * kBK + key) : 0;
+      const int my_idx = valid ? (idx_in_smem ? sidx[tile * kBK + key] : __ldg(idx_row + tile * kBK + key)) : 0;
       const int my_row = valid ? static_cast<int>(kv_row_of(p, b, my_idx)) : -1;
       int rows[16];
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) rows[kk] = __shfl_sync(0xffffffffu, my_row, kk);
-      if (g >= kStages && !__all_sync(0xffffffffu, mbar_wait<true>(&kv_empty[s], ((g / kStages) + 1) & 1, p.status))) { ok = false; break; }
+      if (g >= kStages && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[s], ((g / kStages) + 1) & 1, p.status))) { ok = false; break; }
       gather_rows<kChunks>(sBase + s * Cfg::kStageBytes, kv_bytes, 0, rows, pw, lane);
       cp_async_arrive_noinc(&kv_full[s]);
       ++g;
@@ -238,10 +252,10 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
       ok = mbar_wait(a_ready, 0, p.status);
       for (int tile = 0; ok && tile < ps.ntiles; ++tile) {
         if (smask[tile] == 0ull) continue;
-        const int s = g % kStages, sb = g & 1;
+        const int s = g % kStages, sb = g % kSBufs;
         const uint32_t stage = sBase + s * Cfg::kStageBytes;
         if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
-        if (g >= 2 && !mbar_wait(&s_free[sb], ((g >> 1) + 1) & 1, p.status)) { ok = false; break; }
+        if (g >= kSBufs && !mbar_wait(&s_free[sb], ((g / kSBufs) + 1) & 1, p.status)) { ok = false; break; }
         fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
         const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
@@ -291,7 +305,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
     for (int tile = 0; run && ok && tile < ps.ntiles; ++tile) {
       const unsigned long long mask = smask[tile];
       if (mask == 0ull) continue;
-      const int sb = g & 1;
+      const int sb = g % kSBufs;
       uint32_t sc[64];
       const uint8_t* p_tile = ps.p_ws + (tile0 + tile) * kTileBytes;
       uint4 pv[8];  // MODE 1: this row's P values of the tile, requested before the wait so that their latency hides behind it
@@ -299,7 +313,7 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
 #pragma unroll
         for (int u = 0; u < 8; ++u) pv[u] = *reinterpret_cast<const uint4*>(p_tile + sw128_offset(r, u));
       }
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g >> 1) & 1, p.status))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (g / kSBufs) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
       tmem_ld32(tS + sb * kBK + lane_base, sc);
       tmem_ld32(tS + sb * kBK + 32 + lane_base, sc + 32);
@@ -353,7 +367,8 @@ constexpr uint32_t kBBytes = 3 * kChunkBytes;                   // gathered rows
 constexpr uint32_t kStageBytes = kTileBytes + kBBytes;          // dS tile + rows
 constexpr uint32_t kOffBar = kStages * kStageBytes;
 constexpr uint32_t kOffMask = kOffBar + 128;
-constexpr uint32_t kSmemBytes = kOffMask + kMaxTiles * 8 + 1024;
+constexpr uint32_t kOffIdx = kOffMask + kMaxTiles * 8;
+constexpr uint32_t kSmemBytes = kOffIdx + kIdxInSmem * 4 + 1024;
 constexpr uint32_t kTmemCols = 256;
 static_assert(2 * kSmemBytes <= 232448 - 2048, "two CTAs per SM");
 }  // namespace dq
@@ -388,6 +403,10 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 2) sparse_mla_bwd_dq_kernel(c
     mbar_init_fence();
   }
   for (int i = tid; i < ps.ntiles; i += kThreads) smask[i] = ps.masks[static_cast<int64_t>(ql) * ps.ntiles2 + i];
+  int32_t* sidx = reinterpret_cast<int32_t*>(smem + kOffIdx);
+  const bool idx_in_smem = p.topk <= kIdxInSmem;
+  if (idx_in_smem)
+    for (int i = tid; i < p.topk; i += kThreads) sidx[i] = __ldg(p.indices + static_cast<int64_t>(bt) * p.topk + i);
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -413,12 +432,12 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 2) sparse_mla_bwd_dq_kernel(c
       const int s = g % kStages;
       const int key = pw * 16 + (lane & 15);
       const bool valid = (mask >> key) & 1ull;
-      const int my_idx = valid ? __ldg(idx_row + tile * kBK + key) : 0;
+      const int my_idx = valid ? (idx_in_smem ? sidx[tile * kBK + key] : __ldg(idx_row + tile * kBK + key)) : 0;
       const int my_row = valid ? static_cast<int>(kv_row_of(p, b, my_idx)) : -1;
       int rows[16];
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) rows[kk] = __shfl_sync(0xffffffffu, my_row, kk);
-      if (g >= kStages && !__all_sync(0xffffffffu, mbar_wait<true>(&empty[s], ((g / kStages) + 1) & 1, p.status))) { ok = false; break; }
+      if (g >= kStages && !__all_sync(0xffffffffu, mbar_wait(&empty[s], ((g / kStages) + 1) & 1, p.status))) { ok = false; break; }
       const uint32_t stage = sBase + s * kStageBytes;
       if (pw == 0 && lane == 0) {
         mbar_arrive_expect_tx(&a_full[s], kTileBytes);
@@ -570,7 +589,7 @@ __global__ void __launch_bounds__(bwdtc::dkv::kThreadsDkv, 1) sparse_mla_bwd_dkv
 #pragma unroll 1
         for (int which = 0; which < 2; ++which, ++j) {
           const int s = j % kStages;
-          if (j >= kStages && !mbar_wait<true>(&empty[s], ((j / kStages) + 1) & 1, p.status)) { ok = false; break; }
+          if (j >= kStages && !mbar_wait(&empty[s], ((j / kStages) + 1) & 1, p.status)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[s], kPairBytes);
           bulk_copy_g2s(sBase + s * kPairBytes, (which == 0 ? ps.ds_ws : ps.p_ws) + (tile0 + 2 * tp) * kTileBytes, kPairBytes, &full[s]);
         }
