@@ -327,6 +327,26 @@ def sparse_flash_mla_v4(
 
 
 # ---------------------------------------------------------------------------
+# HISA block-sparse indexer logits
+# ---------------------------------------------------------------------------
+def block_sparse_logits(q: torch.Tensor, k: torch.Tensor, topk_block_indices: torch.Tensor, kv_block_size: int,
+                        weights: torch.Tensor, cu_seqlen_ks: torch.Tensor, cu_seqlen_ke: torch.Tensor) -> torch.Tensor:
+    """logits [S, topk, kv_block_size] fp32: sum_h w[s,h] * relu(q[s,h,:] . k[pos,:]) at pos = block * kv_block_size + b, -inf
+    where pos >= S_kv or pos outside [ks[s], ke[s]).  Follows ref_block_sparse_mqa_attn
+    (examples/HISA/block_sparse_mqa_attn_expert_test.py:548-587); positions beyond the key tensor are not read here
+    (the reference's gather would fail on them)."""
+    S, H, D = q.shape
+    S_kv = k.shape[0]
+    pos = topk_block_indices.long()[:, :, None] * kv_block_size + torch.arange(kv_block_size)[None, None, :]   # [S, topk, bs]
+    safe = pos.clamp(0, S_kv - 1)
+    kg = k.float()[safe.reshape(-1)].reshape(S, -1, D)                                                         # [S, topk*bs, D]
+    sc = torch.einsum("shd,snd->snh", q.float(), kg).relu() * weights.float()[:, None, :]
+    logits = sc.sum(-1).reshape(S, -1, kv_block_size)
+    bad = (pos >= S_kv) | (pos < 0) | (pos < cu_seqlen_ks.long()[:, None, None]) | (pos >= cu_seqlen_ke.long()[:, None, None])
+    return logits.masked_fill(bad, NEG_INF)
+
+
+# ---------------------------------------------------------------------------
 # seeded synthetic inputs of the benchmark configurations
 # ---------------------------------------------------------------------------
 def make_sparse_mla_inputs(B: int, S: int, S_kv: int, H: int, topk: int, *, D: int = 576, seed: int = 0,

@@ -154,6 +154,20 @@ def main() -> None:
                         act_q=np.array(act_q), act_kv=np.array(act_kv), ci=ci, ratio=np.int64(ratio), win=np.int64(win),
                         out3=bits(o3), lse3=l3.numpy(), out2=bits(o2), lse2=l2.numpy(), out1=bits(o1), lse1=l1.numpy())
 
+    # ---- HISA block-sparse indexer logits ---------------------------------------------------------
+    env = load_functions(os.path.join(ref, "examples/HISA/block_sparse_mqa_attn_expert_test.py"), ["ref_block_sparse_mqa_attn"])
+    g = torch.Generator().manual_seed(21)
+    S, S_kv, H, D, bs, topk = 12, 256, 8, 32, 16, 4
+    qh = torch.rand((S, H, D), generator=g).to(torch.float16) - 0.5
+    kh = torch.rand((S_kv, D), generator=g).to(torch.float16) - 0.5
+    wh = (torch.rand((S, H), generator=g) - 0.3).to(torch.float16)
+    ks_ = torch.randint(0, 40, (S,), generator=g, dtype=torch.int32)
+    ke_ = (torch.arange(1, S + 1, dtype=torch.int32) * (S_kv // S)).clamp(max=S_kv)
+    blk = torch.randint(0, S_kv // bs, (S, topk), generator=g, dtype=torch.int32)
+    hl = env["ref_block_sparse_mqa_attn"](qh, kh, blk, bs, wh, ks_, ke_)
+    np.savez_compressed(os.path.join(HERE, "hisa_block_sparse_logits.npz"), q=bits(qh), k=bits(kh), w=bits(wh), ks=ks_.numpy(), ke=ke_.numpy(),
+                        blk=blk.numpy(), bs=np.int64(bs), logits=hl.numpy())
+
     # ---- lightning indexer, production golden ---------------------------------------------------
     env = load_functions(os.path.join(ref, "examples/deepseek_v4/lightning_indexer.py"),
                          ["_NEG_INF", "cpu_lightning_indexer"])

@@ -1,0 +1,45 @@
+"""HISA block-sparse indexer logits on the GPU against the oracle."""
+import pytest
+import torch
+
+from gpu_util import check_status
+from oracle import dsa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("S,S_kv,H,D,bs,topk,dtype,wdtype", [
+    (64, 4096, 32, 128, 128, 8, torch.float16, torch.float16),     # the reference test's shape family (fp16)
+    (33, 1000, 64, 128, 64, 12, torch.bfloat16, torch.float32),    # S_kv not a multiple of the block: the last block is cut
+    (5, 300, 7, 64, 48, 4, torch.bfloat16, torch.bfloat16),        # block size that is not a multiple of 32, odd head count
+])
+def test_block_sparse_logits_match_oracle(S, S_kv, H, D, bs, topk, dtype, wdtype):
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator().manual_seed(S)
+    q = (torch.rand((S, H, D), generator=g) - 0.5).to(dtype)
+    k = (torch.rand((S_kv, D), generator=g) - 0.5).to(dtype)
+    w = (torch.rand((S, H), generator=g) - 0.3).to(wdtype)
+    ks = torch.randint(0, S_kv // 8, (S,), generator=g, dtype=torch.int32)
+    ke = (torch.arange(1, S + 1, dtype=torch.int32) * (S_kv // S)).clamp(max=S_kv)
+    blk = torch.randint(0, (S_kv + bs - 1) // bs, (S, topk), generator=g, dtype=torch.int32)
+    kernel = dsa.block_sparse_mqa_attn_return_logits(S, S_kv, bs, topk, H, D, block_N=8 if bs % 8 == 0 else 1)
+    out = kernel(q.cuda(), k.cuda(), blk.cuda(), w.cuda(), ks.cuda(), ke.cuda()).cpu()
+    check_status()
+    ref = orc.block_sparse_logits(q, k, blk, bs, w, ks, ke)
+    assert out.shape == ref.shape == (S, topk, bs)
+    assert torch.equal(torch.isinf(out), torch.isinf(ref)), "masked positions differ"
+    fin = torch.isfinite(ref)
+    # products of 16-bit inputs are exact in fp32; only the summation order differs
+    torch.testing.assert_close(out[fin], ref[fin], rtol=2e-5, atol=2e-4)
+
+
+def test_block_sparse_logits_argument_checks():
+    import tilelang_ascend_b200 as dsa
+    with pytest.raises(AssertionError):
+        dsa.block_sparse_mqa_attn_return_logits(8, 64, 16, 6, 4, 32)      # topk not divisible by 4
+    kernel = dsa.block_sparse_mqa_attn_return_logits(8, 64, 16, 4, 4, 32)
+    q = torch.zeros((8, 4, 32), dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        kernel(q, torch.zeros((64, 16), dtype=torch.float16, device="cuda"), torch.zeros((8, 4), dtype=torch.int32, device="cuda"),
+               torch.zeros((8, 4), dtype=torch.float16, device="cuda"), torch.zeros(8, dtype=torch.int32, device="cuda"),
+               torch.zeros(8, dtype=torch.int32, device="cuda"))

@@ -72,6 +72,16 @@ def test_sparse_flash_mla_v4_matches_reference_golden(golden):
         torch.testing.assert_close(out.float().permute(0, 2, 1, 3), from_bits(g["out" + tag]).float(), rtol=2e-2, atol=2e-2, msg=tag)
 
 
+def test_block_sparse_logits_match_reference_golden(golden):
+    g = golden("hisa_block_sparse_logits.npz")
+    q, k, w = from_bits(g["q"], torch.float16), from_bits(g["k"], torch.float16), from_bits(g["w"], torch.float16)
+    out = orc.block_sparse_logits(q, k, torch.from_numpy(g["blk"]), int(g["bs"]), w, torch.from_numpy(g["ks"]), torch.from_numpy(g["ke"]))
+    ref = torch.from_numpy(g["logits"])
+    assert torch.equal(torch.isinf(out), torch.isinf(ref))
+    fin = torch.isfinite(ref)
+    torch.testing.assert_close(out[fin], ref[fin], rtol=1e-5, atol=1e-5)
+
+
 def test_lightning_indexer_matches_reference_golden(golden):
     g = golden("lightning_indexer.npz")
     for tag in ("causal", "full", "ties"):

@@ -24,6 +24,8 @@ int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_
 int launch_sparse_mla_bwd(const BwdParams& bp, bool bf16, cudaStream_t stream);
 int launch_sink_combine(const void* out_a, const float* lse_a, const void* out_b, const float* lse_b, const float* sinks, void* out, float* lse,
                         int64_t rows, int H, int DV, bool bf16, cudaStream_t stream);
+bool block_sparse_logits_supported(const BlockSparseLogitsParams& p);
+int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
 bool sparse_mla_bwd_tc_supported(const FwdParams& p);
 size_t sparse_mla_bwd_tc_bytes_per_query(int H, int topk);
 int launch_sparse_mla_bwd_tc(const BwdParams& bp, bool bf16, void* workspace, size_t workspace_bytes, int queries_per_pass, cudaStream_t stream);
@@ -295,6 +297,20 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
   if (rows <= 0 || H <= 0 || DV <= 0 || rows % H != 0) return fail("rows must be a positive multiple of H; DV positive");
   int err = dsa::launch_sink_combine(out_a, lse_a, out_b, lse_b, sinks, out, lse, rows, H, DV, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("sink_combine launch", err) : 0;
+}
+
+int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_indices, const void* weights, const int32_t* ks,
+                            const int32_t* ke, float* logits, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t kv_block_size,
+                            int32_t topk, int32_t dtype, int32_t weights_dtype, void* stream) {
+  if (!q || !k || !block_indices || !weights || !ks || !ke || !logits) return fail("null tensor pointer");
+  if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
+  if (weights_dtype < 0 || weights_dtype > 2) return fail("weights_dtype must be 0 (bfloat16), 1 (float16) or 2 (float32)");
+  if (S <= 0 || S_kv <= 0 || kv_block_size <= 0 || topk <= 0) return fail("S, S_kv, kv_block_size and topk must be positive");
+  dsa::BlockSparseLogitsParams p{q, k, block_indices, weights, ks, ke, logits, S, S_kv, H, D, kv_block_size, topk, weights_dtype};
+  if (!dsa::block_sparse_logits_supported(p)) return fail("block-sparse logits need 1 <= heads <= 64 and index_dim a multiple of 8, at most 256");
+  if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u)) return fail("q and k must be 16-byte aligned");
+  int err = dsa::launch_block_sparse_logits(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("block_sparse_logits launch", err) : 0;
 }
 
 }  // extern "C"

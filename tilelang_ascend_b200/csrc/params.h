@@ -62,4 +62,17 @@ struct IndexerParams {
   int* status;
 };
 
+// Block-sparse indexer logits (HISA).
+struct BlockSparseLogitsParams {
+  const void* q;            // [S, H, D]
+  const void* k;            // [S_kv, D]
+  const int32_t* blocks;    // [S, topk]
+  const void* w;            // [S, H], dtype w_dtype
+  const int32_t* ks;        // [S]
+  const int32_t* ke;        // [S]
+  float* logits;            // [S, topk, block]
+  int S, S_kv, H, D, block, topk;
+  int w_dtype;              // 0 bf16, 1 fp16, 2 fp32
+};
+
 }  // namespace dsa

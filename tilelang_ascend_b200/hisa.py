@@ -1,0 +1,57 @@
+"""HISA block-sparse indexer logits behind the factory signature of the reference
+(examples/HISA/block_sparse_mqa_attn_expert_test.py:24-45): the step before the token-level top-k at very long context --
+the lightning-indexer score of every key of a query's selected KV blocks."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .adapter import check_inputs, current_stream, dtype_code, ptr
+
+_W_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def block_sparse_logits_raw(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke, kv_block_size: int):
+    """One launch through the C ABI.  q [S,H,D], k [S_kv,D], topk_block_indices [S,topk] int32, weights [S,H] (q's dtype or
+    fp32), cu_seqlen_ks / cu_seqlen_ke [S] int32 -> logits [S, topk, kv_block_size] fp32."""
+    dev = check_inputs([q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke], [None, q.dtype, torch.int32, None, torch.int32, torch.int32],
+                       ["q", "k", "topk_block_indices", "weights", "cu_seqlen_ks", "cu_seqlen_ke"])
+    if q.dim() != 3 or k.dim() != 2 or k.shape[1] != q.shape[2]:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}")
+    S, H, D = q.shape
+    if topk_block_indices.shape[0] != S or tuple(weights.shape) != (S, H) or cu_seqlen_ks.shape != (S,) or cu_seqlen_ke.shape != (S,):
+        raise ValueError("topk_block_indices / weights / cu_seqlen_ks / cu_seqlen_ke do not match q")
+    if weights.dtype not in _W_DTYPES:
+        raise ValueError(f"weights must be bfloat16, float16 or float32, got {weights.dtype}")
+    topk = topk_block_indices.shape[1]
+    logits = torch.empty((S, topk, kv_block_size), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().dsa_block_sparse_logits(ptr(q), ptr(k), ptr(topk_block_indices), ptr(weights), ptr(cu_seqlen_ks), ptr(cu_seqlen_ke),
+                                                       ptr(logits), S, k.shape[0], H, D, int(kv_block_size), topk, dtype_code(q.dtype),
+                                                       _W_DTYPES[weights.dtype], current_stream(dev)))
+    return logits
+
+
+class BlockSparseLogitsKernel:
+    """Callable returned by :func:`block_sparse_mqa_attn_return_logits`:
+    ``kernel(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke) -> logits``; only inputs are passed, the output
+    is allocated on the device of ``q`` and the launch goes to the current stream without synchronising."""
+
+    def __init__(self, seq_len, seq_len_kv, kv_block_size, topk, heads, index_dim):
+        self.shape = (seq_len, seq_len_kv, kv_block_size, topk, heads, index_dim)
+
+    def __call__(self, q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke):
+        seq_len, seq_len_kv, kv_block_size, topk, heads, index_dim = self.shape
+        if tuple(q.shape) != (seq_len, heads, index_dim) or tuple(k.shape) != (seq_len_kv, index_dim) or \
+                tuple(topk_block_indices.shape) != (seq_len, topk):
+            raise ValueError("tensor shapes differ from the factory's static parameters")
+        return block_sparse_logits_raw(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke, kv_block_size)
+
+
+def block_sparse_mqa_attn_return_logits(seq_len: int, seq_len_kv: int, kv_block_size: int, topk: int, heads: int, index_dim: int,
+                                        block_N: int = 8, num_stages: int = 2, threads: int = 2, grid_size: int = 24):
+    """Factory with the reference's signature; ``block_N``, ``num_stages``, ``threads`` and ``grid_size`` (tile / core-count
+    knobs of the Ascend kernel) are accepted and ignored, its argument checks are kept (:54-55)."""
+    assert kv_block_size % block_N == 0, "block_N must divide kv_block_size"
+    assert topk % 4 == 0, "topk must be divisible by 4 for 4x unrolled loop"
+    return BlockSparseLogitsKernel(seq_len, seq_len_kv, kv_block_size, topk, heads, index_dim)
