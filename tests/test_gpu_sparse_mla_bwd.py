@@ -71,3 +71,19 @@ def test_tensor_core_backward_rejects_other_shapes():
     lse = torch.zeros((1, 2, 4), dtype=torch.float32, device="cuda")
     with pytest.raises(ValueError):
         dsa.sparse_mla_bwd_raw(q, kv, idx, out, lse, out, sm_scale=0.1, q_start=14, causal=True, impl="tensor_core")
+
+
+def test_tensor_core_backward_fp16():
+    import tilelang_ascend_b200 as dsa
+    B, S, S_kv, H, topk = 1, 4, 200, 128, 128
+    q, kv, idx = orc.make_sparse_mla_inputs(B, S, S_kv, H, topk, seed=9, dtype=torch.float16)
+    g = torch.Generator().manual_seed(4)
+    d_out = torch.randn((B, S, H, 512), generator=g).to(torch.float16)
+    scale = 576 ** -0.5
+    qc, kvc, ic = q.cuda(), kv.cuda(), idx.cuda()
+    out, lse = dsa.sparse_mla_fwd_raw(qc, kvc, ic, sm_scale=scale, q_start=S_kv - S, causal=True, dv=512)
+    d_q, d_kv = dsa.sparse_mla_bwd_raw(qc, kvc, ic, out, lse, d_out.cuda(), sm_scale=scale, q_start=S_kv - S, causal=True, impl="tensor_core")
+    check_status()
+    ref_dq, ref_dkv = orc.sparse_mla_bwd(q, kv, idx, d_out)
+    assert_close_fp(d_q.cpu(), ref_dq, "dQ fp16")
+    assert_close_fp(d_kv.cpu(), ref_dkv, "dKV fp16", atol=2e-2 * max(1.0, (H * S / 16) ** 0.5))
