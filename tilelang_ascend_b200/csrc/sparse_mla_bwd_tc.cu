@@ -5,8 +5,8 @@
 //
 // The five contractions do not fit one CTA's tensor memory (dQ alone is 128 x 576 fp32 = 576 of the 512 columns),
 // so the work is cut into four tcgen05 kernels that hand P and dS (input dtype) to each other through a workspace.
-// The workspace is small next to the arithmetic (two 16 KB tiles per 64 keys of a query, against 90 MFLOP) and a pass
-// over a few hundred queries mostly stays in L2.  A pass handles `nq` consecutive queries:
+// The workspace traffic is small next to the arithmetic (two 16 KB tiles per 64 keys of a query, against 90 MFLOP).
+// A pass handles `nq` consecutive queries:
 //
 //   prep    delta = sum_d dO*O per (query, head); 64-bit validity mask per (query, tile of 64 keys)
 //   scores  MODE 0: S = Q K^T   (A = Q of 128 heads in tensor memory, B = gathered KV rows, 9 chunks of 64 dims)  -> P
