@@ -44,6 +44,7 @@ def test_autograd_function():
     (1, 6, 700, 128, 448, 4),     # 7 tiles (odd count), two passes, ring buffers wrap
     (1, 5, 40, 128, 192, 2),      # more slots than keys: tiles without any key are skipped, early queries nearly empty
     (2, 3, 520, 200, 320, 0),     # two head blocks, the second partly filled
+    (1, 2, 3000, 128, 2112, 0),   # more than 2048 slots: the index list stays in global memory; 33 tiles
 ])
 def test_tensor_core_backward_passes_and_tiles(B, S, S_kv, H, topk, qpp):
     """Tensor-core backward: several passes through a small workspace, many key tiles, skipped tiles, padded head blocks."""
