@@ -149,6 +149,47 @@ def measure_backward(dev, peaks, S_b: int, reps: int = 10, warm: int = 3) -> dic
                         "allocation and dKV zeroing inside the timed call)"}
 
 
+def measure_v4(dev) -> dict:
+    """DeepSeek-V4 sparse_flash_mla on the shapes of the reference's own benchmark table
+    (examples/deepseek_v4/sparse_flash_mla/bench_mark.md: B=1, 64 heads, D=512, TND, bf16, block 128, window 127, K=512,
+    S=8192 prefill / one token against 8193 keys decode); synthetic tensors, whole front-door call timed (index lists built
+    on the device, two sparse-forward calls, sink combine)."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator(device=dev).manual_seed(5)
+    N1, D, bs, K = 64, 512, 128, 512
+    res = {}
+    for mode, S_q, S_kv in (("prefill", 8192, 8192), ("decode", 1, 8193)):
+        q = torch.randn((S_q, N1, D), generator=g, device=dev).to(torch.bfloat16)
+        nblk = (S_kv + bs - 1) // bs
+        ori = torch.randn((nblk, bs, 1, D), generator=g, device=dev).to(torch.bfloat16)
+        ori_bt = torch.randperm(nblk, generator=g, device=dev).to(torch.int32).view(1, nblk)
+        cu = torch.tensor([0, S_q], dtype=torch.int32, device=dev)
+        used = torch.tensor([S_kv], dtype=torch.int32, device=dev)
+        sinks = torch.randn((N1,), generator=g, device=dev)
+        common = dict(ori_kv=ori, ori_block_table=ori_bt, cu_seqlens_q=cu, seqused_kv=used, sinks=sinks, softmax_scale=D ** -0.5,
+                      return_softmax_lse=True)
+        for name, ratio in (("swa", 4), ("hca", 128), ("csa", 4)):
+            kw = dict(common)
+            if name != "swa":
+                ncmp = max(S_kv // ratio, 1)
+                cblk = (ncmp + bs - 1) // bs
+                kw.update(cmp_kv=torch.randn((cblk, bs, 1, D), generator=g, device=dev).to(torch.bfloat16),
+                          cmp_block_table=torch.arange(cblk, dtype=torch.int32, device=dev).view(1, cblk), cmp_ratio=ratio)
+            if name == "csa":
+                pos = torch.arange(S_q, device=dev) + (S_kv - S_q)
+                thr = ((pos + 1) // ratio).clamp(min=1)
+                ci = (torch.rand((S_q, K), generator=g, device=dev) * thr[:, None]).to(torch.int32)   # K draws below the threshold
+                ci = torch.where(torch.arange(K, device=dev)[None, :] < thr[:, None], ci, torch.full_like(ci, -1))
+                kw.update(cmp_sparse_indices=ci.view(S_q, 1, K).contiguous())
+            t = _time_ms(lambda: dsa.sparse_flash_mla(q, **kw), reps=5, warm=2)
+            res[f"{name}_{mode}"] = {"us": t * 1e3}
+    assert dsa.kernel_status() == 0
+    res["workload"] = "sparse_flash_mla, B=1, 64 heads, D=512, TND, bf16, block 128, window 127, K=512; prefill S=8192, decode 1 token vs 8193 keys"
+    res["reference_published_us_tilelang_ascend"] = {"swa_prefill": 1490.9, "hca_prefill": 3141.9, "csa_prefill": 6022.7, "swa_decode": 13.8,
+                                                     "hca_decode": 18.6, "csa_decode": 31.7}
+    return res
+
+
 def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU.
     small: the last 1024 queries / 16 sequences only (for profiler captures)."""
@@ -271,9 +312,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward"],
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "v4"],
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
-                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls)")
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="queries the CPU baseline / parity sample covers")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
@@ -303,6 +344,10 @@ def main() -> None:
 
     w = WORKLOAD
     peaks = load_peaks()
+    if args.stage == "v4":
+        if rank == 0:
+            print(json.dumps({"sparse_flash_mla_v4": measure_v4(dev)}), flush=True)
+        return
     if args.stage == "backward":
         if rank == 0:
             print(json.dumps({"backward": measure_backward(dev, peaks, w["S"], reps=1, warm=1)}), flush=True)

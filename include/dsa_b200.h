@@ -29,7 +29,8 @@ extern "C" {
 #define DSA_DTYPE_BF16 0
 #define DSA_DTYPE_FP16 1
 
-/* Kernel choice for dsa_sparse_mla_fwd: the tensor-core kernel needs D = 576 and DV = 512. */
+/* Kernel choice for dsa_sparse_mla_fwd: the tensor-core kernel needs DV = 512 and D = 576 (512 latent + 64 rope dims) or
+ * D = 512 (no rope dims: keys and values are the same rows). */
 #define DSA_IMPL_AUTO 0
 #define DSA_IMPL_GENERIC 1
 #define DSA_IMPL_TENSOR_CORE 2
@@ -178,6 +179,20 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
 int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_indices, const void* weights, const int32_t* ks,
                             const int32_t* ke, float* logits, int32_t S, int32_t S_kv, int32_t H, int32_t D,
                             int32_t kv_block_size, int32_t topk, int32_t dtype, int32_t weights_dtype, void* stream);
+
+/* Index lists of sparse_flash_mla for T query tokens: ori_rows [T, ori_win_left + 1] and cmp_rows [T, K] int32 receive the
+ * physical row numbers (block_table[b, pos / block_size] * block_size + pos % block_size) of each token's sliding window
+ * of the original cache and of its compressed keys, -1 where a slot takes no part; they are the `indices` of two
+ * dsa_sparse_mla_fwd calls over the flattened pools.  tnd != 0: tokens are packed and cu_seqlens_q [B + 1] gives the sequence
+ * starts; tnd == 0: token = b * S + s (cu_seqlens_q optional: actual lengths, padded tokens get empty lists).
+ * scenario 1: window only (cmp_* unused); 2: every compressed token below floor((p + 1) / cmp_ratio); 3: the caller's
+ * cmp_sparse_indices [T, K], cut at the first -1.  Replaces the per-token key selection inside the reference kernel
+ * (examples/deepseek_v4/sparse_flash_mla/sparse_flash_mla_kernel.py; rules restated from sparse_flash_mla_golden.py:16-53, 95-118). */
+int dsa_v4_build_indices(const int32_t* cu_seqlens_q, const int32_t* seqused_kv, const int32_t* ori_block_table,
+                         const int32_t* cmp_block_table, const int32_t* cmp_sparse_indices, int32_t* ori_rows, int32_t* cmp_rows,
+                         int32_t B, int32_t T, int32_t S, int32_t tnd, int32_t ori_table_len, int32_t ori_block_size,
+                         int32_t ori_win_left, int32_t cmp_table_len, int32_t cmp_block_size, int32_t cmp_ratio, int32_t scenario,
+                         int32_t K, void* stream);
 
 #ifdef __cplusplus
 }

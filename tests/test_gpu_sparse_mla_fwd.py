@@ -249,3 +249,21 @@ def test_split_kv_fp16_paged():
     ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx, q_start_index_s=10 ** 9)
     assert_close_fp(spl.cpu(), ref_o, "out vs oracle")
     assert_close_fp(spl_l.cpu(), ref_l, "lse vs oracle")
+
+
+def test_tensor_core_forward_without_rope_dims():
+    """D = DV = 512 (keys are the values, no rope dims): tensor-core kernel against the oracle and the CUDA-core kernel."""
+    import tilelang_ascend_b200 as dsa
+    from tilelang_ascend_b200 import _lib
+    B, S, S_kv, H, topk = 2, 5, 400, 64, 192
+    q, kv, idx = orc.make_sparse_mla_inputs(B, S, S_kv, H, topk, D=512, seed=12)
+    scale = 512 ** -0.5
+    qc, kvc, ic = q.cuda(), kv.cuda(), idx.cuda()
+    out, lse = dsa.sparse_mla_fwd_raw(qc, kvc, ic, sm_scale=scale, q_start=S_kv - S, causal=True, dv=512, impl=_lib.IMPL_TENSOR_CORE)
+    out_g, lse_g = dsa.sparse_mla_fwd_raw(qc, kvc, ic, sm_scale=scale, q_start=S_kv - S, causal=True, dv=512, impl=_lib.IMPL_GENERIC)
+    check_status()
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx, sm_scale=scale, dv=512)
+    assert_close_fp(out.cpu(), ref_o, "out (D=512, tensor core)")
+    assert_close_fp(lse.cpu(), ref_l, "lse (D=512, tensor core)")
+    assert_close_fp(out.cpu(), out_g.cpu(), "tensor core vs CUDA core")
+    assert_close_fp(lse.cpu(), lse_g.cpu(), "lse tensor core vs CUDA core")

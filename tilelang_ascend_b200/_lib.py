@@ -46,6 +46,7 @@ SIGNATURES = {
                                      c_void_p]),
     "dsa_block_sparse_logits": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                           c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "dsa_v4_build_indices": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int32] * 12 + [c_void_p]),
     "dsa_sink_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                    c_int32, c_void_p]),
     "dsa_sparse_mla_bwd_tc_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),

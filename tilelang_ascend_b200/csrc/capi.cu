@@ -24,6 +24,9 @@ int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_
 int launch_sparse_mla_bwd(const BwdParams& bp, bool bf16, cudaStream_t stream);
 int launch_sink_combine(const void* out_a, const float* lse_a, const void* out_b, const float* lse_b, const float* sinks, void* out, float* lse,
                         int64_t rows, int H, int DV, bool bf16, cudaStream_t stream);
+int launch_v4_build_indices(const int32_t* cu_q, const int32_t* seqused_kv, const int32_t* ori_bt, const int32_t* cmp_bt, const int32_t* cmp_idx,
+                            int32_t* ori_rows, int32_t* cmp_rows, int B, int T, int S, int tnd, int ori_table_len, int ori_bs, int win_left,
+                            int cmp_table_len, int cmp_bs, int ratio, int scenario, int K, cudaStream_t stream);
 bool block_sparse_logits_supported(const BlockSparseLogitsParams& p);
 int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
 bool sparse_mla_bwd_tc_supported(const FwdParams& p);
@@ -200,7 +203,7 @@ int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, vo
                       kv_len_b, q_len_b, block_table, block_size, max_blocks))
     return 1;
   const bool tc_ok = dsa::sparse_mla_fwd_tc_supported(p);
-  if (impl == DSA_IMPL_TENSOR_CORE && !tc_ok) return fail("the tensor-core kernel needs D = 576, DV = 512 and topk <= 8192");
+  if (impl == DSA_IMPL_TENSOR_CORE && !tc_ok) return fail("the tensor-core kernel needs D = 576 or 512, DV = 512 and topk <= 8192");
   if (impl != DSA_IMPL_AUTO && impl != DSA_IMPL_GENERIC && impl != DSA_IMPL_TENSOR_CORE) return fail("unknown impl");
   const bool use_tc = impl == DSA_IMPL_TENSOR_CORE || (impl == DSA_IMPL_AUTO && tc_ok);
   int err = use_tc ? dsa::launch_sparse_mla_fwd_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream))
@@ -231,7 +234,7 @@ int dsa_sparse_mla_fwd_splitkv(const void* q, const void* kv, const int32_t* ind
   if (fill_fwd_params(&p, q, kv, indices, out, lse, B, S, S_kv, H, D, DV, topk, sm_scale, q_start, causal, dtype, q_start_b,
                       kv_len_b, q_len_b, block_table, block_size, max_blocks))
     return 1;
-  if (!dsa::sparse_mla_fwd_tc_supported(p)) return fail("split-KV needs the tensor-core kernel: D = 576, DV = 512 and topk <= 8192");
+  if (!dsa::sparse_mla_fwd_tc_supported(p)) return fail("split-KV needs the tensor-core kernel: D = 576 or 512, DV = 512 and topk <= 8192");
   if (nsplit < 1 || nsplit > 64) return fail("nsplit must be in [1, 64]");
   if (nsplit > 1) {
     const size_t need = dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, DV, nsplit);
@@ -311,6 +314,23 @@ int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_i
   if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u)) return fail("q and k must be 16-byte aligned");
   int err = dsa::launch_block_sparse_logits(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("block_sparse_logits launch", err) : 0;
+}
+
+int dsa_v4_build_indices(const int32_t* cu_seqlens_q, const int32_t* seqused_kv, const int32_t* ori_block_table, const int32_t* cmp_block_table,
+                         const int32_t* cmp_sparse_indices, int32_t* ori_rows, int32_t* cmp_rows, int32_t B, int32_t T, int32_t S, int32_t tnd,
+                         int32_t ori_table_len, int32_t ori_block_size, int32_t ori_win_left, int32_t cmp_table_len, int32_t cmp_block_size,
+                         int32_t cmp_ratio, int32_t scenario, int32_t K, void* stream) {
+  if (!seqused_kv || !ori_block_table || !ori_rows) return fail("null tensor pointer");
+  if (B <= 0 || T <= 0 || ori_table_len <= 0 || ori_block_size <= 0 || ori_win_left < 0) return fail("B, T, table length and block size must be positive");
+  if (tnd ? !cu_seqlens_q : (S <= 0 || T != B * S)) return fail("packed tokens need cu_seqlens_q; otherwise T must equal B * S");
+  if (scenario < 1 || scenario > 3) return fail("scenario must be 1 (window only), 2 (all compressed tokens) or 3 (selected compressed tokens)");
+  if (scenario != 1 && (!cmp_block_table || !cmp_rows || cmp_table_len <= 0 || cmp_block_size <= 0 || cmp_ratio <= 0 || K <= 0))
+    return fail("compressed-token scenarios need the compressed block table, an output buffer, a positive ratio and K");
+  if (scenario == 3 && !cmp_sparse_indices) return fail("scenario 3 needs cmp_sparse_indices");
+  int err = dsa::launch_v4_build_indices(cu_seqlens_q, seqused_kv, ori_block_table, cmp_block_table, cmp_sparse_indices, ori_rows, cmp_rows, B, T, S, tnd,
+                                         ori_table_len, ori_block_size, ori_win_left, cmp_table_len, cmp_block_size, cmp_ratio, scenario, K,
+                                         static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("v4_build_indices launch", err) : 0;
 }
 
 }  // extern "C"

@@ -8,7 +8,7 @@
 // of the paged variant (example_sparse_flash_attn_mask_pa.py:221-238).
 //
 // Two kernels:
-//  * sparse_mla_fwd_tc_kernel  -- D = 576, DV = 512: tcgen05 tensor-core MMAs with TMEM accumulators,
+//  * sparse_mla_fwd_tc_kernel  -- D = 576 (or 512, rows without rope dims), DV = 512: tcgen05 MMAs with TMEM accumulators,
 //    one 2-CTA cluster per (query, block of 128 heads); the two CTAs split the contraction dims of
 //    Q K^T and the output columns of P V and exchange partial scores through distributed shared memory.
 //  * sparse_mla_fwd_generic_kernel -- any D <= 640 / DV <= 512 (e.g. the GQA example with dim 128):
@@ -152,9 +152,12 @@ constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays bel
 constexpr uint32_t kGatherBarrier = 5;                // named barrier of the 128 gather threads
 }  // namespace tc
 
-template <bool kBF16>
+// kRope = false: rows of 512 dims without the 64 rope dims (D = DV = 512: the keys ARE the values, as in DeepSeek-V4's
+// sparse_flash_mla); the rope buffers are zero-filled and the two rope MMA steps are left out, everything else is unchanged.
+template <bool kBF16, bool kRope>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) sparse_mla_fwd_tc_kernel(const FwdParams p) {
   using namespace tc;
+  constexpr int kRowBytes = kRope ? kD * 2 : kDV * 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sBase = smem_u32(smem);
@@ -238,10 +241,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       const int it_item = it_unit / nsplit;
       const int nbt = it_item / head_blocks, nh = (it_item - nbt * head_blocks) * kM + r;
       if (nh >= p.H) return;
-      const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * (kD * 2);
+      const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * kRowBytes;
 #pragma unroll
       for (int j = 0; j < 4; ++j) prefetch_l2(nq + rank * 512 + j * 128);
-      prefetch_l2(nq + 1024 + rank * 64);
+      if (kRope) prefetch_l2(nq + 1024 + rank * 64);
     };
     if (run_all) prefetch_q(item_of(0));  // the first item's rows: behind the wait for its tile list
     int g = 0;
@@ -256,10 +259,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       if (nvt > 0) {
         // all QK MMAs of the previous item are complete (their last s_full was waited for below): Q can be replaced
         const bool row_ok = h0 + r < p.H;
-        const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0 + (row_ok ? r : 0)) * (kD * 2);
+        const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0 + (row_ok ? r : 0)) * kRowBytes;
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-          cp_async16(sQRope + sw64_offset(r, u), qrow + 1024 + (4 * rank + u) * 16, row_ok ? 16u : 0u);
+          cp_async16(sQRope + sw64_offset(r, u), kRope ? qrow + 1024 + (4 * rank + u) * 16 : qrow, (row_ok && kRope) ? 16u : 0u);
         cp_async_commit();
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
@@ -400,7 +403,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
 #pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
           const uint32_t row = static_cast<uint32_t>(rows[kk] < 0 ? 0 : rows[kk]);
-          cp_async16(lat_dst + sw128_offset(kk, lane & 7), lat_src + static_cast<size_t>(row) * (kD * 2), rows[kk] < 0 ? 0u : 16u);
+          cp_async16(lat_dst + sw128_offset(kk, lane & 7), lat_src + static_cast<size_t>(row) * kRowBytes, rows[kk] < 0 ? 0u : 16u);
         }
         // the 64 rope bytes of the 16 keys: 4 lanes per key, two instructions
 #pragma unroll
@@ -408,7 +411,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           const int kk = hh * 8 + (lane >> 2);
           const int row = __shfl_sync(0xffffffffu, my_row, kk);
           cp_async16(stage + kRopeOff + sw64_offset(pw * 16 + kk, lane & 3),
-                     kv_bytes + static_cast<size_t>(row < 0 ? 0 : row) * (kD * 2) + 1024 + (4 * rank + (lane & 3)) * 16, row < 0 ? 0u : 16u);
+                     kv_bytes + static_cast<size_t>(row < 0 ? 0 : row) * kRowBytes + (kRope ? 1024 + (4 * rank + (lane & 3)) * 16 : 0),
+                     (row < 0 || !kRope) ? 0u : 16u);
         }
         cp_async_arrive_noinc(&kv_full[s]);
       }
@@ -448,8 +452,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           }
           const uint64_t da0 = make_smem_desc(sQRope, 16, 512, kSwizzle64B);
           const uint64_t dr0 = make_smem_desc(stage + kRopeOff, 16, 512, kSwizzle64B);
+          if constexpr (kRope) {
 #pragma unroll
-          for (int kq = 0; kq < 2; ++kq) umma_ss(tS + sb * kBK, da0 + ((kq * 32) >> 4), dr0 + ((kq * 32) >> 4), idesc_qk, 1);
+            for (int kq = 0; kq < 2; ++kq) umma_ss(tS + sb * kBK, da0 + ((kq * 32) >> 4), dr0 + ((kq * 32) >> 4), idesc_qk, 1);
+          }
           umma_commit(&s_full[sb]);
         }
         if (!ok) break;
@@ -818,11 +824,13 @@ __global__ void __launch_bounds__(128) sparse_mla_fwd_combine_kernel(const float
 // -------------------------------------------------------------------------------------------------
 bool sparse_mla_fwd_tc_supported(const FwdParams& p) {
   // (row numbers inside kv are kept in 32 bits by the gather warps)
-  return p.D == tc::kD && p.DV == tc::kDV && p.topk <= tc::kMaxTiles * tc::kBK && static_cast<long long>(p.B) * p.S_kv <= 0x7fffffffLL;
+  return (p.D == tc::kD || p.D == tc::kDV) && p.DV == tc::kDV && p.topk <= tc::kMaxTiles * tc::kBK && static_cast<long long>(p.B) * p.S_kv <= 0x7fffffffLL;
 }
 
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream) {
-  auto kern = bf16 ? sparse_mla_fwd_tc_kernel<true> : sparse_mla_fwd_tc_kernel<false>;
+  const bool rope = p.D == tc::kD;
+  auto kern = rope ? (bf16 ? sparse_mla_fwd_tc_kernel<true, true> : sparse_mla_fwd_tc_kernel<false, true>)
+                   : (bf16 ? sparse_mla_fwd_tc_kernel<true, false> : sparse_mla_fwd_tc_kernel<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tc::kSmemBytes));
   if (e != cudaSuccess) return static_cast<int>(e);
   int dev = 0, sms = 0;

@@ -55,7 +55,7 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
     lse = torch.empty((B, S, H), dtype=torch.float32, device=dev) if return_lse else None
     lib = _lib.load()
     with torch.cuda.device(dev):
-        tc_shape = D == 576 and dv == 512 and topk <= 8192 and impl != _lib.IMPL_GENERIC
+        tc_shape = D in (576, 512) and dv == 512 and topk <= 8192 and impl != _lib.IMPL_GENERIC
         if nsplit is None:
             nsplit = int(lib.dsa_sparse_mla_fwd_splitkv_nsplit(B, S, H, topk)) if tc_shape else 1
         nsplit = int(nsplit)

@@ -2,10 +2,10 @@
 with a per-head attention sink, behind the signature of the reference's front door
 (examples/deepseek_v4/sparse_flash_mla/sparse_flash_mla_api.py:94-253; golden sparse_flash_mla_golden.py:56-153).
 
-What runs where: the index lists of both key sets are built on the device from the lengths, block tables and the
-caller's compressed-token indices (integer tensor ops, a few KB per token); the attention itself is two calls of the
-sparse forward kernel (one per key set, physical row numbers into the paged pools) and one call of the sink-combine
-kernel that merges the two partial results and the sink.  K and V are the same 512-d rows (MLA latent), one KV head.
+What runs where: one kernel builds the index lists of both key sets (physical row numbers into the paged pools) from the
+lengths, block tables and the caller's compressed-token indices; the attention itself is two calls of the sparse forward
+kernel (one per key set; the tcgen05 kernel for D = 512) and one call of the sink-combine kernel that merges the two
+partial results and the sink.  K and V are the same 512-d rows (MLA latent), one KV head.
 """
 from __future__ import annotations
 
@@ -18,15 +18,6 @@ from .adapter import check_inputs, current_stream, dtype_code, ptr
 from .sparse_flash_attention import sparse_mla_fwd_raw
 
 DEFAULT_CORE_NUM = 24  # accepted and ignored (a tile-scheduling knob of the reference kernel)
-
-
-def _physical_rows(block_table: torch.Tensor, bid: torch.Tensor, pos: torch.Tensor, valid: torch.Tensor, block_size: int) -> torch.Tensor:
-    """Row numbers inside a paged pool [blocks * block_size] of logical positions ``pos`` [T, n] of sequences ``bid`` [T];
-    -1 where ``valid`` is False."""
-    safe = torch.where(valid, pos, torch.zeros_like(pos))
-    blk = torch.gather(block_table[bid.long()], 1, (safe // block_size).clamp_(max=block_table.shape[1] - 1).long())
-    rows = blk.long() * block_size + safe % block_size
-    return torch.where(valid, rows, torch.full_like(rows, -1)).to(torch.int32)
 
 
 def sink_combine_raw(out_a, lse_a, out_b, lse_b, sinks, H: int):
@@ -81,83 +72,67 @@ def sparse_flash_mla(
     dev = check_inputs([q, ori_kv], [None, q.dtype], ["q", "ori_kv"])
     scenario = 1 if cmp_kv is None else (2 if cmp_sparse_indices is None else 3)
 
+    lib = _lib.load()
     if layout_q == "TND":
         assert cu_seqlens_q is not None, "cu_seqlens_q is required for TND"
         T, N1, D = q.shape
-        cu = cu_seqlens_q.to(device=dev, dtype=torch.int64)
-        B = cu.numel() - 1
-        len_q = cu[1:] - cu[:-1]
-        tok = torch.arange(T, device=dev)
-        bid = torch.searchsorted(cu[1:].contiguous(), tok, right=True).clamp_(max=B - 1)
-        s_local = tok - cu[bid]
-        exists = torch.ones(T, dtype=torch.bool, device=dev)
+        B, S = cu_seqlens_q.numel() - 1, 0
         q_flat = q
         ci = cmp_sparse_indices
     else:
         B, S, N1, D = q.shape
         T = B * S
-        len_q = torch.full((B,), S, dtype=torch.int64, device=dev)
-        if cu_seqlens_q is not None:
-            cu = cu_seqlens_q.to(device=dev, dtype=torch.int64)
-            len_q = cu[1:] - cu[:-1]
-        tok = torch.arange(T, device=dev)
-        bid, s_local = tok // S, tok % S
-        exists = s_local < len_q[bid]
         q_flat = q.reshape(T, N1, D)
         ci = None if cmp_sparse_indices is None else cmp_sparse_indices.reshape(T, cmp_sparse_indices.shape[2], cmp_sparse_indices.shape[3])
     if ori_kv.shape[2] != 1 or ori_kv.shape[3] != D:
         raise ValueError(f"ori_kv must be [blocks, block_size, 1, {D}], got {tuple(ori_kv.shape)}")
     if D % 8 != 0 or D > 512:
         raise ValueError(f"head dim must be a multiple of 8, at most 512 (got {D})")
+    K = 0
     if scenario == 3:
         if ci.shape[1] != 1:
             raise ValueError("only one KV head is supported (cmp_sparse_indices.shape[-2] must be 1)")
+        K = ci.shape[2]
         if topk_cmp is not None:
-            assert ci.shape[2] == topk_cmp, "topk_cmp does not match cmp_sparse_indices last dim"
-    if scenario != 1 and (cmp_ratio is None or cmp_ratio <= 0):
-        raise ValueError("cmp_ratio must be a positive integer when cmp_kv is given")
+            assert K == topk_cmp, "topk_cmp does not match cmp_sparse_indices last dim"
+        ci = ci.reshape(T, K).to(device=dev, dtype=torch.int32).contiguous()
+    if scenario != 1:
+        if cmp_ratio is None or cmp_ratio <= 0:
+            raise ValueError("cmp_ratio must be a positive integer when cmp_kv is given")
+        check_inputs([cmp_kv], [q.dtype], ["cmp_kv"])
+    if scenario == 2:
+        # every compressed token below the threshold: the list is as wide as the longest sequence needs (the reference's
+        # front door reads seqused_kv on the host for the same purpose, sparse_flash_mla_api.py:176-180)
+        K = max(-(-(int(seqused_kv.max().item()) // cmp_ratio) // 64) * 64, 64)
 
-    act_kv = seqused_kv.to(device=dev, dtype=torch.int64)
-    pos = act_kv[bid] - len_q[bid] + s_local                      # absolute position of every token
+    def i32(t):
+        return None if t is None else t.to(device=dev, dtype=torch.int32).contiguous()
+
+    cu, used, ori_bt, cmp_bt = i32(cu_seqlens_q), i32(seqused_kv), i32(ori_block_table), i32(cmp_block_table)
     sinks_dev = sinks.to(device=dev, dtype=torch.float32).contiguous()
-
-    # ---- key set 1: the sliding window of the original cache ------------------------------------------------------
     W = ori_win_left + 1
-    w = pos[:, None] - ori_win_left + torch.arange(W, device=dev)[None, :]
-    w_valid = (w >= 0) & exists[:, None] & (pos[:, None] >= 0)
+    ori_rows = torch.empty((1, T, 1, W), dtype=torch.int32, device=dev)
+    cmp_rows = torch.empty((1, T, 1, K), dtype=torch.int32, device=dev) if scenario != 1 else None
     ori_bs = ori_kv.shape[1]
-    ori_rows = _physical_rows(ori_block_table.to(device=dev, dtype=torch.int64), bid, w, w_valid, ori_bs)
+    cmp_bs = cmp_kv.shape[1] if scenario != 1 else 0
+    with torch.cuda.device(dev):
+        _lib.check(lib.dsa_v4_build_indices(ptr(cu), ptr(used), ptr(ori_bt), ptr(cmp_bt), ptr(ci) if scenario == 3 else None, ptr(ori_rows),
+                                            ptr(cmp_rows), B, T, S, 1 if layout_q == "TND" else 0, ori_bt.shape[1], ori_bs, int(ori_win_left),
+                                            cmp_bt.shape[1] if scenario != 1 else 0, cmp_bs, int(cmp_ratio or 0), scenario, K,
+                                            current_stream(dev)))
     q4 = q_flat.reshape(1, T, N1, D)
     pool = ori_kv.reshape(1, ori_kv.shape[0] * ori_bs, 1, D)
-    out_a, lse_a = sparse_mla_fwd_raw(q4, pool, ori_rows.reshape(1, T, 1, W).contiguous(), sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
-
-    # ---- key set 2: compressed tokens ------------------------------------------------------------------------------
+    out_a, lse_a = sparse_mla_fwd_raw(q4, pool, ori_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
     out_b = lse_b = None
     if scenario != 1:
-        check_inputs([cmp_kv], [q.dtype], ["cmp_kv"])
-        threshold = torch.div(pos + 1, cmp_ratio, rounding_mode="floor").clamp_(min=0)
-        cmp_len = torch.div(act_kv[bid], cmp_ratio, rounding_mode="floor")
-        if scenario == 3:
-            ci = ci[:, 0, :].to(device=dev, dtype=torch.int64)
-            K = ci.shape[1]
-            slot = torch.arange(K, device=dev)[None, :]
-            ended = torch.cumsum((ci == -1).to(torch.int32), dim=1) > 0          # a -1 ends the list
-            c_valid = (slot < threshold[:, None]) & ~ended & (ci >= 0) & (ci < torch.minimum(threshold, cmp_len)[:, None])
-            c_pos = ci
-        else:
-            K = max(int(threshold.max().item()) if T > 0 else 0, 1)
-            c_pos = torch.arange(K, device=dev)[None, :].expand(T, K)
-            c_valid = c_pos < threshold[:, None]
-        c_valid = c_valid & exists[:, None]
-        cmp_bs = cmp_kv.shape[1]
-        cmp_rows = _physical_rows(cmp_block_table.to(device=dev, dtype=torch.int64), bid, c_pos, c_valid, cmp_bs)
         cpool = cmp_kv.reshape(1, cmp_kv.shape[0] * cmp_bs, 1, D)
-        out_b, lse_b = sparse_mla_fwd_raw(q4, cpool, cmp_rows.reshape(1, T, 1, K).contiguous(), sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
+        out_b, lse_b = sparse_mla_fwd_raw(q4, cpool, cmp_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
         out_b, lse_b = out_b.reshape(T, N1, D), lse_b.reshape(T, N1)
 
     out, lse = sink_combine_raw(out_a.reshape(T, N1, D), lse_a.reshape(T, N1), out_b, lse_b, sinks_dev, N1)
     if layout_q == "BSND":
-        if not bool(exists.all()):  # padded tokens of short sequences: the reference leaves them at zero
+        if cu is not None:  # padded tokens of short sequences: the reference leaves them at zero
+            exists = (torch.arange(S, device=dev)[None, :] < (cu[1:] - cu[:-1])[:, None]).reshape(T)
             out = out * exists[:, None, None].to(out.dtype)
             lse = lse * exists[:, None].to(lse.dtype)
         out, lse = out.reshape(B, S, N1, D), lse.reshape(B, S, N1)
