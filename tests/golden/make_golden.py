@@ -59,9 +59,12 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("DSA_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("DSA_REFERENCE_ROOT"),
+                    help="root of a checkout of the reference project (or set DSA_REFERENCE_ROOT)")
     args = ap.parse_args()
     ref = args.reference
+    if not ref or not os.path.isdir(ref):
+        raise SystemExit("give the reference checkout with --reference or DSA_REFERENCE_ROOT")
     sys.path.insert(0, os.path.join(HERE, "..", ".."))
     from oracle import dsa_oracle as orc
 
