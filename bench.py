@@ -190,6 +190,25 @@ def measure_v4(dev) -> dict:
     return res
 
 
+def measure_hisa(dev) -> dict:
+    """HISA block-sparse indexer logits on the default shape of the reference's test script
+    (examples/HISA/block_sparse_mqa_attn_expert_test.py:670-680: 1024 queries, 128 K keys, 32 heads x 128 dims, 64 selected
+    blocks of 128 keys, fp16); synthetic tensors."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator(device=dev).manual_seed(3)
+    S, S_kv, H, D, bs, topk = 1024, 128 * 1024, 32, 128, 128, 64
+    q = torch.rand((S, H, D), generator=g, device=dev).to(torch.float16)
+    k = torch.rand((S_kv, D), generator=g, device=dev).to(torch.float16)
+    w = torch.rand((S, H), generator=g, device=dev).to(torch.float16)
+    ks = torch.zeros(S, dtype=torch.int32, device=dev)
+    ke = (torch.arange(1, S + 1, dtype=torch.int32, device=dev) * (S_kv // S)).clamp(max=S_kv)
+    blk = torch.randint(0, S_kv // bs, (S, topk), generator=g, device=dev, dtype=torch.int32)
+    kernel = dsa.block_sparse_mqa_attn_return_logits(S, S_kv, bs, topk, H, D)
+    t = _time_ms(lambda: kernel(q, k, blk, w, ks, ke), reps=5, warm=2)
+    flop = S * topk * bs * H * D * 2
+    return {"ms": t, "tflops": flop / (t * 1e-3) / 1e12, "workload": f"S={S} S_kv={S_kv} heads={H} index_dim={D} topk={topk} blocks of {bs} keys, fp16"}
+
+
 def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     """Lightning indexer + top-k (S_q=4096, S_kv=8192, 64x128) and decode (B=64, S_kv=32768) on one GPU.
     small: the last 1024 queries / 16 sequences only (for profiler captures)."""
@@ -312,9 +331,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "v4"],
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "v4", "hisa"],
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
-                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes")
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
     ap.add_argument("--cpu-sample", type=int, default=4096, help="queries the CPU baseline / parity sample covers")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
@@ -344,6 +363,10 @@ def main() -> None:
 
     w = WORKLOAD
     peaks = load_peaks()
+    if args.stage == "hisa":
+        if rank == 0:
+            print(json.dumps({"hisa_block_sparse_logits": measure_hisa(dev)}), flush=True)
+        return
     if args.stage == "v4":
         if rank == 0:
             print(json.dumps({"sparse_flash_mla_v4": measure_v4(dev)}), flush=True)

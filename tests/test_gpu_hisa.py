@@ -9,7 +9,9 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("S,S_kv,H,D,bs,topk,dtype,wdtype", [
-    (64, 4096, 32, 128, 128, 8, torch.float16, torch.float16),     # the reference test's shape family (fp16)
+    (64, 4096, 32, 128, 128, 8, torch.float16, torch.float16),     # the reference test's shape family (fp16): tensor-core kernel
+    (40, 5000, 64, 128, 128, 12, torch.bfloat16, torch.float32),   # tensor-core kernel, S_kv not a multiple of the block, 64 heads
+    (9, 700, 20, 128, 128, 4, torch.bfloat16, torch.bfloat16),     # tensor-core kernel, head count below 64 and not a multiple of 16
     (33, 1000, 64, 128, 64, 12, torch.bfloat16, torch.float32),    # S_kv not a multiple of the block: the last block is cut
     (5, 300, 7, 64, 48, 4, torch.bfloat16, torch.bfloat16),        # block size that is not a multiple of 32, odd head count
 ])
@@ -25,6 +27,10 @@ def test_block_sparse_logits_match_oracle(S, S_kv, H, D, bs, topk, dtype, wdtype
     kernel = dsa.block_sparse_mqa_attn_return_logits(S, S_kv, bs, topk, H, D, block_N=8 if bs % 8 == 0 else 1)
     out = kernel(q.cuda(), k.cuda(), blk.cuda(), w.cuda(), ks.cuda(), ke.cuda()).cpu()
     check_status()
+    # the CUDA-core kernel on the same inputs (the first case runs on the tensor cores by default)
+    out_c = dsa.block_sparse_logits_raw(q.cuda(), k.cuda(), blk.cuda(), w.cuda(), ks.cuda(), ke.cuda(), bs, impl=1).cpu()
+    assert torch.equal(torch.isinf(out), torch.isinf(out_c))
+    torch.testing.assert_close(out[torch.isfinite(out)], out_c[torch.isfinite(out_c)], rtol=2e-5, atol=2e-4)
     ref = orc.block_sparse_logits(q, k, blk, bs, w, ks, ke)
     assert out.shape == ref.shape == (S, topk, bs)
     assert torch.equal(torch.isinf(out), torch.isinf(ref)), "masked positions differ"

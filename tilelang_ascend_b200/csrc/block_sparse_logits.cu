@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "params.h"
 
 namespace dsa {
@@ -99,4 +101,174 @@ int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cuda
   return static_cast<int>(cudaGetLastError());
 }
 
+}  // namespace dsa
+
+// -------------------------------------------------------------------------------------------------
+// tcgen05 kernel: blocks of 128 keys, index_dim 128, up to 64 heads
+// -------------------------------------------------------------------------------------------------
+// One CTA per query (two resident per SM).  A selected block is one UMMA tile: A = its 128 keys x 128 dims (two
+// K-major chunks of 64 dims in the 128-byte swizzle, fetched row by row with cp.async into a 2-stage ring), B = the
+// query's heads x 128 dims (loaded once, rows beyond the head count are zero), D = 128 keys x 64 heads fp32 in one of two
+// tensor-memory buffers.  The epilogue thread of a key reads its 64 head scores, applies ReLU and the head weights and
+// writes one logit; a warp writes 32 consecutive logits.
+#include "ptx.cuh"
+
+namespace dsa {
+namespace bsltc {
+constexpr int kKeys = 128, kDim = 128, kHeads = 64, kStages = 2, kThreads = 288;
+constexpr uint32_t kChunk = kKeys * 128;                  // 128 keys x 64 dims
+constexpr uint32_t kStageBytes = 2 * kChunk;              // 32 KB
+constexpr uint32_t kOffQ = kStages * kStageBytes;         // B operand: two chunks of [64 heads x 128 B]
+constexpr uint32_t kOffBar = kOffQ + 2 * kHeads * 128;
+constexpr uint32_t kOffW = kOffBar + 128;
+constexpr uint32_t kSmemBytes = kOffW + kHeads * 4 + 1024;
+static_assert(2 * kSmemBytes <= 232448 - 2048, "two CTAs per SM");
+}  // namespace bsltc
+
+template <bool kBF16>
+__global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_kernel(const BlockSparseLogitsParams p) {
+  using namespace bsltc;
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sBase = smem_u32(smem), sQ = sBase + kOffQ;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+  uint64_t* full = bars;          // [2] count 128: the block's rows landed (and were made visible to the tensor core's proxy)
+  uint64_t* empty = bars + 3;     // [2] count 1: commit after the MMAs of the stage
+  uint64_t* d_full = bars + 6;    // [2] count 1: commit after the MMAs of a block
+  uint64_t* d_free = bars + 8;    // [2] count 4: the epilogue warps have read the buffer
+  uint64_t* q_ready = bars + 10;  // count 128
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  float* sw = reinterpret_cast<float*>(smem + kOffW);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, qi = blockIdx.x;
+  // status word: these kernels have none of their own; a failed wait ends the CTA's loops (results of the CTA are then wrong,
+  // which the bounded wait only prevents from becoming a hang)
+  __shared__ int s_status;
+  if (tid == 0) {
+    s_status = kStatusOk;
+    for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 128); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&d_full[i], 1); mbar_init(&d_free[i], 4); }
+    mbar_init(q_ready, 128);
+    mbar_init_fence();
+  }
+  for (int h = tid; h < kHeads; h += kThreads) {
+    float v = 0.f;
+    if (h < p.H) {
+      const int64_t wi = static_cast<int64_t>(qi) * p.H + h;
+      v = p.w_dtype == 2 ? reinterpret_cast<const float*>(p.w)[wi]
+          : p.w_dtype == 0 ? static_cast<float>(reinterpret_cast<const __nv_bfloat16*>(p.w)[wi])
+                           : static_cast<float>(reinterpret_cast<const __half*>(p.w)[wi]);
+    }
+    sw[h] = v;
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tD = *tmem_slot;
+  const int32_t* blocks = p.blocks + static_cast<int64_t>(qi) * p.topk;
+  bool ok = true;
+
+  if (warp >= 4 && warp < 8) {
+    // ================================ loaders: thread = key row of every block ======================
+    const int r = tid - 128;
+    {  // the query's heads: thread r < 64 copies head r (256 bytes), rows without a head are zero-filled
+      if (r < kHeads) {
+        const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(qi) * p.H + (r < p.H ? r : 0)) * (kDim * 2);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) cp_async16(sQ + (u >> 3) * (kHeads * 128) + sw128_offset(r, u & 7), qrow + u * 16, r < p.H ? 16u : 0u);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      mbar_arrive(q_ready);
+    }
+    for (int j = 0; j < p.topk && ok; ++j) {
+      const int s = j % kStages;
+      const int64_t pos = static_cast<int64_t>(blocks[j]) * kKeys + r;
+      const bool in_range = pos >= 0 && pos < p.S_kv;
+      const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.k) + (in_range ? pos : 0) * (kDim * 2);
+      if (j >= kStages && !mbar_wait<true>(&empty[s], ((j / kStages) + 1) & 1, &s_status)) { ok = false; break; }
+      const uint32_t stage = sBase + s * kStageBytes;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) cp_async16(stage + (u >> 3) * kChunk + sw128_offset(r, u & 7), krow + u * 16, in_range ? 16u : 0u);
+      cp_async_commit();
+      // the previous block's rows have landed once only this block's group is outstanding
+      if (j >= 1) {
+        cp_async_wait<1>();
+        fence_proxy_async_smem();
+        mbar_arrive(&full[(j - 1) % kStages]);
+      }
+    }
+    cp_async_wait<0>();
+    if (ok && p.topk >= 1) {
+      fence_proxy_async_smem();
+      mbar_arrive(&full[(p.topk - 1) % kStages]);
+    }
+  } else if (warp == 8) {
+    // ================================ MMA issuer ====================================================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBF16, kKeys, kHeads, 0, 0);
+      ok = mbar_wait(q_ready, 0, &s_status);
+      const uint64_t db0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
+      for (int j = 0; j < p.topk && ok; ++j) {
+        const int s = j % kStages, db = j & 1;
+        if (!mbar_wait(&full[s], (j / kStages) & 1, &s_status)) { ok = false; break; }
+        if (j >= 2 && !mbar_wait(&d_free[db], ((j >> 1) + 1) & 1, &s_status)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t da0 = make_smem_desc(sBase + s * kStageBytes, 16, 1024, kSwizzle128B);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int kq = 0; kq < 4; ++kq)
+            umma_ss(tD + db * kHeads, da0 + ((c * kChunk + kq * 32) >> 4), db0 + ((c * (kHeads * 128) + kq * 32) >> 4), idesc, (c | kq) != 0);
+        }
+        umma_commit(&d_full[db]);
+        umma_commit(&empty[s]);
+      }
+    }
+  } else {
+    // ================================ epilogue: thread = key ========================================
+    const int r = warp * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int lo = p.ks[qi], hi = p.ke[qi];
+    for (int j = 0; j < p.topk && ok; ++j) {
+      const int db = j & 1;
+      const int64_t pos = static_cast<int64_t>(blocks[j]) * kKeys + r;
+      const bool valid = pos >= 0 && pos < p.S_kv && pos >= lo && pos < hi;
+      if (!__all_sync(0xffffffffu, mbar_wait(&d_full[db], (j >> 1) & 1, &s_status))) { ok = false; break; }
+      tc_fence_after();
+      uint32_t v[64];
+      tmem_ld32(tD + db * kHeads + lane_base, v);
+      tmem_ld32(tD + db * kHeads + 32 + lane_base, v + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&d_free[db]);
+      float total = 0.f;
+#pragma unroll
+      for (int h = 0; h < kHeads; ++h) total += sw[h] * fmaxf(__uint_as_float(v[h]), 0.f);
+      p.logits[(static_cast<int64_t>(qi) * p.topk + j) * kKeys + r] = valid ? total : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tD, 128);
+}
+
+bool block_sparse_logits_tc_supported(const BlockSparseLogitsParams& p) {
+  return p.block == bsltc::kKeys && p.D == bsltc::kDim && p.H >= 1 && p.H <= bsltc::kHeads && (reinterpret_cast<uintptr_t>(p.k) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+}
+
+int launch_block_sparse_logits_tc(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream) {
+  auto kern = bf16 ? block_sparse_logits_tc_kernel<true> : block_sparse_logits_tc_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bsltc::kSmemBytes));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<static_cast<unsigned>(p.S), bsltc::kThreads, bsltc::kSmemBytes, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
 }  // namespace dsa

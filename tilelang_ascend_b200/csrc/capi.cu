@@ -28,6 +28,8 @@ int launch_v4_build_indices(const int32_t* cu_q, const int32_t* seqused_kv, cons
                             int32_t* ori_rows, int32_t* cmp_rows, int B, int T, int S, int tnd, int ori_table_len, int ori_bs, int win_left,
                             int cmp_table_len, int cmp_bs, int ratio, int scenario, int K, cudaStream_t stream);
 bool block_sparse_logits_supported(const BlockSparseLogitsParams& p);
+bool block_sparse_logits_tc_supported(const BlockSparseLogitsParams& p);
+int launch_block_sparse_logits_tc(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
 int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
 bool sparse_mla_bwd_tc_supported(const FwdParams& p);
 size_t sparse_mla_bwd_tc_bytes_per_query(int H, int topk);
@@ -304,7 +306,7 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
 
 int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_indices, const void* weights, const int32_t* ks,
                             const int32_t* ke, float* logits, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t kv_block_size,
-                            int32_t topk, int32_t dtype, int32_t weights_dtype, void* stream) {
+                            int32_t topk, int32_t dtype, int32_t weights_dtype, int32_t impl, void* stream) {
   if (!q || !k || !block_indices || !weights || !ks || !ke || !logits) return fail("null tensor pointer");
   if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
   if (weights_dtype < 0 || weights_dtype > 2) return fail("weights_dtype must be 0 (bfloat16), 1 (float16) or 2 (float32)");
@@ -312,7 +314,11 @@ int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_i
   dsa::BlockSparseLogitsParams p{q, k, block_indices, weights, ks, ke, logits, S, S_kv, H, D, kv_block_size, topk, weights_dtype};
   if (!dsa::block_sparse_logits_supported(p)) return fail("block-sparse logits need 1 <= heads <= 64 and index_dim a multiple of 8, at most 256");
   if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u)) return fail("q and k must be 16-byte aligned");
-  int err = dsa::launch_block_sparse_logits(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  // blocks of 128 keys with index_dim 128 and up to 64 heads go to the tensor cores (impl = DSA_IMPL_GENERIC keeps them off)
+  const bool use_tc = impl != DSA_IMPL_GENERIC && dsa::block_sparse_logits_tc_supported(p);
+  if (impl == DSA_IMPL_TENSOR_CORE && !use_tc) return fail("the tensor-core kernel needs kv_block_size = 128, index_dim = 128 and at most 64 heads");
+  int err = use_tc ? dsa::launch_block_sparse_logits_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream))
+                   : dsa::launch_block_sparse_logits(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("block_sparse_logits launch", err) : 0;
 }
 

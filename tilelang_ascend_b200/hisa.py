@@ -11,9 +11,10 @@ from .adapter import check_inputs, current_stream, dtype_code, ptr
 _W_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
-def block_sparse_logits_raw(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke, kv_block_size: int):
+def block_sparse_logits_raw(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke, kv_block_size: int, impl: int = _lib.IMPL_AUTO):
     """One launch through the C ABI.  q [S,H,D], k [S_kv,D], topk_block_indices [S,topk] int32, weights [S,H] (q's dtype or
-    fp32), cu_seqlen_ks / cu_seqlen_ke [S] int32 -> logits [S, topk, kv_block_size] fp32."""
+    fp32), cu_seqlen_ks / cu_seqlen_ke [S] int32 -> logits [S, topk, kv_block_size] fp32.  impl: _lib.IMPL_AUTO (tcgen05 kernel
+    for blocks of 128 keys, index_dim 128, at most 64 heads), IMPL_GENERIC (CUDA cores) or IMPL_TENSOR_CORE."""
     dev = check_inputs([q, k, topk_block_indices, weights, cu_seqlen_ks, cu_seqlen_ke], [None, q.dtype, torch.int32, None, torch.int32, torch.int32],
                        ["q", "k", "topk_block_indices", "weights", "cu_seqlen_ks", "cu_seqlen_ke"])
     if q.dim() != 3 or k.dim() != 2 or k.shape[1] != q.shape[2]:
@@ -28,7 +29,7 @@ def block_sparse_logits_raw(q, k, topk_block_indices, weights, cu_seqlen_ks, cu_
     with torch.cuda.device(dev):
         _lib.check(_lib.load().dsa_block_sparse_logits(ptr(q), ptr(k), ptr(topk_block_indices), ptr(weights), ptr(cu_seqlen_ks), ptr(cu_seqlen_ke),
                                                        ptr(logits), S, k.shape[0], H, D, int(kv_block_size), topk, dtype_code(q.dtype),
-                                                       _W_DTYPES[weights.dtype], current_stream(dev)))
+                                                       _W_DTYPES[weights.dtype], int(impl), current_stream(dev)))
     return logits
 
 
