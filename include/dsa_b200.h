@@ -174,13 +174,18 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
 /* Block-sparse indexer logits (HISA): logits[s, j, b] = sum_h w[s,h] * relu(q[s,h,:] . k[block_indices[s,j] * kv_block_size + b, :]),
  * -inf where that position is outside [0, S_kv) or outside [ks[s], ke[s]).  q [S,H,D], k [S_kv,D] (dtype), block_indices
  * [S,topk] int32, weights [S,H] (weights_dtype: 0 bf16, 1 fp16, 2 fp32), ks / ke [S] int32, logits [S,topk,kv_block_size] fp32.
+ * Paged keys: with block_table [B, max_blocks] (else NULL) k is the cache [num_phys_blocks, kv_block_size, 1, D], the indices
+ * name LOGICAL blocks of the sequence of query s (sequence = s / tokens_per_seq) and S_kv is ignored; this is the kernel of
+ * paged_block_sparse_mqa_attn_return_logits (examples/HISA/paged_block_sparse_mqa_attn_expert.py:54-420, golden :425-468)
+ * with ks = 0 and ke = the sequence's context length.
  * impl: DSA_IMPL_AUTO = the tcgen05 kernel when kv_block_size = 128, D = 128 and H <= 64, else CUDA cores; DSA_IMPL_GENERIC /
  * DSA_IMPL_TENSOR_CORE force one.
  * Replaces the kernel of block_sparse_mqa_attn_return_logits (examples/HISA/block_sparse_mqa_attn_expert_test.py:24-545;
  * golden ref_block_sparse_mqa_attn :548-587). */
 int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_indices, const void* weights, const int32_t* ks,
                             const int32_t* ke, float* logits, int32_t S, int32_t S_kv, int32_t H, int32_t D,
-                            int32_t kv_block_size, int32_t topk, int32_t dtype, int32_t weights_dtype, int32_t impl, void* stream);
+                            int32_t kv_block_size, int32_t topk, int32_t dtype, int32_t weights_dtype, int32_t impl,
+                            const int32_t* block_table, int32_t max_blocks, int32_t tokens_per_seq, void* stream);
 
 /* Index lists of sparse_flash_mla for T query tokens: ori_rows [T, ori_win_left + 1] and cmp_rows [T, K] int32 receive the
  * physical row numbers (block_table[b, pos / block_size] * block_size + pos % block_size) of each token's sliding window

@@ -346,6 +346,22 @@ def block_sparse_logits(q: torch.Tensor, k: torch.Tensor, topk_block_indices: to
     return logits.masked_fill(bad, NEG_INF)
 
 
+def paged_block_sparse_logits(q: torch.Tensor, kv_cache: torch.Tensor, topk_block_indices: torch.Tensor, kv_block_size: int,
+                              weights: torch.Tensor, context_lens: torch.Tensor, block_tables: torch.Tensor) -> torch.Tensor:
+    """Paged variant: q [B,S,H,D], kv_cache [blocks, bs, 1, D], topk_block_indices [B,S,topk] (logical blocks), weights [B,S,H],
+    context_lens [B], block_tables [B, max_blocks] -> logits [B, S, topk * bs] fp32, -inf at logical positions >= the context
+    length.  Follows ref_paged_block_sparse_mqa_attn (examples/HISA/paged_block_sparse_mqa_attn_expert.py:425-468)."""
+    B, S, H, D = q.shape
+    topk = topk_block_indices.shape[2]
+    phys = torch.gather(block_tables.long(), 1, topk_block_indices.long().reshape(B, S * topk)).reshape(B, S, topk)
+    kb = kv_cache.float()[:, :, 0, :][phys]                                     # [B, S, topk, bs, D]
+    sc = torch.einsum("bshd,bstnd->bstnh", q.float(), kb).relu() * weights.float()[:, :, None, None, :]
+    logits = sc.sum(-1)                                                         # [B, S, topk, bs]
+    pos = topk_block_indices.long()[..., None] * kv_block_size + torch.arange(kv_block_size)
+    logits = logits.masked_fill(pos >= context_lens.long()[:, None, None, None], NEG_INF)
+    return logits.reshape(B, S, topk * kv_block_size)
+
+
 # ---------------------------------------------------------------------------
 # seeded synthetic inputs of the benchmark configurations
 # ---------------------------------------------------------------------------

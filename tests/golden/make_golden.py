@@ -171,6 +171,19 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "hisa_block_sparse_logits.npz"), q=bits(qh), k=bits(kh), w=bits(wh), ks=ks_.numpy(), ke=ke_.numpy(),
                         blk=blk.numpy(), bs=np.int64(bs), logits=hl.numpy())
 
+    env = load_functions(os.path.join(ref, "examples/HISA/paged_block_sparse_mqa_attn_expert.py"), ["ref_paged_block_sparse_mqa_attn"])
+    g = torch.Generator().manual_seed(22)
+    B, S, H, D, bs, topk, maxb, nphys = 2, 3, 8, 32, 16, 4, 6, 14
+    qp = torch.rand((B, S, H, D), generator=g).to(torch.float16) - 0.5
+    cache = torch.rand((nphys, bs, 1, D), generator=g).to(torch.float16) - 0.5
+    wp = (torch.rand((B, S, H), generator=g) - 0.3).to(torch.float16)
+    ctx = torch.tensor([70, 41], dtype=torch.int32)
+    bt = torch.stack([torch.randperm(nphys, generator=g)[:maxb] for _ in range(B)]).to(torch.int32)
+    blkp = torch.randint(0, maxb, (B, S, topk), generator=g, dtype=torch.int32)
+    pl = env["ref_paged_block_sparse_mqa_attn"](qp, cache, blkp, bs, wp, ctx, bt)
+    np.savez_compressed(os.path.join(HERE, "hisa_paged_logits.npz"), q=bits(qp), cache=bits(cache), w=bits(wp), ctx=ctx.numpy(), bt=bt.numpy(),
+                        blk=blkp.numpy(), bs=np.int64(bs), logits=pl.numpy())
+
     # ---- lightning indexer, production golden ---------------------------------------------------
     env = load_functions(os.path.join(ref, "examples/deepseek_v4/lightning_indexer.py"),
                          ["_NEG_INF", "cpu_lightning_indexer"])

@@ -49,3 +49,25 @@ def test_block_sparse_logits_argument_checks():
         kernel(q, torch.zeros((64, 16), dtype=torch.float16, device="cuda"), torch.zeros((8, 4), dtype=torch.int32, device="cuda"),
                torch.zeros((8, 4), dtype=torch.float16, device="cuda"), torch.zeros(8, dtype=torch.int32, device="cuda"),
                torch.zeros(8, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("B,S,H,D,bs,topk,maxb,nphys", [
+    (2, 5, 32, 128, 128, 8, 20, 48),     # tensor-core kernel
+    (3, 2, 12, 64, 32, 4, 9, 30),        # CUDA-core kernel
+])
+def test_paged_block_sparse_logits_match_oracle(B, S, H, D, bs, topk, maxb, nphys):
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator().manual_seed(B * 7 + S)
+    q = (torch.rand((B, S, H, D), generator=g) - 0.5).to(torch.float16)
+    cache = (torch.rand((nphys, bs, 1, D), generator=g) - 0.5).to(torch.float16)
+    w = (torch.rand((B, S, H), generator=g) - 0.3).to(torch.float16)
+    ctx = torch.randint(bs, maxb * bs, (B,), generator=g, dtype=torch.int32)
+    bt = torch.stack([torch.randperm(nphys, generator=g)[:maxb] for _ in range(B)]).to(torch.int32)
+    blk = torch.randint(0, maxb, (B, S, topk), generator=g, dtype=torch.int32)
+    kernel = dsa.paged_block_sparse_mqa_attn_return_logits(B, S, nphys, bs, topk, H, D, maxb)
+    out = kernel(q.view(B * S, H, D).cuda(), cache.cuda(), blk.view(B * S, topk).cuda(), w.view(B * S, H).cuda(), ctx.cuda(), bt.cuda()).cpu()
+    check_status()
+    ref = orc.paged_block_sparse_logits(q, cache, blk, bs, w, ctx, bt).reshape(B * S, topk, bs)
+    assert torch.equal(torch.isinf(out), torch.isinf(ref)), "masked positions differ"
+    fin = torch.isfinite(ref)
+    torch.testing.assert_close(out[fin], ref[fin], rtol=2e-5, atol=2e-4)

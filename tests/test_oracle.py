@@ -82,6 +82,16 @@ def test_block_sparse_logits_match_reference_golden(golden):
     torch.testing.assert_close(out[fin], ref[fin], rtol=1e-5, atol=1e-5)
 
 
+def test_paged_block_sparse_logits_match_reference_golden(golden):
+    g = golden("hisa_paged_logits.npz")
+    q, cache, w = from_bits(g["q"], torch.float16), from_bits(g["cache"], torch.float16), from_bits(g["w"], torch.float16)
+    out = orc.paged_block_sparse_logits(q, cache, torch.from_numpy(g["blk"]), int(g["bs"]), w, torch.from_numpy(g["ctx"]), torch.from_numpy(g["bt"]))
+    ref = torch.from_numpy(g["logits"])
+    assert torch.equal(torch.isinf(out), torch.isinf(ref))
+    fin = torch.isfinite(ref)
+    torch.testing.assert_close(out[fin], ref[fin], rtol=1e-5, atol=1e-5)
+
+
 def test_lightning_indexer_matches_reference_golden(golden):
     g = golden("lightning_indexer.npz")
     for tag in ("causal", "full", "ties"):

@@ -3,7 +3,7 @@ the TileLang-Ascend examples: lightning indexer -> top-k selector -> sparse MLA 
 backward).  Python / PyTorch host code over a C-ABI CUDA library; there is no CPU fallback."""
 from . import _lib
 from .deepseek_mla import mla_decode
-from .hisa import block_sparse_logits_raw, block_sparse_mqa_attn_return_logits
+from .hisa import block_sparse_logits_raw, block_sparse_mqa_attn_return_logits, paged_block_sparse_mqa_attn_return_logits
 from .host_pipeline import HostPipelinedForward
 from .lightning_indexer import indexer, indexer_scores_raw, lightning_indexer, lightning_indexer_raw
 from .sharding import shard_batch, shard_queries, shard_range, all_reduce_key_gradient, sparse_mla_bwd_sharded
@@ -16,6 +16,6 @@ kernel_status = _lib.kernel_status
 
 __all__ = [
     "indexer", "lightning_indexer", "simple_topk_selector", "sparse_attention_fwd", "sparse_attn_tilelang", "mla_decode",
-    "sparse_flash_mla", "sink_combine_raw", "block_sparse_mqa_attn_return_logits", "block_sparse_logits_raw", "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
+    "sparse_flash_mla", "sink_combine_raw", "block_sparse_mqa_attn_return_logits", "paged_block_sparse_mqa_attn_return_logits", "block_sparse_logits_raw", "sparse_mla", "sparse_mla_fwd_raw", "sparse_mla_bwd_raw", "indexer_scores_raw", "lightning_indexer_raw",
     "topk_select_raw", "HostPipelinedForward", "shard_range", "shard_queries", "shard_batch", "all_reduce_key_gradient", "sparse_mla_bwd_sharded", "kernel_status",
 ]

@@ -45,7 +45,7 @@ SIGNATURES = {
                                      c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                      c_void_p]),
     "dsa_block_sparse_logits": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
-                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_int32, c_int32, c_void_p]),
     "dsa_v4_build_indices": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int32] * 12 + [c_void_p]),
     "dsa_sink_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                    c_int32, c_void_p]),

@@ -52,14 +52,16 @@ __global__ void __launch_bounds__(bsl::kThreads) block_sparse_logits_kernel(cons
     const int j = j0 + item / chunks, c = item % chunks;
     if (j >= p.topk) break;
     const int off = c * 32 + lane;
-    const int64_t pos = static_cast<int64_t>(p.blocks[static_cast<int64_t>(qi) * p.topk + j]) * p.block + off;
+    const int blk = p.blocks[static_cast<int64_t>(qi) * p.topk + j];
+    const int64_t pos = static_cast<int64_t>(blk) * p.block + off;   // logical position
     const bool in_block = off < p.block;
-    const bool valid = in_block && pos >= 0 && pos < p.S_kv && pos >= lo && pos < hi;
+    const bool valid = in_block && blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
+    const int64_t row = !valid ? 0 : p.block_table ? static_cast<int64_t>(p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk]) * p.block + off : pos;
     float acc[kMaxH];
 #pragma unroll
     for (int h = 0; h < kMaxH; ++h) acc[h] = 0.f;
     if (valid) {
-      const uint4* krow = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.k) + pos * p.D);
+      const uint4* krow = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.k) + row * p.D);
       for (int d0 = 0; d0 < p.D; d0 += 8) {
         float kf[8];
         unpack8<T>(__ldg(krow + (d0 >> 3)), kf);
@@ -188,9 +190,11 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
     }
     for (int j = 0; j < p.topk && ok; ++j) {
       const int s = j % kStages;
-      const int64_t pos = static_cast<int64_t>(blocks[j]) * kKeys + r;
-      const bool in_range = pos >= 0 && pos < p.S_kv;
-      const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.k) + (in_range ? pos : 0) * (kDim * 2);
+      const int blk = blocks[j];
+      const int64_t pos = static_cast<int64_t>(blk) * kKeys + r;
+      const bool in_range = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv);
+      const int64_t row = !in_range ? 0 : p.block_table ? static_cast<int64_t>(p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk]) * kKeys + r : pos;
+      const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.k) + row * (kDim * 2);
       if (j >= kStages && !mbar_wait<true>(&empty[s], ((j / kStages) + 1) & 1, &s_status)) { ok = false; break; }
       const uint32_t stage = sBase + s * kStageBytes;
 #pragma unroll
@@ -237,8 +241,9 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
     const int lo = p.ks[qi], hi = p.ke[qi];
     for (int j = 0; j < p.topk && ok; ++j) {
       const int db = j & 1;
-      const int64_t pos = static_cast<int64_t>(blocks[j]) * kKeys + r;
-      const bool valid = pos >= 0 && pos < p.S_kv && pos >= lo && pos < hi;
+      const int blk = blocks[j];
+      const int64_t pos = static_cast<int64_t>(blk) * kKeys + r;
+      const bool valid = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
       if (!__all_sync(0xffffffffu, mbar_wait(&d_full[db], (j >> 1) & 1, &s_status))) { ok = false; break; }
       tc_fence_after();
       uint32_t v[64];

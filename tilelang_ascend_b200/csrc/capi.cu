@@ -306,12 +306,15 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
 
 int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_indices, const void* weights, const int32_t* ks,
                             const int32_t* ke, float* logits, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t kv_block_size,
-                            int32_t topk, int32_t dtype, int32_t weights_dtype, int32_t impl, void* stream) {
+                            int32_t topk, int32_t dtype, int32_t weights_dtype, int32_t impl, const int32_t* block_table, int32_t max_blocks,
+                            int32_t tokens_per_seq, void* stream) {
   if (!q || !k || !block_indices || !weights || !ks || !ke || !logits) return fail("null tensor pointer");
   if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
   if (weights_dtype < 0 || weights_dtype > 2) return fail("weights_dtype must be 0 (bfloat16), 1 (float16) or 2 (float32)");
   if (S <= 0 || S_kv <= 0 || kv_block_size <= 0 || topk <= 0) return fail("S, S_kv, kv_block_size and topk must be positive");
-  dsa::BlockSparseLogitsParams p{q, k, block_indices, weights, ks, ke, logits, S, S_kv, H, D, kv_block_size, topk, weights_dtype};
+  if (block_table && (max_blocks <= 0 || tokens_per_seq <= 0)) return fail("max_blocks and tokens_per_seq must be positive with a block table");
+  dsa::BlockSparseLogitsParams p{q, k, block_indices, weights, ks, ke, logits, S, S_kv, H, D, kv_block_size, topk, weights_dtype,
+                                 block_table, max_blocks, tokens_per_seq};
   if (!dsa::block_sparse_logits_supported(p)) return fail("block-sparse logits need 1 <= heads <= 64 and index_dim a multiple of 8, at most 256");
   if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u)) return fail("q and k must be 16-byte aligned");
   // blocks of 128 keys with index_dim 128 and up to 64 heads go to the tensor cores (impl = DSA_IMPL_GENERIC keeps them off)

@@ -73,6 +73,10 @@ struct BlockSparseLogitsParams {
   float* logits;            // [S, topk, block]
   int S, S_kv, H, D, block, topk;
   int w_dtype;              // 0 bf16, 1 fp16, 2 fp32
+  // paged keys (nullable): k is [num_phys_blocks, block, 1, D]; logical block j of the sequence of query s sits at
+  // block_table[(s / tokens_per_seq) * max_blocks + j]
+  const int32_t* block_table;
+  int max_blocks, tokens_per_seq;
 };
 
 }  // namespace dsa
