@@ -215,7 +215,8 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
   } else if (warp == 8) {
     // ================================ MMA issuer ====================================================
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBF16, kKeys, kHeads, 0, 0);
+      // UMMA N = the head count rounded up to 16 (rows of the B image beyond the head count are zero)
+      const uint32_t idesc = make_idesc_f16(kBF16, kKeys, static_cast<uint32_t>((p.H + 15) & ~15), 0, 0);
       ok = mbar_wait(q_ready, 0, &s_status);
       const uint64_t db0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
       for (int j = 0; j < p.topk && ok; ++j) {
@@ -248,8 +249,17 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
       tc_fence_after();
       uint32_t v[64];
       tmem_ld32(tD + db * kHeads + lane_base, v);
-      tmem_ld32(tD + db * kHeads + 32 + lane_base, v + 32);
+      if (p.H > 32) {
+        tmem_ld32(tD + db * kHeads + 32 + lane_base, v + 32);
+      } else {  // columns the MMAs do not write are not read
+#pragma unroll
+        for (int h = 32; h < 64; ++h) v[h] = 0u;
+      }
       tmem_wait_ld();
+      if (p.H <= 16) {
+#pragma unroll
+        for (int h = 16; h < 32; ++h) v[h] = 0u;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&d_free[db]);
