@@ -83,6 +83,20 @@ int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t 
                           int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
                           void* stream);
 
+/* dsa_lightning_indexer over a PAGED key cache: k_cache [num_blocks, block_size, 1, D] (dtype), block_table [B, max_blocks]
+ * int32; logical key j of batch b is cache row block_table[b, j / block_size] * block_size + j % block_size.  S2 is the
+ * largest logical key count (max_blocks * block_size >= S2); k_len_b [B] gives each sequence's count.  Table entries that
+ * are padding (negative, or >= num_blocks) are never dereferenced; keys they would name lie beyond k_len_b in a well-formed
+ * call.  The tensor-core kernel addresses the cache through the table tile by tile (TMA boxes inside one block when the
+ * block size has a power-of-two factor >= 8, per-row copies otherwise): no dense copy of the keys is made.
+ * Replaces the PA_BSND path of the kernel launched by lightning_indexer(..., layout_key="PA_BSND", block_table=...)
+ * (examples/deepseek_v4/lightning_indexer.py:1256-1305; paged cube loads :661-793). */
+int dsa_lightning_indexer_paged(const void* q, const void* k_cache, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1,
+                                int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b,
+                                const int32_t* block_table, int32_t block_size, int32_t max_blocks, int32_t num_blocks,
+                                int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 /* Size in bytes of the scratch array built into the library image (per GPU, held until the process exits). */
 #define DSA_NOALLOC_SCRATCH_BYTES (32u << 20)
 size_t dsa_lightning_indexer_noalloc_max_bytes(void);
@@ -97,6 +111,9 @@ size_t dsa_lightning_indexer_noalloc_max_bytes(void);
  * Limits: 256 + round256(4 B S1) + 4 B S1 S2 bytes must fit the array, otherwise the call fails with a
  * message and launches nothing.  The first call on each device resolves the array's device address
  * (cudaGetSymbolAddress) with that device current: make that first call before any stream capture begins.
+ * The array itself is reserved on a GPU when the library's device code is loaded there, which with CUDA's lazy loading
+ * is the first call into the library on that device: a caller that then takes all remaining device memory for its own
+ * pool must make that first call BEFORE the grab, or the load will fail for lack of memory.
  * All calls on a device share the one array and it keeps the previous call's contents (the call clears the
  * status word itself; nothing else needs to start at zero).  Two calls that overlap on the GPU -- different
  * streams, or different host threads -- race on it: serialise them. */

@@ -267,6 +267,30 @@ def mla_decode(q: torch.Tensor, q_pe: torch.Tensor, kv: torch.Tensor, k_pe: torc
     return torch.matmul(torch.softmax(s, dim=-1), k2)
 
 
+def mla_decode_paged(q: torch.Tensor, q_pe: torch.Tensor, kv_pool: torch.Tensor, k_pe_pool: torch.Tensor, block_table: torch.Tensor,
+                     cache_seqlens, block_size: int, softmax_scale: float = 1.0) -> torch.Tensor:
+    """Dense MLA decode over a paged cache in fp32 -> [B,H,dv] fp32.  kv_pool [rows,1,dv], k_pe_pool [rows,1,dpe]; logical
+    position p of sequence b is pool row block_table[b, p // block_size] * block_size + p % block_size; the first
+    cache_seqlens[b] positions take part.  ``softmax_scale`` multiplies the scores (the reference test passes 1.0 because
+    its Q is pre-scaled).
+
+    Follows golden_mla_decode_paged,
+    examples_experiment/deepseek_mla/example_mla_decode_paged/test_mla_decode_paged.py:35-87.
+    """
+    B, H, dv = q.shape
+    out = torch.zeros((B, H, dv), dtype=torch.float32)
+    bt = block_table.long()
+    for b in range(B):
+        n = int(cache_seqlens[b])
+        pos = torch.arange(n)
+        rows = bt[b, pos // block_size] * block_size + pos % block_size
+        k2 = kv_pool[rows, 0, :].float()
+        p2 = k_pe_pool[rows, 0, :].float()
+        s = (q[b].float() @ k2.T + q_pe[b].float() @ p2.T) * float(softmax_scale)
+        out[b] = torch.softmax(s, dim=-1) @ k2
+    return out
+
+
 # ---------------------------------------------------------------------------
 # DeepSeek-V4 sparse_flash_mla: sliding window + compressed tokens + sink
 # ---------------------------------------------------------------------------

@@ -235,6 +235,38 @@ def main() -> None:
     out = env["ref_mla_decode"](q, q_pe, kv, k_pe)
     np.savez_compressed(os.path.join(HERE, "mla_decode.npz"), q=bits(q), q_pe=bits(q_pe), kv=bits(kv), k_pe=bits(k_pe),
                         out=bits(out))
+    # ---- dense MLA decode, paged cache (the caller pre-scales Q; the golden is called with scale 1) -----
+    env = load_functions(os.path.join(ref, "examples_experiment/deepseek_mla/example_mla_decode_paged/test_mla_decode_paged.py"),
+                         ["golden_mla_decode_paged"])
+    g = torch.Generator().manual_seed(6)
+    B, H, dv, dpe, bs, nblk = 2, 16, 512, 64, 64, 3
+    seqlens = torch.tensor([150, 150], dtype=torch.int32)   # a tail inside the third block
+    qf = (torch.randn((B, H, dv + dpe), generator=g) * (dv + dpe) ** -0.5).half()
+    pool = torch.randn((B * nblk, bs, 1, dv + dpe), generator=g).half()
+    btp = torch.randperm(B * nblk, generator=g).to(torch.int32).view(B, nblk)
+    kvp = pool[..., :dv].reshape(-1, 1, dv).contiguous()
+    kpp = pool[..., dv:].reshape(-1, 1, dpe).contiguous()
+    outp = env["golden_mla_decode_paged"](qf[..., :dv].contiguous(), qf[..., dv:].contiguous(), kvp, kpp, btp, seqlens, B, H, 1, dv, dpe,
+                                          bs, nblk * bs, softmax_scale=1.0)
+    np.savez_compressed(os.path.join(HERE, "mla_decode_paged.npz"), q=bits(qf), pool=bits(pool), block_table=btp.numpy(),
+                        seqlen=np.int64(150), block_size=np.int64(bs), out=bits(outp))
+
+    # ---- dense MLA decode, persistent variant's golden (einops path when einops is importable, as in the reference) -----
+    try:
+        from einops import einsum as _einsum, rearrange as _rearrange
+    except ImportError:
+        _einsum = _rearrange = None
+    env = load_functions(os.path.join(ref, "examples_experiment/deepseek_mla/example_mla_decode_persistent/test_mla_decode_persistent.py"),
+                         ["ref_mla_decode"], {"rearrange": _rearrange, "einsum": _einsum})
+    g = torch.Generator().manual_seed(8)
+    B, H, N, D, pe = 2, 64, 192, 512, 64
+    q = torch.randn((B, H, D), generator=g).half()
+    q_pe = torch.randn((B, H, pe), generator=g).half()
+    kv = torch.randn((B, N, 1, D), generator=g).half()
+    k_pe = torch.randn((B, N, 1, pe), generator=g).half()
+    out = env["ref_mla_decode"](q, q_pe, kv, k_pe)
+    np.savez_compressed(os.path.join(HERE, "mla_decode_persistent.npz"), q=bits(q), q_pe=bits(q_pe), kv=bits(kv), k_pe=bits(k_pe),
+                        out=bits(out))
     print("golden fixtures written to", HERE)
 
 

@@ -141,3 +141,119 @@ def test_tma_and_cp_async_key_tiles_agree(monkeypatch):
     assert torch.equal(a[fin], b[fin])
     ref = orc.indexer_scores(q.cpu(), k.cpu(), w.cpu(), sparse_mode=3)
     _scores_close(a.cpu().numpy(), ref.numpy() if hasattr(ref, "numpy") else np.asarray(ref))
+
+
+def _build_paged(k: torch.Tensor, act_k, block_size: int, block_num: int, seed: int = 42):
+    """Scatter BSND keys [B, S2, 1, D] into a paged cache [block_num, block_size, 1, D] with a shuffled block table whose
+    unused entries are -1 (the construction of the reference's own examples,
+    examples/deepseek_v4/lightning_indexer.py:1505-1533)."""
+    B, S2, _, D = k.shape
+    cols = -(-S2 // block_size)
+    perm = np.random.default_rng(seed).permutation(block_num)
+    bt = np.full((B, max(cols, 1)), -1, dtype=np.int32)
+    cache = torch.zeros((block_num, block_size, 1, D), dtype=k.dtype)
+    c = 0
+    for b in range(B):
+        for i in range(-(-int(act_k[b]) // block_size)):
+            bt[b, i] = perm[c]
+            s0, s1 = i * block_size, min((i + 1) * block_size, int(act_k[b]))
+            cache[perm[c], : s1 - s0] = k[b, s0:s1]
+            c += 1
+    return cache, torch.from_numpy(bt)
+
+
+@pytest.mark.parametrize("block_size,N1,no_tma", [(128, 64, False), (256, 32, False), (48, 16, False), (16, 8, False),
+                                                  (128, 64, True), (80, 16, True), (64, 5, False)])
+def test_paged_keys_match_dense_keys(block_size, N1, no_tma, monkeypatch):
+    """layout_key="PA_BSND": the kernel walks the cache through the block table (TMA boxes inside a block, per-row copies
+    when DSA_INDEXER_NO_TMA is set, CUDA cores for a head count the tensor-core kernel does not take); the result must be
+    bit-equal to the dense-key call on the same logical keys, and equal to the oracle."""
+    import tilelang_ascend_b200 as dsa
+    if no_tma:
+        monkeypatch.setenv("DSA_INDEXER_NO_TMA", "1")
+    B, S1, S2, K = 2, 33, 1000, 256
+    act_k = [1000, 517]
+    q, k, w = orc.make_indexer_inputs(B, S1, S2, N1, 128, seed=block_size + N1)
+    k[1, act_k[1]:] = 0
+    nblk = sum(-(-a // block_size) for a in act_k) + 5
+    cache, bt = _build_paged(k, act_k, block_size, nblk)
+    aq = torch.tensor([S1, 20])
+    ak = torch.tensor(act_k)
+    dense_idx, _ = dsa.lightning_indexer(q.cuda(), k.cuda(), w.cuda(), actual_seq_lengths_query=aq, actual_seq_lengths_key=ak,
+                                         sparse_count=K, sparse_mode=3)
+    paged_idx, vals = dsa.lightning_indexer(q.cuda(), cache.cuda(), w.cuda(), actual_seq_lengths_query=aq, actual_seq_lengths_key=ak,
+                                            block_table=bt.cuda(), layout_key="PA_BSND", sparse_count=K, sparse_mode=3)
+    check_status()
+    assert vals.numel() == 0
+    assert torch.equal(paged_idx, dense_idx)
+    ref = orc.lightning_indexer(q, k, w, sparse_count=K, sparse_mode=3, actual_seq_lengths_query=aq, actual_seq_lengths_key=ak).numpy()
+    got = paged_idx.cpu().numpy()
+    for b in range(B):
+        sc = orc.indexer_scores(q[b:b + 1], k[b:b + 1], w[b:b + 1], sparse_mode=3, actual_q=int(aq[b]), actual_k=act_k[b])[0].numpy()
+        n = int(aq[b])
+        same, rows = topk_three_step(got[b, :n, 0], ref[b, :n, 0], sc, K)
+        assert same >= rows - 1
+        assert (got[b, n:] == -1).all()
+    with pytest.raises(ValueError, match="return_value"):
+        dsa.lightning_indexer(q.cuda(), cache.cuda(), w.cuda(), block_table=bt.cuda(), layout_key="PA_BSND", return_value=True)
+
+
+def _uniform(shape, g, absolute=False):
+    x = (torch.rand(shape, generator=g) * 2 - 1).half()
+    return x.abs() if absolute else x
+
+
+def test_reference_layout_scenarios():
+    """The four layout scenarios the reference runs against its CPU golden (examples/deepseek_v4/lightning_indexer.py:1574-1647;
+    fp16 uniform(-1, 1) inputs, non-negative weights), checked with the reference's 3-step rule against the oracle."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator().manual_seed(0)
+
+    def check(idx, q, k, w, aq, ak, K, mode):
+        ref = orc.lightning_indexer(q, k, w, sparse_count=K, sparse_mode=mode, actual_seq_lengths_query=aq, actual_seq_lengths_key=ak).numpy()
+        for b in range(q.shape[0]):
+            n = int(aq[b])
+            sc = orc.indexer_scores(q[b:b + 1], k[b:b + 1], w[b:b + 1], sparse_mode=mode, actual_q=n, actual_k=int(ak[b]))[0].numpy()
+            assert np.array_equal(idx[b, :n] < 0, ref[b, :n, 0] < 0)
+            topk_three_step(idx[b, :n], ref[b, :n, 0], sc, K)
+
+    # 1: BSND + BSND, B=2, S1=3, S2=32768, 64 heads, top 2048, causal
+    B, S1, S2, N1, K = 2, 3, 32768, 64, 2048
+    q, k, w = _uniform((B, S1, N1, 128), g), _uniform((B, S2, 1, 128), g), _uniform((B, S1, N1), g, True)
+    idx, val = dsa.lightning_indexer(q.cuda(), k.cuda(), w.cuda(), actual_seq_lengths_query=torch.full((B,), S1), actual_seq_lengths_key=torch.full((B,), S2),
+                                     sparse_count=K, sparse_mode=3, return_value=True)
+    check(idx.cpu().numpy().reshape(B, S1, K), q, k, w.float(), [S1] * B, [S2] * B, K, 3)
+    assert val.dtype == torch.float16 and val.numel() == B * S1 * K
+
+    # 2: BSND + PA_BSND, B=2, S1=1, 8 heads, blocks of 128, 32 blocks, keys 1024 / 2048, all keys candidates
+    B, S1, N1, K, bs, nb, act_k = 2, 1, 8, 2048, 128, 32, [1024, 2048]
+    q, w, k = _uniform((B, S1, N1, 128), g), _uniform((B, S1, N1), g, True), _uniform((B, max(act_k), 1, 128), g)
+    cache, bt = _build_paged(k, act_k, bs, nb)
+    bt_full = torch.full((B, nb), -1, dtype=torch.int32)
+    bt_full[:, :bt.shape[1]] = bt
+    idx, _ = dsa.lightning_indexer(q.cuda(), cache.cuda(), w.cuda(), actual_seq_lengths_query=torch.full((B,), S1), actual_seq_lengths_key=torch.tensor(act_k),
+                                   block_table=bt_full.cuda(), layout_key="PA_BSND", sparse_count=K, sparse_mode=0)
+    check(idx.cpu().numpy().reshape(B, S1, K), q, k, w.float(), [S1] * B, act_k, K, 0)
+
+    # 3: TND + TND, B=8, S1=64, S2=3072, 24 heads, all keys candidates
+    B, S1, S2, N1 = 8, 64, 3072, 24
+    q, k, w = _uniform((B * S1, N1, 128), g), _uniform((B * S2, 1, 128), g), _uniform((B * S1, N1), g, True)
+    idx, _ = dsa.lightning_indexer(q.cuda(), k.cuda(), w.cuda(), actual_seq_lengths_query=torch.arange(1, B + 1) * S1,
+                                   actual_seq_lengths_key=torch.arange(1, B + 1) * S2, layout_query="TND", layout_key="TND", sparse_count=K, sparse_mode=0)
+    check(idx.cpu().numpy().reshape(B, S1, K), q.view(B, S1, N1, 128), k.view(B, S2, 1, 128), w.view(B, S1, N1).float(), [S1] * B, [S2] * B, K, 0)
+
+    # 4: TND + PA_BSND, 8 heads, blocks of 128, queries 1024 / 2048 (here 96 / 160: the CPU oracle is the slow part), keys 4096 / 8192
+    N1, bs, nb, act_q, act_k = 8, 128, 128, [96, 160], [4096, 8192]
+    q, w, k = _uniform((sum(act_q), N1, 128), g), _uniform((sum(act_q), N1), g, True), _uniform((2, max(act_k), 1, 128), g)
+    cache, bt = _build_paged(k, act_k, bs, nb)
+    idx, _ = dsa.lightning_indexer(q.cuda(), cache.cuda(), w.cuda(), actual_seq_lengths_query=torch.tensor(act_q).cumsum(0),
+                                   actual_seq_lengths_key=torch.tensor(act_k), block_table=bt.cuda(), layout_query="TND", layout_key="PA_BSND",
+                                   sparse_count=K, sparse_mode=0)
+    idx = idx.cpu().numpy().reshape(sum(act_q), K)
+    qp, wp = torch.zeros((2, max(act_q), N1, 128), dtype=torch.float16), torch.zeros((2, max(act_q), N1))
+    qp[0, :96], qp[1] = q[:96], q[96:]
+    wp[0, :96], wp[1] = w[:96].float(), w[96:].float()
+    ip = np.full((2, max(act_q), K), -1, dtype=np.int32)
+    ip[0, :96], ip[1] = idx[:96], idx[96:]
+    check(ip, qp, k, wp, act_q, act_k, K, 0)
+    check_status()

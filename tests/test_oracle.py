@@ -142,6 +142,24 @@ def test_mla_decode_matches_reference_golden(golden):
     torch.testing.assert_close(out, from_bits(g["out"], h).float(), rtol=2e-3, atol=1e-3)
 
 
+def test_mla_decode_paged_matches_reference_golden(golden):
+    g = golden("mla_decode_paged.npz")
+    h = torch.float16
+    q, pool = from_bits(g["q"], h), from_bits(g["pool"], h)
+    bs, n = int(g["block_size"]), int(g["seqlen"])
+    B = q.shape[0]
+    out = orc.mla_decode_paged(q[..., :512], q[..., 512:], pool[..., :512].reshape(-1, 1, 512), pool[..., 512:].reshape(-1, 1, 64),
+                               torch.from_numpy(g["block_table"]), [n] * B, bs, softmax_scale=1.0)
+    torch.testing.assert_close(out, from_bits(g["out"], h).float(), rtol=2e-3, atol=1e-3)
+
+
+def test_mla_decode_matches_persistent_variant_golden(golden):
+    g = golden("mla_decode_persistent.npz")
+    h = torch.float16
+    out = orc.mla_decode(from_bits(g["q"], h), from_bits(g["q_pe"], h), from_bits(g["kv"], h), from_bits(g["k_pe"], h))
+    torch.testing.assert_close(out, from_bits(g["out"], h).float(), rtol=2e-3, atol=1e-3)
+
+
 def test_backward_oracle_is_consistent_with_finite_differences():
     q, kv, idx = orc.make_sparse_mla_inputs(1, 2, 12, 2, 4, D=16, seed=0, dtype=torch.float32)
     do = torch.randn(1, 2, 2, 8)

@@ -27,6 +27,9 @@ SIGNATURES = {
     "dsa_lightning_indexer": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                         c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_size_t,
                                         c_void_p]),
+    "dsa_lightning_indexer_paged": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                              c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                              c_void_p, c_void_p, c_size_t, c_void_p]),
     "dsa_lightning_indexer_noalloc_max_bytes": (c_size_t, []),
     "dsa_lightning_indexer_noalloc": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                 c_int32, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p,

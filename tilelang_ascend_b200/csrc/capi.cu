@@ -146,19 +146,32 @@ int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_st
   return err ? fail_cuda("topk_select launch", err) : 0;
 }
 
+// Paged keys of the indexer: block table [B, max_blocks] over a cache of num_blocks blocks of block_size rows (all zero = dense k).
+struct PagedKeys {
+  const int32_t* block_table = nullptr;
+  int32_t block_size = 0, max_blocks = 0, num_blocks = 0;
+};
+
 static int indexer_scores_impl(const void* q, const void* k, const float* w, float* scores, int32_t B, int32_t S1, int32_t S2,
                                int32_t N1, int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b,
-                               const int32_t* k_len_b, int32_t* limits_out, int32_t fill_masked, void* stream) {
+                               const int32_t* k_len_b, int32_t* limits_out, int32_t fill_masked, void* stream,
+                               const PagedKeys& paged = PagedKeys()) {
   if (!q || !k || !w || !scores) return fail("null tensor pointer");
   if (!dtype_ok(dtype)) return fail("dtype must be 0 (bfloat16) or 1 (float16)");
   if (B <= 0 || S1 <= 0 || S2 <= 0 || N1 <= 0 || D <= 0) return fail("B, S1, S2, N1 and D must be positive");
   if (sparse_mode != 0 && sparse_mode != 3) return fail("sparse_mode must be 0 or 3");
   if (D % 8 != 0) return fail("D must be a multiple of 8");
-  dsa::IndexerParams p;
+  dsa::IndexerParams p{};
   p.q = q; p.k = k; p.w = w; p.scores = scores;
   p.B = B; p.S1 = S1; p.S2 = S2; p.N1 = N1; p.D = D;
   p.sparse_mode = sparse_mode; p.q_len_b = q_len_b; p.k_len_b = k_len_b; p.limits = limits_out;
   p.fill_masked = fill_masked ? 1 : 0;
+  if (paged.block_table) {
+    if (paged.block_size <= 0 || paged.max_blocks <= 0 || paged.num_blocks <= 0) return fail("block_size, max_blocks and num_blocks must be positive with a block table");
+    if (static_cast<int64_t>(paged.max_blocks) * paged.block_size < S2) return fail("the block table covers fewer than S2 keys");
+    if (static_cast<int64_t>(paged.num_blocks) * paged.block_size > 0x7fffffffLL) return fail("paged key cache too large");
+    p.block_table = paged.block_table; p.block_size = paged.block_size; p.max_blocks = paged.max_blocks; p.num_blocks = paged.num_blocks;
+  }
   if (get_status_word(&p.status)) return 1;
   int err;
   if (dsa::indexer_tc_supported(p)) {
@@ -192,6 +205,22 @@ int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t 
   float* scores = static_cast<float*>(workspace);
   int32_t* limits = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ((rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255)));
   int rc = indexer_scores_impl(q, k, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream);
+  if (rc) return rc;
+  return dsa_topk_select(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream);
+}
+
+int dsa_lightning_indexer_paged(const void* q, const void* k_cache, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
+                                int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, const int32_t* block_table,
+                                int32_t block_size, int32_t max_blocks, int32_t num_blocks, int32_t top_k, int32_t* out_idx, float* out_val,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < dsa_lightning_indexer_workspace_bytes(B, S1, S2)) return fail("workspace missing or too small");
+  if (!out_idx || !block_table) return fail("null tensor pointer");
+  const size_t rows = static_cast<size_t>(B) * S1;
+  float* scores = static_cast<float*>(workspace);
+  int32_t* limits = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ((rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255)));
+  PagedKeys paged;
+  paged.block_table = block_table; paged.block_size = block_size; paged.max_blocks = max_blocks; paged.num_blocks = num_blocks;
+  int rc = indexer_scores_impl(q, k_cache, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream, paged);
   if (rc) return rc;
   return dsa_topk_select(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream);
 }

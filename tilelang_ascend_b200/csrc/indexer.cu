@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(itc::kThreads, 1)
   if (warp > kMmaWarp) {
     // ================================ key-tile producers ============================================
     const int pt = tid - (kMmaWarp + 1) * 32;
-    const T* kbase = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(b) * p.S2 * kD;
+    const T* kbase = reinterpret_cast<const T*>(p.k) + (p.block_table ? 0 : static_cast<int64_t>(b) * p.S2 * kD);
     if (use_tma) {
       // one thread: k as a 2-D tensor [B * S2 keys, 128 dims]; keys past the row's limit (or past the batch entry: they
       // belong to the next one) only produce scores that the reduce warps replace by -inf
@@ -136,8 +136,21 @@ __global__ void __launch_bounds__(itc::kThreads, 1)
           if (it >= kStages && !mbar_wait(&k_empty[s], ((it / kStages) + 1) & 1, p.status)) { ok = false; break; }
           const uint32_t stage = sK + s * kKStageBytes, full = smem_u32(&k_full[s]);
           mbar_arrive_expect_tx(&k_full[s], kKStageBytes);
-          tma_load_2d(stage, &kmap, full, 0, b * p.S2 + it * kKeys);
-          tma_load_2d(stage + kKeys * 128, &kmap, full, 64, b * p.S2 + it * kKeys);
+          if (p.block_table) {
+            // paged cache: the tile is 128 / box_rows boxes, each inside one block (box_rows divides the block size);
+            // a table entry that is padding (< 0) or beyond the pool gives a row coordinate outside the tensor: zeros
+            const int R = p.box_rows;
+            for (int j = 0; j < kKeys / R; ++j) {
+              const int key0 = it * kKeys + j * R, lb = key0 / p.block_size;
+              const int phys = lb < p.max_blocks ? __ldg(p.block_table + static_cast<int64_t>(b) * p.max_blocks + lb) : -1;
+              const int y = (phys >= 0 && phys < p.num_blocks) ? phys * p.block_size + key0 % p.block_size : -R;
+              tma_load_2d(stage + j * R * 128, &kmap, full, 0, y);
+              tma_load_2d(stage + kKeys * 128 + j * R * 128, &kmap, full, 64, y);
+            }
+          } else {
+            tma_load_2d(stage, &kmap, full, 0, b * p.S2 + it * kKeys);
+            tma_load_2d(stage + kKeys * 128, &kmap, full, 64, b * p.S2 + it * kKeys);
+          }
         }
       }
     } else
@@ -150,8 +163,15 @@ __global__ void __launch_bounds__(itc::kThreads, 1)
         const int u = pt + 128 * j;
         const int r = u >> 4, unit = u & 15;
         const int key = it * kKeys + r;
-        const bool v = key < ak;
-        const T* src = v ? kbase + static_cast<int64_t>(key) * kD + unit * 8 : kbase;
+        bool v = key < ak;
+        int64_t row = key;
+        if (p.block_table) {  // logical key -> row of the paged cache; padding entries of the table are not read
+          const int lb = key / p.block_size;
+          const int phys = (v && lb < p.max_blocks) ? __ldg(p.block_table + static_cast<int64_t>(b) * p.max_blocks + lb) : -1;
+          v = phys >= 0 && phys < p.num_blocks;
+          row = static_cast<int64_t>(phys) * p.block_size + key % p.block_size;
+        }
+        const T* src = v ? kbase + row * kD + unit * 8 : kbase;
         cp_async16(stage + (unit >> 3) * (kKeys * 128) + sw128_offset(r, unit & 7), src, v ? 16u : 0u);
       }
       cp_async_commit();
@@ -290,7 +310,14 @@ __global__ void __launch_bounds__(256) indexer_scores_generic_kernel(const Index
   for (int key = threadIdx.x; key < kend; key += blockDim.x) {
     float score = -INFINITY;
     if (key < lim) {
-      const T* krow = reinterpret_cast<const T*>(p.k) + (static_cast<int64_t>(b) * p.S2 + key) * p.D;
+      int64_t row = static_cast<int64_t>(b) * p.S2 + key;
+      if (p.block_table) {
+        const int lb = key / p.block_size;
+        const int phys = lb < p.max_blocks ? p.block_table[static_cast<int64_t>(b) * p.max_blocks + lb] : -1;
+        if (phys < 0 || phys >= p.num_blocks) { out[key] = 0.f; continue; }  // a candidate key without a block: no contribution
+        row = static_cast<int64_t>(phys) * p.block_size + key % p.block_size;
+      }
+      const T* krow = reinterpret_cast<const T*>(p.k) + row * p.D;
       score = 0.f;
       for (int h = 0; h < p.N1; ++h) {
         float dot = 0.f;
@@ -325,11 +352,13 @@ EncodeTiledFn encode_tiled_fn() {
 // possible (then the kernel's cp.async producers fetch the tiles)
 bool make_k_map(const IndexerParams& p, bool bf16, CUtensorMap* map) {
   EncodeTiledFn encode = encode_tiled_fn();
-  const long long rows = static_cast<long long>(p.B) * p.S2;
+  // paged cache: all rows of the pool; a box must lie inside one block, so its row count has to divide the block size
+  const long long rows = p.block_table ? static_cast<long long>(p.num_blocks) * p.block_size : static_cast<long long>(p.B) * p.S2;
   if (!encode || (reinterpret_cast<uintptr_t>(p.k) & 15u) || rows <= 0 || rows > 0x7fffffffLL) return false;
+  if (p.block_table && (p.box_rows < 8 || itc::kKeys % p.box_rows != 0 || p.block_size % p.box_rows != 0)) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(itc::kD), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(itc::kD) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(itc::kKeys)}, estr[2] = {1, 1};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(p.block_table ? p.box_rows : itc::kKeys)}, estr[2] = {1, 1};
   return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(p.k), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -337,7 +366,13 @@ bool make_k_map(const IndexerParams& p, bool bf16, CUtensorMap* map) {
 }  // namespace
 
 template <bool kBF16, int N1>
-static int launch_indexer_tc_n1(const IndexerParams& p, cudaStream_t stream) {
+static int launch_indexer_tc_n1(const IndexerParams& p_in, cudaStream_t stream) {
+  IndexerParams p = p_in;
+  // rows per TMA box of a paged cache: the largest power of two (8..128) that divides the block size
+  p.box_rows = 0;
+  if (p.block_table)
+    for (int r = itc::kKeys; r >= 8; r >>= 1)
+      if (p.block_size % r == 0) { p.box_rows = r; break; }
   auto kern = indexer_scores_tc_kernel<kBF16, N1>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(itc::kSmemBytes));
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -95,7 +95,7 @@ int dsa_lightning_indexer_noalloc(const void* q, const void* k, const float* w, 
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int), st);
   if (e != cudaSuccess) return fail(std::string("cudaMemsetAsync(status word): ") + cudaGetErrorString(e));
 
-  dsa::IndexerParams p;
+  dsa::IndexerParams p{};  // (no paged keys on this path)
   p.q = q; p.k = k; p.w = w; p.scores = scores;
   p.B = B; p.S1 = S1; p.S2 = S2; p.N1 = N1; p.D = D;
   p.sparse_mode = sparse_mode; p.q_len_b = q_len_b; p.k_len_b = k_len_b; p.limits = limits;

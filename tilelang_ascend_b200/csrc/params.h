@@ -60,6 +60,11 @@ struct IndexerParams {
   int32_t* limits;            // [B, S1] out, nullable: number of leading keys that are candidates per row
   int fill_masked;            // 1: also write -inf into tiles that lie entirely beyond the limit
   int* status;
+  // paged keys (nullable): k is the cache [num_blocks, block_size, 1, D]; logical key j of batch b is row
+  // block_table[b * max_blocks + j / block_size] * block_size + j % block_size; S2 is the largest logical length
+  const int32_t* block_table;
+  int block_size, max_blocks, num_blocks;
+  int box_rows;               // set by the launcher: rows per TMA box of a paged cache
 };
 
 // Block-sparse indexer logits (HISA).

@@ -38,15 +38,30 @@ def indexer_scores_raw(query, key, weights, *, sparse_mode: int = 3, q_len_b=Non
 
 
 def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode: int, q_len_b=None, k_len_b=None,
-                          return_value: bool = False, workspace: Optional[torch.Tensor] = None):
-    """Fused scores + top-k of BSND inputs: indices int32 [B,S1,1,K] (+ fp32 values)."""
-    opt = [t for t in (q_len_b, k_len_b) if t is not None]
+                          return_value: bool = False, workspace: Optional[torch.Tensor] = None, block_table=None,
+                          max_keys: Optional[int] = None):
+    """Fused scores + top-k of BSND inputs: indices int32 [B,S1,1,K] (+ fp32 values).
+
+    With ``block_table`` [B, max_blocks] int32, ``key`` is a paged cache [num_blocks, block_size, 1, D] that the kernel
+    addresses through the table (no dense copy); ``max_keys`` (default max_blocks * block_size) is the largest logical
+    key count, i.e. the width of the score rows."""
+    opt = [t for t in (q_len_b, k_len_b, block_table) if t is not None]
     dev = check_inputs([query, key, weights] + opt, [None, query.dtype, torch.float32] + [torch.int32] * len(opt),
-                       ["query", "key", "weights"] + ["actual lengths"] * len(opt))
+                       ["query", "key", "weights"] + ["int32 side input"] * len(opt))
     B, S1, N1, D = query.shape
-    S2 = key.shape[1]
-    if key.shape != (B, S2, 1, D) or weights.shape != (B, S1, N1):
-        raise ValueError(f"shape mismatch: query {tuple(query.shape)}, key {tuple(key.shape)}, weights {tuple(weights.shape)}")
+    if block_table is not None:
+        if key.dim() != 4 or key.shape[2] != 1 or key.shape[3] != D or block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError(f"paged keys: cache {tuple(key.shape)} / block table {tuple(block_table.shape)} do not fit query {tuple(query.shape)}")
+        num_blocks, block_size, max_blocks = key.shape[0], key.shape[1], block_table.shape[1]
+        S2 = max_blocks * block_size if max_keys is None else int(max_keys)
+        if not 1 <= S2 <= max_blocks * block_size:
+            raise ValueError(f"max_keys must be in [1, {max_blocks * block_size}]")
+    else:
+        S2 = key.shape[1]
+        if key.shape != (B, S2, 1, D):
+            raise ValueError(f"shape mismatch: query {tuple(query.shape)}, key {tuple(key.shape)}")
+    if weights.shape != (B, S1, N1):
+        raise ValueError(f"shape mismatch: query {tuple(query.shape)}, weights {tuple(weights.shape)}")
     lib = _lib.load()
     need = lib.dsa_lightning_indexer_workspace_bytes(B, S1, S2)
     if workspace is None:
@@ -56,9 +71,15 @@ def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode
     idx = torch.empty((B, S1, 1, sparse_count), dtype=torch.int32, device=dev)
     val = torch.empty((B, S1, 1, sparse_count), dtype=torch.float32, device=dev) if return_value else None
     with torch.cuda.device(dev):
-        _lib.check(lib.dsa_lightning_indexer(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
-                                             int(sparse_mode), ptr(q_len_b), ptr(k_len_b), int(sparse_count), ptr(idx), ptr(val),
-                                             ptr(workspace), need, current_stream(dev)))
+        if block_table is not None:
+            _lib.check(lib.dsa_lightning_indexer_paged(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
+                                                       int(sparse_mode), ptr(q_len_b), ptr(k_len_b), ptr(block_table), block_size, max_blocks,
+                                                       num_blocks, int(sparse_count), ptr(idx), ptr(val), ptr(workspace), need,
+                                                       current_stream(dev)))
+        else:
+            _lib.check(lib.dsa_lightning_indexer(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
+                                                 int(sparse_mode), ptr(q_len_b), ptr(k_len_b), int(sparse_count), ptr(idx), ptr(val),
+                                                 ptr(workspace), need, current_stream(dev)))
     return idx, val
 
 
@@ -71,6 +92,14 @@ def _per_batch(lengths, B: int, default: int, dev) -> torch.Tensor:
 def _prefix_to_lengths(prefix) -> list:
     p = [int(x) for x in torch.as_tensor(prefix).tolist()]
     return [p[0]] + [p[i] - p[i - 1] for i in range(1, len(p))]
+
+
+def _packed_positions(lengths: list, dev):
+    """(sequence number, position inside the sequence) of every token of a packed (TND) tensor, on ``dev``."""
+    lens = torch.tensor(lengths, dtype=torch.int64, device=dev)
+    seq = torch.repeat_interleave(torch.arange(len(lengths), device=dev), lens)
+    starts = torch.cumsum(lens, 0) - lens
+    return seq, torch.arange(int(lens.sum().item()), device=dev) - starts[seq]
 
 
 def lightning_indexer(
@@ -127,11 +156,9 @@ def lightning_indexer(
         B, S1 = len(q_lens), max(q_lens) if q_lens else 0
         q_pad = query.new_zeros((B, max(S1, 1), N1, D))
         w_pad = weights.new_zeros((B, max(S1, 1), N1))
-        off = 0
-        for b, n in enumerate(q_lens):
-            q_pad[b, :n] = query[off:off + n]
-            w_pad[b, :n] = weights[off:off + n]
-            off += n
+        q_seq, q_pos = _packed_positions(q_lens, dev)   # one scatter per tensor, whatever the number of sequences
+        q_pad[q_seq, q_pos] = query[:q_seq.numel()]
+        w_pad[q_seq, q_pos] = weights[:q_seq.numel()]
         query, weights = q_pad, w_pad
         q_len_b = torch.tensor(q_lens, dtype=torch.int32, device=dev)
     else:
@@ -139,15 +166,13 @@ def lightning_indexer(
         q_tot = B * S1
         q_len_b = _per_batch(actual_seq_lengths_query, B, S1, dev)
 
-    # ---- keys: BSND as is; TND padded; paged blocks gathered into BSND through the block table ------
+    # ---- keys: BSND as is; TND padded; a paged cache is passed on with its block table -------------------
     if is_tnd_key:
         k_lens = _prefix_to_lengths(actual_seq_lengths_key)
         S2 = max(k_lens) if k_lens else 0
         k_pad = key.new_zeros((B, max(S2, 1), key.shape[1], key.shape[2]))
-        off = 0
-        for b, n in enumerate(k_lens):
-            k_pad[b, :n] = key[off:off + n]
-            off += n
+        k_seq, k_pos = _packed_positions(k_lens, dev)
+        k_pad[k_seq, k_pos] = key[:k_seq.numel()]
         key = k_pad
         k_len_b = torch.tensor(k_lens, dtype=torch.int32, device=dev)
     elif is_pa:
@@ -158,14 +183,16 @@ def lightning_indexer(
             raise ValueError(f"PA block_size must be a positive multiple of 16 and <= 1024, got {bs}")
         k_len_b = _per_batch(actual_seq_lengths_key, B, 0, dev)
         S2 = int(k_len_b.max().item()) if B else 0
-        nblk = (max(S2, 1) + bs - 1) // bs
-        bt = block_table.to(dev).long()[:, :nblk].clamp(min=0)
-        key = key[bt].reshape(B, nblk * bs, n2k, key.shape[-1])[:, :max(S2, 1)]
+        # the cache stays where it is: the kernel walks it through the block table
+        paged_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+        if S2 > paged_table.shape[1] * bs:
+            raise ValueError(f"block_table covers {paged_table.shape[1] * bs} keys, actual_seq_lengths_key asks for {S2}")
     else:
         S2 = key.shape[1]
         k_len_b = _per_batch(actual_seq_lengths_key, B, S2, dev)
     assert D == 128, f"head dim must be 128, got {D}"
     assert key.shape[2] == 1, f"N2 must be 1, got N2={key.shape[2]}"
+    assert key.shape[-1] == D, f"key head dim {key.shape[-1]} differs from query head dim {D}"
     if N1 > 64:
         raise ValueError(f"query head_num (N1) must be <= 64, got {N1}")
     assert query.device == key.device == weights.device, "tensors must be on same device"
@@ -178,12 +205,12 @@ def lightning_indexer(
         return indices, values
 
     idx, val = lightning_indexer_raw(query.contiguous(), key.contiguous(), weights.contiguous(), sparse_count=sparse_count,
-                                     sparse_mode=sparse_mode, q_len_b=q_len_b, k_len_b=k_len_b, return_value=return_value)
+                                     sparse_mode=sparse_mode, q_len_b=q_len_b, k_len_b=k_len_b, return_value=return_value,
+                                     block_table=paged_table if is_pa else None, max_keys=max(S2, 1) if is_pa else None)
     if is_tnd:
-        q_lens = q_len_b.tolist()
-        idx = torch.cat([idx[b, :n] for b, n in enumerate(q_lens)], dim=0)
+        idx = idx[q_seq, q_pos]
         if return_value:
-            val = torch.cat([val[b, :n] for b, n in enumerate(q_lens)], dim=0)
+            val = val[q_seq, q_pos]
     values = val.to(query.dtype) if return_value else empty_vals
     return idx, values
 
