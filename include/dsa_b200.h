@@ -48,6 +48,14 @@ const char* dsa_get_last_error(void);
  * reference launcher returns void and faults surface at the next synchronisation. */
 int dsa_kernel_status(int* status);
 
+/* Self-test of the kernels' bounded waits: launches one tiny kernel whose single waiting thread waits, for at most
+ * budget_cycles SM clock cycles (1 .. 2e9; a million is about half a millisecond), on a barrier that nothing completes.
+ * The wait runs out, the kernel sets the device status word to 1 and ends normally -- the mechanism by which every
+ * tcgen05 kernel of this library turns a lost hand-over into a status instead of a hang.  gave_up: device int32 or
+ * NULL, receives 1.  Afterwards dsa_kernel_status reports 1 (and clears the word); kernels launched while the word
+ * is set return at once without writing results.  No reference counterpart. */
+int dsa_selftest_bounded_wait(int64_t budget_cycles, int32_t* gave_up, void* stream);
+
 /* Row-wise top-k.  scores [rows, row_stride] fp32 (n <= row_stride entries per row are looked at);
  * limits [rows] int32 or NULL: number of leading entries of each row that are candidates;
  * out_idx [rows, top_k] int32; out_val [rows, top_k] fp32 or NULL.
@@ -192,7 +200,9 @@ int dsa_sink_combine(const void* out_a, const float* lse_a, const void* out_b, c
  * -inf where that position is outside [0, S_kv) or outside [ks[s], ke[s]).  q [S,H,D], k [S_kv,D] (dtype), block_indices
  * [S,topk] int32, weights [S,H] (weights_dtype: 0 bf16, 1 fp16, 2 fp32), ks / ke [S] int32, logits [S,topk,kv_block_size] fp32.
  * Paged keys: with block_table [B, max_blocks] (else NULL) k is the cache [num_phys_blocks, kv_block_size, 1, D], the indices
- * name LOGICAL blocks of the sequence of query s (sequence = s / tokens_per_seq) and S_kv is ignored; this is the kernel of
+ * name LOGICAL blocks of the sequence of query s (sequence = s / tokens_per_seq) and S_kv = num_phys_blocks * kv_block_size (the
+ * rows of the cache).  A table entry is read only for positions inside [ks[s], ke[s]) -- entries of blocks past a sequence's
+ * context may be padding such as -1 -- and an entry outside [0, num_phys_blocks) is not dereferenced (its logits are -inf); this is the kernel of
  * paged_block_sparse_mqa_attn_return_logits (examples/HISA/paged_block_sparse_mqa_attn_expert.py:54-420, golden :425-468)
  * with ks = 0 and ke = the sequence's context length.
  * impl: DSA_IMPL_AUTO = the tcgen05 kernel when kv_block_size = 128, D = 128 and H <= 64, else CUDA cores; DSA_IMPL_GENERIC /

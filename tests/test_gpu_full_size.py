@@ -1,4 +1,5 @@
-"""BASELINE-size cases on the GPU: size-independent properties plus oracle checks on sampled rows.
+"""Full-size cases on the GPU (the named benchmark shapes and the reference examples' own shapes): size-independent
+properties plus oracle checks on sampled rows.
 
 The oracle is too slow for the full tensors, so each case checks (a) a sample of query rows against the fp32
 oracle, and (b) properties that hold for every row: determinism, agreement between the tensor-core and the
@@ -154,3 +155,33 @@ def test_backward_prefill_shape_properties():
     check_status()
     assert_close_fp(dq_t.float().cpu(), dq_c.float().cpu(), "dQ tensor-core vs CUDA-core")
     assert_close_fp(dk_t.cpu(), dk_c.cpu(), "dKV tensor-core vs CUDA-core", atol=5e-2)
+
+
+@pytest.mark.parametrize("name,B,S,S_kv,q_start", [
+    ("base_example", 1, 128, 32768, 28672),        # example_sparse_flash_attn.py:295-326
+    ("dynamic_shape", 2, 273, 44444, 28672),       # example_sparse_flash_attn_dynamic_shape.py:341-373
+    ("mask_from_zero", 1, 1024, 32768, 0),         # example_sparse_flash_attn_mask.py:350-383 (query t sees keys 0..t)
+])
+def test_reference_example_shapes(name, B, S, S_kv, q_start):
+    """The shapes the reference's own example scripts pin (H=128, D=576, topk=2048, bf16, padding sentinel S_kv, index lists
+    drawn as randperm(max(1, t + q_start))[:topk]); sampled rows against the oracle with the scripts' rtol = atol = 1e-2."""
+    import tilelang_ascend_b200 as dsa
+    H, topk = 128, 2048
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn((B, S, H, 576), generator=g).to(torch.bfloat16)
+    kv = torch.randn((B, S_kv, 1, 576), generator=g).to(torch.bfloat16)
+    idx = torch.full((B, S, 1, topk), S_kv, dtype=torch.int32)
+    for b in range(B):
+        for t in range(S):
+            sel = torch.randperm(max(1, t + q_start), generator=g)[:topk]
+            idx[b, t, 0, :len(sel)] = sel.to(torch.int32)
+    kernel = dsa.sparse_attention_fwd(H, 512, 64, topk, 1, return_softmax_lse=True)
+    out, lse = kernel(q.to(DEV), kv.to(DEV), idx.to(DEV), q_start_index_s=q_start)
+    check_status()
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    rows = sorted(set([0, 1, 2, 63, 64, 65, S // 2, S - 2, S - 1]))
+    for b in range(B):
+        for r in rows:
+            ro, rl = orc.sparse_mla_fwd(q[b:b + 1, r:r + 1], kv[b:b + 1], idx[b:b + 1, r:r + 1], q_start_index_s=q_start + r)
+            torch.testing.assert_close(out[b:b + 1, r:r + 1].float().cpu(), ro, rtol=1e-2, atol=1e-2)
+            assert_close_fp(lse[b:b + 1, r:r + 1].cpu(), rl, f"{name} lse row {r}")

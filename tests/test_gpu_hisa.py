@@ -12,6 +12,7 @@ pytestmark = pytest.mark.gpu
     (64, 4096, 32, 128, 128, 8, torch.float16, torch.float16),     # the reference test's shape family (fp16): tensor-core kernel
     (40, 5000, 64, 128, 128, 12, torch.bfloat16, torch.float32),   # tensor-core kernel, S_kv not a multiple of the block, 64 heads
     (9, 700, 20, 128, 128, 4, torch.bfloat16, torch.bfloat16),     # tensor-core kernel, head count below 64 and not a multiple of 16
+    (11, 900, 40, 128, 128, 4, torch.bfloat16, torch.float32),     # 40 heads: UMMA N = 48, accumulator columns 48..63 are never written
     (33, 1000, 64, 128, 64, 12, torch.bfloat16, torch.float32),    # S_kv not a multiple of the block: the last block is cut
     (5, 300, 7, 64, 48, 4, torch.bfloat16, torch.bfloat16),        # block size that is not a multiple of 32, odd head count
 ])
@@ -71,3 +72,38 @@ def test_paged_block_sparse_logits_match_oracle(B, S, H, D, bs, topk, maxb, nphy
     assert torch.equal(torch.isinf(out), torch.isinf(ref)), "masked positions differ"
     fin = torch.isfinite(ref)
     torch.testing.assert_close(out[fin], ref[fin], rtol=2e-5, atol=2e-4)
+
+
+@pytest.mark.parametrize("H,D,bs", [(32, 128, 128), (12, 64, 32)])
+def test_paged_table_padding_is_never_dereferenced(H, D, bs):
+    """Block-table entries past a sequence's context are padding (-1, as the reference's indexer front door writes them, or a
+    number beyond the cache): logical blocks that lie wholly past the context must come back -inf on both kernels without the
+    entry being used as an address, and blocks inside the context must be unaffected."""
+    import tilelang_ascend_b200 as dsa
+    B, S, topk, maxb, nphys = 2, 3, 8, 10, 24
+    g = torch.Generator().manual_seed(H)
+    q = (torch.rand((B, S, H, D), generator=g) - 0.5).to(torch.float16)
+    cache = (torch.rand((nphys, bs, 1, D), generator=g) - 0.5).to(torch.float16)
+    w = (torch.rand((B, S, H), generator=g) - 0.3).to(torch.float16)
+    ctx = torch.tensor([3 * bs + 17, 6 * bs], dtype=torch.int32)
+    bt = torch.stack([torch.randperm(nphys, generator=g)[:maxb] for _ in range(B)]).to(torch.int32)
+    used = (ctx + bs - 1) // bs
+    good = bt.clone()                      # oracle input: padding replaced by a valid block (its logits are masked anyway)
+    for b in range(B):
+        bt[b, int(used[b]):] = torch.tensor([-1, 1 << 20] * maxb)[: maxb - int(used[b])]
+        good[b, int(used[b]):] = 0
+    blk = torch.randint(0, maxb, (B, S, topk), generator=g, dtype=torch.int32)   # up to the batch-wide maximum, as the reference's test draws them
+    ref = orc.paged_block_sparse_logits(q, cache, blk, bs, w, ctx, good).reshape(B * S, topk, bs)
+    kernel = dsa.paged_block_sparse_mqa_attn_return_logits(B, S, nphys, bs, topk, H, D, maxb)
+    args = (q.view(B * S, H, D).cuda(), cache.cuda(), blk.view(B * S, topk).cuda(), w.view(B * S, H).cuda(), ctx.cuda(), bt.cuda())
+    out = kernel(*args).cpu()
+    ke = ctx.repeat_interleave(S).contiguous().cuda()
+    out_c = dsa.block_sparse_logits_raw(args[0], cache.view(nphys * bs, D).cuda(), args[2], args[3], torch.zeros_like(ke), ke, bs, impl=1,
+                                        block_table=bt.cuda(), tokens_per_seq=S).cpu()
+    check_status()
+    past = (blk.view(B * S, topk) >= used.repeat_interleave(S)[:, None])
+    assert past.any() and torch.isinf(out[past]).all() and torch.isinf(out_c[past]).all()
+    for got in (out, out_c):
+        assert torch.equal(torch.isinf(got), torch.isinf(ref)), "masked positions differ"
+        fin = torch.isfinite(ref)
+        torch.testing.assert_close(got[fin], ref[fin], rtol=2e-5, atol=2e-4)

@@ -20,6 +20,7 @@ SIGNATURES = {
     "dsa_init": (c_int32, []),
     "dsa_get_last_error": (c_char_p, []),
     "dsa_kernel_status": (c_int32, [ctypes.POINTER(c_int32)]),
+    "dsa_selftest_bounded_wait": (c_int32, [c_int64, c_void_p, c_void_p]),
     "dsa_topk_select": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "dsa_indexer_scores": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
                                      c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
@@ -84,8 +85,15 @@ class DsaError(RuntimeError):
 
 
 def check(rc: int) -> None:
+    """Raise on a failed call.  With DSA_DEBUG_SYNC=1 in the environment every successful launch is also followed by a
+    device synchronisation and a read of the kernels' status word, so that a bounded in-kernel wait that gave up raises
+    at the call that caused it (a debugging aid: it serialises host and device)."""
     if rc != 0:
         raise DsaError(load().dsa_get_last_error().decode())
+    if os.environ.get("DSA_DEBUG_SYNC") == "1":
+        st = kernel_status()
+        if st != 0:
+            raise DsaError(f"kernel status word = {st}: a bounded in-kernel wait gave up; results of this call are not valid")
 
 
 def kernel_status() -> int:

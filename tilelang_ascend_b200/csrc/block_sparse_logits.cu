@@ -55,8 +55,16 @@ __global__ void __launch_bounds__(bsl::kThreads) block_sparse_logits_kernel(cons
     const int blk = p.blocks[static_cast<int64_t>(qi) * p.topk + j];
     const int64_t pos = static_cast<int64_t>(blk) * p.block + off;   // logical position
     const bool in_block = off < p.block;
-    const bool valid = in_block && blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
-    const int64_t row = !valid ? 0 : p.block_table ? static_cast<int64_t>(p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk]) * p.block + off : pos;
+    bool valid = in_block && blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
+    int64_t row = pos;
+    if (valid && p.block_table) {
+      // the table is read only for positions that take part (entries past a sequence's context are padding), and a
+      // physical block outside the cache is not dereferenced
+      const int phys = p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk];
+      valid = phys >= 0 && (static_cast<int64_t>(phys) + 1) * p.block <= p.S_kv;
+      row = static_cast<int64_t>(phys) * p.block + off;
+    }
+    if (!valid) row = 0;
     float acc[kMaxH];
 #pragma unroll
     for (int h = 0; h < kMaxH; ++h) acc[h] = 0.f;
@@ -143,11 +151,12 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   float* sw = reinterpret_cast<float*>(smem + kOffW);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, qi = blockIdx.x;
-  // status word: these kernels have none of their own; a failed wait ends the CTA's loops (results of the CTA are then wrong,
-  // which the bounded wait only prevents from becoming a hang)
-  __shared__ int s_status;
+  // a failed wait records its status in the device status word and ends the CTA's loops; launches that find the word set exit
+  __shared__ int s_start_status;
+  if (tid == 0) s_start_status = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_start_status != kStatusOk) return;
   if (tid == 0) {
-    s_status = kStatusOk;
     for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 128); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&d_full[i], 1); mbar_init(&d_free[i], 4); }
     mbar_init(q_ready, 128);
@@ -177,6 +186,7 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
   if (warp >= 4 && warp < 8) {
     // ================================ loaders: thread = key row of every block ======================
     const int r = tid - 128;
+    const int lo = p.ks[qi], hi = p.ke[qi];
     {  // the query's heads: thread r < 64 copies head r (256 bytes), rows without a head are zero-filled
       if (r < kHeads) {
         const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(qi) * p.H + (r < p.H ? r : 0)) * (kDim * 2);
@@ -192,10 +202,18 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
       const int s = j % kStages;
       const int blk = blocks[j];
       const int64_t pos = static_cast<int64_t>(blk) * kKeys + r;
-      const bool in_range = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv);
-      const int64_t row = !in_range ? 0 : p.block_table ? static_cast<int64_t>(p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk]) * kKeys + r : pos;
+      // a row is fetched only if its logit is kept: inside the key tensor / block table AND inside [ks, ke).  Table entries of
+      // blocks past a sequence's context are padding and are not read; a physical block outside the cache is not dereferenced.
+      bool in_range = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
+      int64_t row = pos;
+      if (in_range && p.block_table) {
+        const int phys = p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk];
+        in_range = phys >= 0 && (static_cast<int64_t>(phys) + 1) * kKeys <= p.S_kv;
+        row = static_cast<int64_t>(phys) * kKeys + r;
+      }
+      if (!in_range) row = 0;
       const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.k) + row * (kDim * 2);
-      if (j >= kStages && !mbar_wait<true>(&empty[s], ((j / kStages) + 1) & 1, &s_status)) { ok = false; break; }
+      if (j >= kStages && !mbar_wait<true>(&empty[s], ((j / kStages) + 1) & 1, p.status)) { ok = false; break; }
       const uint32_t stage = sBase + s * kStageBytes;
 #pragma unroll
       for (int u = 0; u < 16; ++u) cp_async16(stage + (u >> 3) * kChunk + sw128_offset(r, u & 7), krow + u * 16, in_range ? 16u : 0u);
@@ -217,12 +235,12 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
     if (lane == 0) {
       // UMMA N = the head count rounded up to 16 (rows of the B image beyond the head count are zero)
       const uint32_t idesc = make_idesc_f16(kBF16, kKeys, static_cast<uint32_t>((p.H + 15) & ~15), 0, 0);
-      ok = mbar_wait(q_ready, 0, &s_status);
+      ok = mbar_wait(q_ready, 0, p.status);
       const uint64_t db0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
       for (int j = 0; j < p.topk && ok; ++j) {
         const int s = j % kStages, db = j & 1;
-        if (!mbar_wait(&full[s], (j / kStages) & 1, &s_status)) { ok = false; break; }
-        if (j >= 2 && !mbar_wait(&d_free[db], ((j >> 1) + 1) & 1, &s_status)) { ok = false; break; }
+        if (!mbar_wait(&full[s], (j / kStages) & 1, p.status)) { ok = false; break; }
+        if (j >= 2 && !mbar_wait(&d_free[db], ((j >> 1) + 1) & 1, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint64_t da0 = make_smem_desc(sBase + s * kStageBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
@@ -244,28 +262,24 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
       const int db = j & 1;
       const int blk = blocks[j];
       const int64_t pos = static_cast<int64_t>(blk) * kKeys + r;
-      const bool valid = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
-      if (!__all_sync(0xffffffffu, mbar_wait(&d_full[db], (j >> 1) & 1, &s_status))) { ok = false; break; }
+      bool valid = blk >= 0 && (p.block_table ? blk < p.max_blocks : pos < p.S_kv) && pos >= lo && pos < hi;
+      if (valid && p.block_table) {  // same rule as the loader: a row that was not fetched has no logit
+        const int phys = p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk];
+        valid = phys >= 0 && (static_cast<int64_t>(phys) + 1) * kKeys <= p.S_kv;
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(&d_full[db], (j >> 1) & 1, p.status))) { ok = false; break; }
       tc_fence_after();
       uint32_t v[64];
       tmem_ld32(tD + db * kHeads + lane_base, v);
-      if (p.H > 32) {
-        tmem_ld32(tD + db * kHeads + 32 + lane_base, v + 32);
-      } else {  // columns the MMAs do not write are not read
-#pragma unroll
-        for (int h = 32; h < 64; ++h) v[h] = 0u;
-      }
+      if (p.H > 32) tmem_ld32(tD + db * kHeads + 32 + lane_base, v + 32);
       tmem_wait_ld();
-      if (p.H <= 16) {
-#pragma unroll
-        for (int h = 16; h < 32; ++h) v[h] = 0u;
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&d_free[db]);
       float total = 0.f;
 #pragma unroll
-      for (int h = 0; h < kHeads; ++h) total += sw[h] * fmaxf(__uint_as_float(v[h]), 0.f);
+      for (int h = 0; h < kHeads; ++h)   // columns at or beyond the head count hold stale tensor memory (or were not loaded): skipped
+        if (h < p.H) total += sw[h] * fmaxf(__uint_as_float(v[h]), 0.f);
       p.logits[(static_cast<int64_t>(qi) * p.topk + j) * kKeys + r] = valid ? total : -INFINITY;
     }
   }

@@ -31,6 +31,7 @@ bool block_sparse_logits_supported(const BlockSparseLogitsParams& p);
 bool block_sparse_logits_tc_supported(const BlockSparseLogitsParams& p);
 int launch_block_sparse_logits_tc(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
 int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cudaStream_t stream);
+int launch_bounded_wait_selftest(int* status, long long budget_cycles, int* gave_up, cudaStream_t stream);
 bool sparse_mla_bwd_tc_supported(const FwdParams& p);
 size_t sparse_mla_bwd_tc_bytes_per_query(int H, int topk);
 int launch_sparse_mla_bwd_tc(const BwdParams& bp, bool bf16, void* workspace, size_t workspace_bytes, int queries_per_pass, cudaStream_t stream);
@@ -130,6 +131,14 @@ int dsa_kernel_status(int* status) {
   }
   if (status) *status = host;
   return 0;
+}
+
+int dsa_selftest_bounded_wait(int64_t budget_cycles, int32_t* gave_up, void* stream) {
+  if (budget_cycles < 1 || budget_cycles > 2000000000LL) return fail("budget_cycles must be in [1, 2e9]");
+  int* s = nullptr;
+  if (get_status_word(&s)) return 1;
+  int err = dsa::launch_bounded_wait_selftest(s, budget_cycles, gave_up, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("bounded_wait_selftest launch", err) : 0;
 }
 
 int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
@@ -343,7 +352,8 @@ int dsa_block_sparse_logits(const void* q, const void* k, const int32_t* block_i
   if (S <= 0 || S_kv <= 0 || kv_block_size <= 0 || topk <= 0) return fail("S, S_kv, kv_block_size and topk must be positive");
   if (block_table && (max_blocks <= 0 || tokens_per_seq <= 0)) return fail("max_blocks and tokens_per_seq must be positive with a block table");
   dsa::BlockSparseLogitsParams p{q, k, block_indices, weights, ks, ke, logits, S, S_kv, H, D, kv_block_size, topk, weights_dtype,
-                                 block_table, max_blocks, tokens_per_seq};
+                                 block_table, max_blocks, tokens_per_seq, nullptr};
+  if (get_status_word(&p.status)) return 1;
   if (!dsa::block_sparse_logits_supported(p)) return fail("block-sparse logits need 1 <= heads <= 64 and index_dim a multiple of 8, at most 256");
   if ((reinterpret_cast<uintptr_t>(k) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u)) return fail("q and k must be 16-byte aligned");
   // blocks of 128 keys with index_dim 128 and up to 64 heads go to the tensor cores (impl = DSA_IMPL_GENERIC keeps them off)

@@ -82,6 +82,7 @@ struct BlockSparseLogitsParams {
   // block_table[(s / tokens_per_seq) * max_blocks + j]
   const int32_t* block_table;
   int max_blocks, tokens_per_seq;
+  int* status;              // device status word (0 = ok)
 };
 
 }  // namespace dsa

@@ -52,7 +52,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr long long kWaitBudgetCycles = 1000000000LL;
 
 template <bool kBackoff = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -61,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     if constexpr (kBackoff) __nanosleep(64);
     if ((++spins & 0x3ffu) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != kStatusOk) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget_cycles) {
         atomicCAS(status, kStatusOk, kStatusBarrierTimeout);
         return false;
       }

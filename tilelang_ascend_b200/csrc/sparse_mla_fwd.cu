@@ -514,7 +514,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&info_full[qp], (k >> 1) & 1, p.status));
       const int nvt = info[qp * 2];  // read unconditionally: both warps of a row block must walk the same number of tiles
-      const bool active = ok && info[qp * 2 + 1] != 0;
       float m_used = -INFINITY, l = 0.f;
       for (int it = 0; it < nvt; ++it, ++g) {
         const uint32_t mask = static_cast<uint32_t>(masks[qp * kMaxTiles + tile_list[qp * kMaxTiles + it]] >> (32 * ch));
@@ -651,7 +650,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(tc::kThreads, 1) spa
           for (int j = 32 * ch; j < 32 * ch + 32; ++j) reinterpret_cast<float4*>(part_row)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (rank == 0 && ch == 0) p.part_lse[prow_index] = -INFINITY;
         }
-      } else if (active && nvt == 0) {
+      } else if (nvt == 0) {  // no key takes part, or the query does not exist (beyond q_len_b): out = 0, lse = -inf
         if (h < p.H) {
           for (int j = 16 * ch; j < 16 * ch + 16; ++j) reinterpret_cast<uint4*>(orow)[j] = make_uint4(0, 0, 0, 0);
           if (rank == 0 && ch == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
@@ -720,12 +719,20 @@ __global__ void __launch_bounds__(256) sparse_mla_fwd_generic_kernel(const FwdPa
   T* tile = reinterpret_cast<T*>(smem_raw);  // [kBK][D]
   __shared__ int s_idx[kBK];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bt = blockIdx.y;
-  const int h = blockIdx.x * kHeadsPerCta + warp;
+  const int head_groups = (p.H + kHeadsPerCta - 1) / kHeadsPerCta;
+  const int bt = blockIdx.x / head_groups;
+  const int h = (blockIdx.x - bt * head_groups) * kHeadsPerCta + warp;
   const RowCtx ctx = make_row_ctx(p, bt);
-  if (!ctx.active) return;
   const int D = p.D, DV = p.DV;
   const bool head_ok = h < p.H;
+  if (!ctx.active) {  // a query beyond q_len_b: out = 0, lse = -inf (uniform across the CTA)
+    if (head_ok) {
+      T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * DV;
+      for (int d = lane; d < DV; d += 32) orow[d] = static_cast<T>(0.f);
+      if (lane == 0 && p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = -INFINITY;
+    }
+    return;
+  }
 
   float qreg[kMaxD / 32];
   float acc[kMaxDV / 32];
@@ -867,7 +874,8 @@ int sparse_mla_fwd_auto_nsplit(const FwdParams& p, int sms) {
 
 int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(gen::kBK) * p.D * 2;
-  dim3 grid((p.H + gen::kHeadsPerCta - 1) / gen::kHeadsPerCta, p.B * p.S);
+  // (query, group of 8 heads) on grid.x: B * S is not limited to 65535
+  dim3 grid(static_cast<unsigned>(static_cast<long long>(p.B) * p.S * ((p.H + gen::kHeadsPerCta - 1) / gen::kHeadsPerCta)));
   if (bf16)
     sparse_mla_fwd_generic_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(p);
   else

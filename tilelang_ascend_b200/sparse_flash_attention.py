@@ -10,12 +10,24 @@ output follows the reference's own keyword ``return_softmax_lse``
 from __future__ import annotations
 
 import functools
+import os
 from typing import Optional
 
 import torch
 
 from . import _lib
 from .adapter import check_inputs, current_stream, dtype_code, ptr, torch_dtype
+
+
+def _check_distinct_indices(indices: torch.Tensor, S_kv: int) -> None:
+    """Debug check (DSA_DEBUG_BOUNDS=1; synchronises): every query's list must name each key at most once.  The kernels
+    count a repeated index once per occurrence, the reference's torch golden counts it once
+    (example_sparse_flash_attn.py:277-280 builds a mask): results differ silently unless the lists are distinct."""
+    srt, _ = torch.sort(indices.reshape(-1, indices.shape[-1]), dim=1)
+    dup = (srt[:, 1:] == srt[:, :-1]) & (srt[:, 1:] >= 0) & (srt[:, 1:] < S_kv)
+    if bool(dup.any()):
+        row = int(torch.nonzero(dup.any(dim=1))[0])
+        raise ValueError(f"indices of query row {row} name a key more than once; the kernels would count it once per occurrence")
 
 
 def _next_pow2(x: int) -> int:
@@ -50,6 +62,8 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
         max_blocks = block_table.shape[1]
         S_kv = max_blocks * block_size
     topk = indices.shape[3]
+    if os.environ.get("DSA_DEBUG_BOUNDS") == "1":
+        _check_distinct_indices(indices, S_kv)
     if out is None:
         out = torch.empty((B, S, H, dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, S, H), dtype=torch.float32, device=dev) if return_lse else None
