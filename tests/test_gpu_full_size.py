@@ -185,3 +185,34 @@ def test_reference_example_shapes(name, B, S, S_kv, q_start):
             ro, rl = orc.sparse_mla_fwd(q[b:b + 1, r:r + 1], kv[b:b + 1], idx[b:b + 1, r:r + 1], q_start_index_s=q_start + r)
             torch.testing.assert_close(out[b:b + 1, r:r + 1].float().cpu(), ro, rtol=1e-2, atol=1e-2)
             assert_close_fp(lse[b:b + 1, r:r + 1].cpu(), rl, f"{name} lse row {r}")
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_cost_balanced_query_shards_reassemble_bit_exactly(world):
+    """The multi-GPU partition on one GPU: every rank's block of the prefill workload (cut where the cost model says the
+    work is equal) is run in turn with its own q_start, and the concatenation must equal the unsharded call bit for bit --
+    per-query results do not depend on which other queries share the launch."""
+    import tilelang_ascend_b200 as dsa
+    S = S_kv = 4096
+    H, topk = 128, 2048
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = torch.randn((1, S, H, 576), generator=g, device=DEV).to(torch.bfloat16)
+    kv = torch.randn((1, S_kv, 1, 576), generator=g, device=DEV).to(torch.bfloat16)
+    idx = _causal_indices(S, S_kv, topk, g)
+    kernel = dsa.sparse_attention_fwd(H, 512, 64, topk, 1, return_softmax_lse=True)
+    out, lse = kernel(q, kv, idx)
+    costs = dsa.causal_query_costs(S, S_kv, topk)
+    outs, lses, loads, prev = [], [], [], 0
+    for r in range(world):
+        qs, ix, q0 = dsa.shard_queries(q, idx, r, world, s_kv=S_kv, balance=True)
+        s, e = dsa.shard_range_balanced(costs, r, world)
+        assert s == prev and q0 == s and qs.shape[1] == e - s
+        prev = e
+        loads.append(int(costs[s:e].sum()))
+        o, l = kernel(qs, kv, ix, q_start_index_s=q0)
+        outs.append(o)
+        lses.append(l)
+    check_status()
+    assert prev == S
+    assert max(loads) <= 1.01 * sum(loads) / world
+    assert torch.equal(torch.cat(outs, 1), out) and torch.equal(torch.cat(lses, 1), lse)

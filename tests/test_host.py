@@ -77,3 +77,21 @@ def test_shard_queries_keeps_causal_positions():
     assert starts[0][0] == 22
     for (a, n), (b, _) in zip(starts, starts[1:]):
         assert a + n == b
+
+
+def test_balanced_shards_cover_everything_once_and_equalise_cost():
+    costs = dsa.causal_query_costs(4096, 4096, 2048)
+    assert int(costs[0]) == 1 + dsa.sharding.FIXED_TILES_PER_QUERY and int(costs[-1]) == 32 + dsa.sharding.FIXED_TILES_PER_QUERY
+    for world in (1, 2, 3, 4, 8):
+        spans = [dsa.shard_range_balanced(costs, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == 4096
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        loads = [int(costs[s:e].sum()) for s, e in spans]
+        assert max(loads) <= 1.005 * sum(loads) / world
+    # equal counts leave the last rank with 1 / 0.75 of the average number of (query, key) pairs at 8 ranks
+    pairs = [sum(min(t + 1, 2048) for t in range(*dsa.shard_range(4096, r, 8))) for r in range(8)]
+    assert abs(max(pairs) / (sum(pairs) / 8) - 1 / 0.75) < 0.01
+    assert dsa.shard_range_balanced([], 0, 2) == (0, 0)
+    assert [dsa.shard_range_balanced([1.0] * 5, r, 5) for r in range(5)] == [(i, i + 1) for i in range(5)]
+    with pytest.raises(ValueError):
+        dsa.shard_range_balanced(costs, 3, 2)

@@ -23,10 +23,11 @@ def _worker(rank: int, world: int, port: int, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     q, kv, idx = orc.make_sparse_mla_inputs(1, 10, 64, 4, 16, seed=0)
-    qs, ix, q_start = dsa.shard_queries(q, idx, rank, world, s_kv=64)
+    qs, ix, q_start = dsa.shard_queries(q, idx, rank, world, s_kv=64, balance=True)
     # the oracle stands in for the device kernel here: only the partition and reassembly are under test
     out, _ = orc.sparse_mla_fwd(qs, kv, ix, q_start_index_s=q_start)
-    sizes = [dsa.shard_range(10, r, world) for r in range(world)]
+    costs = dsa.causal_query_costs(10, 64, 16)
+    sizes = [dsa.shard_range_balanced(costs, r, world) for r in range(world)]
     pad = max(e - s for s, e in sizes)
     buf = torch.zeros((1, pad) + tuple(out.shape[2:]))
     buf[:, : out.shape[1]] = out

@@ -21,12 +21,14 @@ class HostPipelinedForward:
     """
 
     def __init__(self, kernel, q_shape, kv_shape, idx_shape, dv: int, dtype=torch.bfloat16, chunks: int = 8,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, q_start_index_s: Optional[int] = None):
         self.kernel = kernel
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         B, S, H, D = q_shape
         self.B, self.S, self.H, self.D, self.dv = B, S, H, D, dv
         self.S_kv, self.topk = kv_shape[1], idx_shape[3]
+        # causal position of query 0 of q_h: S_kv - S unless the caller holds a block of a longer sequence (a rank's shard)
+        self.q_start = self.S_kv - S if q_start_index_s is None else int(q_start_index_s)
         self.chunks = max(1, min(int(chunks), S))
         self.bounds = [(S * i // self.chunks, S * (i + 1) // self.chunks) for i in range(self.chunks)]
         cmax = max(e - s for s, e in self.bounds)
@@ -62,7 +64,7 @@ class HostPipelinedForward:
             main.wait_event(ready[i])
             qc = self.q_d[b][:, :n] if n == self.q_d[b].shape[1] else self.q_d[b][:, :n].contiguous()
             ic = self.idx_d[b][:, :n] if n == self.idx_d[b].shape[1] else self.idx_d[b][:, :n].contiguous()
-            o, l = self.kernel(qc, self.kv_d, ic, q_start_index_s=(self.S_kv - self.S) + s)
+            o, l = self.kernel(qc, self.kv_d, ic, q_start_index_s=self.q_start + s)
             done[i].record(main)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done[i])

@@ -15,13 +15,50 @@ def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < rem else 0)
 
 
-def shard_queries(q, indices, rank: int, world: int, s_kv: int):
+# Cost of one query of the causal prefill forward in key tiles: the tiles of 64 keys it gathers plus a fixed part (loading
+# its 128 x 576 Q block, draining and storing its 128 x 512 output) worth about two tiles.
+KEYS_PER_TILE = 64
+FIXED_TILES_PER_QUERY = 2
+
+
+def causal_query_costs(S: int, s_kv: int, topk: int):
+    """Relative cost of each of the S queries of a causal prefill call: query t sees min(s_kv - S + t + 1, topk) keys."""
+    import numpy as np
+    keys = np.minimum(np.arange(S, dtype=np.int64) + (s_kv - S) + 1, topk)
+    return (keys + KEYS_PER_TILE - 1) // KEYS_PER_TILE + FIXED_TILES_PER_QUERY
+
+
+def shard_range_balanced(costs, rank: int, world: int) -> Tuple[int, int]:
+    """[start, end) of ``len(costs)`` items for ``rank`` of ``world``: contiguous, cut where the running sum of ``costs``
+    crosses rank / world of the total, so that every rank gets about the same cost instead of the same count.  With equal
+    counts the causal prefill shape is unbalanced -- the early queries see few keys -- and the slowest rank, which sets the
+    time, would carry 1 / 0.75 of the average work at 8 ranks."""
+    import numpy as np
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} / world {world}")
+    c = np.asarray(costs, dtype=np.float64)
+    n = int(c.shape[0])
+    if n == 0:
+        return 0, 0
+    cum = np.cumsum(c)
+    total = float(cum[-1])
+    # item i belongs to the rank whose share contains the midpoint of the item's cost interval
+    mid = cum - 0.5 * c
+    bounds = [int(np.searchsorted(mid, total * r / world, side="left")) for r in range(world + 1)]
+    bounds[0], bounds[-1] = 0, n
+    return bounds[rank], bounds[rank + 1]
+
+
+def shard_queries(q, indices, rank: int, world: int, s_kv: int, balance: bool = False):
     """Query block of this rank for a BSND prefill call: (q_shard, indices_shard, q_start_index_s).
 
-    The causal position of local query t is ``q_start_index_s + t`` with
-    ``q_start_index_s = (s_kv - S) + start``."""
+    The causal position of local query t is ``q_start_index_s + t`` with ``q_start_index_s = (s_kv - S) + start``.
+    ``balance``: cut by the cost model of :func:`causal_query_costs` instead of by query count."""
     S = q.shape[1]
-    s, e = shard_range(S, rank, world)
+    if balance:
+        s, e = shard_range_balanced(causal_query_costs(S, s_kv, indices.shape[-1]), rank, world)
+    else:
+        s, e = shard_range(S, rank, world)
     return q[:, s:e].contiguous(), indices[:, s:e].contiguous(), (s_kv - S) + s
 
 
