@@ -66,6 +66,13 @@ int dsa_selftest_bounded_wait(int64_t budget_cycles, int32_t* gave_up, void* str
 int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits,
                     int32_t top_k, int32_t* out_idx, float* out_val, void* stream);
 
+/* dsa_topk_select without the final sort: the same SET of top_k indices per row (the same lowest-index tie rule at the
+ * threshold), written in ASCENDING INDEX order instead of descending score order.  For consumers that only need the set --
+ * the sparse attention that follows the indexer -- at about half the selector's time.  No reference counterpart (the reference
+ * selector always sorts). */
+int dsa_topk_select_unordered(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits,
+                              int32_t top_k, int32_t* out_idx, float* out_val, void* stream);
+
 /* Lightning-indexer scores: scores[b,s1,s2] = sum_h w[b,s1,h] * relu(q[b,s1,h,:] . k[b,s2,0,:]).
  * q [B,S1,N1,D], k [B,S2,1,D] (dtype), w [B,S1,N1] fp32, scores [B,S1,S2] fp32.
  * sparse_mode 3 = causal (key s2 is a candidate iff s2 < ak - aq + s1 + 1), 0 = all ak keys.
@@ -90,6 +97,12 @@ int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t 
                           int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b,
                           int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
                           void* stream);
+
+/* dsa_lightning_indexer with the selector of dsa_topk_select_unordered: index sets in ascending index order. */
+int dsa_lightning_indexer_unordered(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1,
+                                    int32_t D, int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b,
+                                    int32_t top_k, int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes,
+                                    void* stream);
 
 /* dsa_lightning_indexer over a PAGED key cache: k_cache [num_blocks, block_size, 1, D] (dtype), block_table [B, max_blocks]
  * int32; logical key j of batch b is cache row block_table[b, j / block_size] * block_size + j % block_size.  S2 is the

@@ -84,3 +84,27 @@ def test_strided_rows():
     got = dsa.topk_select_raw(xs[:, :3000], 256).cpu().numpy()  # row stride 4096, n = 3000
     check_status()
     assert np.array_equal(got, orc.topk_select(x[:, :3000], 256))
+
+
+@pytest.mark.parametrize("rows,n,k", [(64, 4096, 2048), (33, 8192, 2048), (16, 1000, 100), (8, 300, 512)])
+def test_unordered_mode_returns_the_same_sets_in_index_order(rows, n, k):
+    """ordered=False skips the final sort: per row the same index set as the ordered call (ties at the threshold resolved
+    towards the lower index in both), ascending, values in step with the indices, -1 / -inf behind the selected ones."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator().manual_seed(rows + n)
+    x = torch.randn((rows, n), generator=g)
+    cols = torch.arange(7, n, 7)
+    x[:, cols] = x[:, cols - 1]                               # plenty of exact ties
+    lim = torch.randint(1, n + 1, (rows,), generator=g, dtype=torch.int32)
+    xs, ls = x.cuda(), lim.cuda()
+    a, av = dsa.topk_select_raw(xs, k, ls, return_values=True)
+    b, bv = dsa.topk_select_raw(xs, k, ls, return_values=True, ordered=False)
+    check_status()
+    a, b, bv = a.cpu().numpy(), b.cpu().numpy(), bv.cpu().numpy()
+    ref = orc.topk_select(x.numpy(), k, lim.numpy())
+    assert np.array_equal(a, ref)
+    for r in range(rows):
+        sel = b[r][b[r] >= 0]
+        assert np.array_equal(sel, np.sort(ref[r][ref[r] >= 0]))           # same set, ascending
+        assert (b[r][len(sel):] == -1).all() and np.isneginf(bv[r][len(sel):]).all()
+        assert np.array_equal(bv[r][: len(sel)], x.numpy()[r, sel])

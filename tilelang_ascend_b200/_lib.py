@@ -22,6 +22,10 @@ SIGNATURES = {
     "dsa_kernel_status": (c_int32, [ctypes.POINTER(c_int32)]),
     "dsa_selftest_bounded_wait": (c_int32, [c_int64, c_void_p, c_void_p]),
     "dsa_topk_select": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
+    "dsa_topk_select_unordered": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
+    "dsa_lightning_indexer_unordered": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                                  c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_size_t,
+                                                  c_void_p]),
     "dsa_indexer_scores": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
                                      c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "dsa_lightning_indexer_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32]),

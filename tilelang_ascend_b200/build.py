@@ -17,7 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 LIB = os.path.join(PKG, "libdsa_b200.so")
-SOURCES = ["capi.cu", "sparse_mla_fwd.cu", "sparse_mla_bwd.cu", "sparse_mla_bwd_tc.cu", "indexer.cu", "topk.cu", "no_alloc.cu", "sink_combine.cu", "block_sparse_logits.cu", "selftest.cu"]
+SOURCES = ["capi.cu", "sparse_mla_fwd.cu", "sparse_mla_fwd_pair.cu", "sparse_mla_bwd.cu", "sparse_mla_bwd_tc.cu", "indexer.cu", "topk.cu", "no_alloc.cu", "sink_combine.cu", "block_sparse_logits.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

@@ -17,7 +17,7 @@ int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t st
 int sparse_mla_fwd_auto_nsplit(const FwdParams& p, int sms);
 size_t topk_smem_bytes(int n, int top_k, int* kpow2_out);
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
-                       int32_t* out_idx, float* out_val, cudaStream_t stream);
+                       int32_t* out_idx, float* out_val, cudaStream_t stream, int ordered = 1);
 bool indexer_tc_supported(const IndexerParams& p);
 int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream);
@@ -141,8 +141,8 @@ int dsa_selftest_bounded_wait(int64_t budget_cycles, int32_t* gave_up, void* str
   return err ? fail_cuda("bounded_wait_selftest launch", err) : 0;
 }
 
-int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
-                    int32_t* out_idx, float* out_val, void* stream) {
+static int topk_select_impl(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
+                            int32_t* out_idx, float* out_val, void* stream, int ordered) {
   if (!scores || !out_idx) return fail("null tensor pointer");
   if (rows < 0 || n <= 0 || top_k <= 0 || row_stride < n) return fail("need rows >= 0, n > 0, top_k > 0, row_stride >= n");
   if (rows == 0) return 0;
@@ -151,8 +151,18 @@ int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_st
   if (dsa::topk_smem_bytes(static_cast<int>(n), top_k, nullptr) > 220 * 1024)
     return fail("row too long for the shared-memory selector (n * 4 + pow2(top_k) * 8 must fit 220 KB)");
   int err = dsa::launch_topk_select(scores, rows, static_cast<int>(n), row_stride, limits, top_k, out_idx, out_val,
-                                    static_cast<cudaStream_t>(stream));
+                                    static_cast<cudaStream_t>(stream), ordered);
   return err ? fail_cuda("topk_select launch", err) : 0;
+}
+
+int dsa_topk_select(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
+                    int32_t* out_idx, float* out_val, void* stream) {
+  return topk_select_impl(scores, rows, n, row_stride, limits, top_k, out_idx, out_val, stream, 1);
+}
+
+int dsa_topk_select_unordered(const float* scores, int64_t rows, int64_t n, int64_t row_stride, const int32_t* limits, int32_t top_k,
+                              int32_t* out_idx, float* out_val, void* stream) {
+  return topk_select_impl(scores, rows, n, row_stride, limits, top_k, out_idx, out_val, stream, 0);
 }
 
 // Paged keys of the indexer: block table [B, max_blocks] over a cache of num_blocks blocks of block_size rows (all zero = dense k).
@@ -205,33 +215,43 @@ size_t dsa_lightning_indexer_workspace_bytes(int32_t B, int32_t S1, int32_t S2) 
   return scores + rows * sizeof(int32_t);
 }
 
-int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
-                          int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, int32_t top_k,
-                          int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes, void* stream) {
+static int lightning_indexer_impl(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
+                                  int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, int32_t top_k,
+                                  int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes, void* stream,
+                                  const PagedKeys& paged, int ordered) {
   if (!workspace || workspace_bytes < dsa_lightning_indexer_workspace_bytes(B, S1, S2)) return fail("workspace missing or too small");
   if (!out_idx) return fail("null tensor pointer");
   const size_t rows = static_cast<size_t>(B) * S1;
   float* scores = static_cast<float*>(workspace);
   int32_t* limits = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ((rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255)));
-  int rc = indexer_scores_impl(q, k, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream);
+  int rc = indexer_scores_impl(q, k, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream, paged);
   if (rc) return rc;
-  return dsa_topk_select(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream);
+  return topk_select_impl(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream, ordered);
+}
+
+int dsa_lightning_indexer(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
+                          int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, int32_t top_k,
+                          int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes, void* stream) {
+  return lightning_indexer_impl(q, k, w, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, top_k, out_idx, out_val, workspace,
+                                workspace_bytes, stream, PagedKeys(), 1);
+}
+
+int dsa_lightning_indexer_unordered(const void* q, const void* k, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
+                                    int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, int32_t top_k,
+                                    int32_t* out_idx, float* out_val, void* workspace, size_t workspace_bytes, void* stream) {
+  return lightning_indexer_impl(q, k, w, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, top_k, out_idx, out_val, workspace,
+                                workspace_bytes, stream, PagedKeys(), 0);
 }
 
 int dsa_lightning_indexer_paged(const void* q, const void* k_cache, const float* w, int32_t B, int32_t S1, int32_t S2, int32_t N1, int32_t D,
                                 int32_t dtype, int32_t sparse_mode, const int32_t* q_len_b, const int32_t* k_len_b, const int32_t* block_table,
                                 int32_t block_size, int32_t max_blocks, int32_t num_blocks, int32_t top_k, int32_t* out_idx, float* out_val,
                                 void* workspace, size_t workspace_bytes, void* stream) {
-  if (!workspace || workspace_bytes < dsa_lightning_indexer_workspace_bytes(B, S1, S2)) return fail("workspace missing or too small");
-  if (!out_idx || !block_table) return fail("null tensor pointer");
-  const size_t rows = static_cast<size_t>(B) * S1;
-  float* scores = static_cast<float*>(workspace);
-  int32_t* limits = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ((rows * S2 * sizeof(float) + 255) & ~static_cast<size_t>(255)));
+  if (!block_table) return fail("null tensor pointer");
   PagedKeys paged;
   paged.block_table = block_table; paged.block_size = block_size; paged.max_blocks = max_blocks; paged.num_blocks = num_blocks;
-  int rc = indexer_scores_impl(q, k_cache, w, scores, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, limits, 0, stream, paged);
-  if (rc) return rc;
-  return dsa_topk_select(scores, static_cast<int64_t>(rows), S2, S2, limits, top_k, out_idx, out_val, stream);
+  return lightning_indexer_impl(q, k_cache, w, B, S1, S2, N1, D, dtype, sparse_mode, q_len_b, k_len_b, top_k, out_idx, out_val, workspace,
+                                workspace_bytes, stream, paged, 1);
 }
 
 int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B, int32_t S,

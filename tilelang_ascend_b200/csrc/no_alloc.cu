@@ -19,7 +19,7 @@ namespace dsa {
 void set_last_error(const std::string& msg);
 size_t topk_smem_bytes(int n, int top_k, int* kpow2_out);
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
-                       int32_t* out_idx, float* out_val, cudaStream_t stream);
+                       int32_t* out_idx, float* out_val, cudaStream_t stream, int ordered = 1);
 bool indexer_tc_supported(const IndexerParams& p);
 int launch_indexer_scores_tc(const IndexerParams& p, bool bf16, cudaStream_t stream);
 int launch_indexer_scores_generic(const IndexerParams& p, bool bf16, cudaStream_t stream);

@@ -220,6 +220,47 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- the same for a pair of CTAs (cta_group::2): ONE thread of the even CTA of a 2-CTA cluster issues an MMA that runs on
+// both SMs.  Each CTA supplies its half of the rows of A (from its own shared memory or tensor memory) and its half of the
+// rows of B (the N dimension) at the SAME shared-memory offsets / tensor-memory addresses, and receives the rows of D that
+// belong to its rows of A: with M = 128 (64 rows per CTA) D[m][n] sits in lane m + 64 (n / (N/2)), column n % (N/2) of the
+// CTA's tensor memory, and an A operand in tensor memory holds row m in lanes m AND m + 64.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {  // by the same warp of BOTH CTAs
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier at shared-memory offset `bar` of EVERY CTA named in cta_mask (bit i = CTA i of the cluster) receives one
+// arrival once all tcgen05 operations this thread issued so far have completed on both SMs.  (An mbarrier arrive that is
+// broadcast to the CTAs of the cluster -- not a load.)
+__device__ __forceinline__ void umma_pair_commit(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
+
 // TMEM -> registers: the warp reads its 32 lanes (lane field of taddr = 32 * (warp % 4)), each
 // thread gets 32 / 16 / 8 consecutive 32-bit columns of its own lane.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {

@@ -13,85 +13,14 @@
 //    Q K^T and the output columns of P V and exchange partial scores through distributed shared memory.
 //  * sparse_mla_fwd_generic_kernel -- any D <= 640 / DV <= 512 (e.g. the GQA example with dim 128):
 //    CUDA-core fp32, one warp per head.
+#include <stdlib.h>
 #include <type_traits>
 
+#include "fwd_common.cuh"
 #include "params.h"
 #include "ptx.cuh"
 
 namespace dsa {
-
-// -------------------------------------------------------------------------------------------------
-// shared helpers
-// -------------------------------------------------------------------------------------------------
-struct RowCtx {
-  int b, t;         // batch, query inside the batch
-  int pos_limit;    // largest key index allowed by the causal rule (INT_MAX when not causal)
-  int kv_len;       // number of keys of this sequence
-  const int32_t* idx_row;
-  bool active;      // query exists (t < q_len)
-};
-
-__device__ __forceinline__ RowCtx make_row_ctx(const FwdParams& p, int bt) {
-  RowCtx c;
-  c.b = bt / p.S;
-  c.t = bt - c.b * p.S;
-  const int qs = p.q_start_b ? p.q_start_b[c.b] : p.q_start;
-  c.kv_len = p.kv_len_b ? p.kv_len_b[c.b] : p.S_kv;
-  c.pos_limit = p.causal ? qs + c.t : 0x7fffffff;
-  c.idx_row = p.indices + static_cast<int64_t>(bt) * p.topk;
-  c.active = p.q_len_b ? (c.t < p.q_len_b[c.b]) : true;
-  return c;
-}
-
-__device__ __forceinline__ bool index_valid(const RowCtx& c, int idx) {
-  return idx >= 0 && idx < c.kv_len && idx <= c.pos_limit;
-}
-
-// Row number of key `idx` of batch b inside the kv tensor.
-__device__ __forceinline__ int64_t kv_row(const FwdParams& p, int b, int idx) {
-  if (p.block_table) {
-    const int blk = p.block_table[static_cast<int64_t>(b) * p.max_blocks + idx / p.block_size];
-    return static_cast<int64_t>(blk) * p.block_size + idx % p.block_size;
-  }
-  return static_cast<int64_t>(b) * p.S_kv + idx;
-}
-
-// Packed pairs of fp32 (one instruction for two values) and the three-input maximum of sm_100.
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
-template <bool kBF16>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  if constexpr (kBF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
 
 // -------------------------------------------------------------------------------------------------
 // tcgen05 kernel: persistent 2-CTA clusters, one (query, block of 128 heads) item at a time
@@ -834,7 +763,32 @@ bool sparse_mla_fwd_tc_supported(const FwdParams& p) {
   return (p.D == tc::kD || p.D == tc::kDV) && p.DV == tc::kDV && p.topk <= tc::kMaxTiles * tc::kBK && static_cast<long long>(p.B) * p.S_kv <= 0x7fffffffLL;
 }
 
+bool sparse_mla_fwd_pair_supported(const FwdParams& p);
+int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, int sms, cudaStream_t stream);
+
+static int launch_combine(const FwdParams& p, bool bf16, cudaStream_t stream) {
+  const int64_t rows = static_cast<int64_t>(p.B) * p.S * p.H;
+  if (bf16)
+    sparse_mla_fwd_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 128, 0, stream>>>(p.part_out, p.part_lse, reinterpret_cast<__nv_bfloat16*>(p.out),
+                                                                                                p.lse, rows, p.nsplit, p.DV);
+  else
+    sparse_mla_fwd_combine_kernel<__half><<<static_cast<unsigned>(rows), 128, 0, stream>>>(p.part_out, p.part_lse, reinterpret_cast<__half*>(p.out), p.lse,
+                                                                                         rows, p.nsplit, p.DV);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream) {
+  // DSA_FWD_KERNEL=pair in the environment selects the kernel of sparse_mla_fwd_pair.cu (cta_group::2 MMAs)
+  const char* which = getenv("DSA_FWD_KERNEL");
+  if (which && which[0] == 'p' && sparse_mla_fwd_pair_supported(p)) {
+    int dev = 0, sms = 0;
+    cudaError_t e0;
+    if ((e0 = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(e0);
+    if ((e0 = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e0);
+    int rc = launch_sparse_mla_fwd_pair(p, bf16, sms, stream);
+    if (rc != 0 || p.nsplit <= 1) return rc;
+    return launch_combine(p, bf16, stream);
+  }
   const bool rope = p.D == tc::kD;
   auto kern = rope ? (bf16 ? sparse_mla_fwd_tc_kernel<true, true> : sparse_mla_fwd_tc_kernel<false, true>)
                    : (bf16 ? sparse_mla_fwd_tc_kernel<true, false> : sparse_mla_fwd_tc_kernel<false, false>);

@@ -11,7 +11,8 @@
 // compaction (per-warp counts, prefix over warps, ordered write) takes everything above it plus the
 // lowest-index ties, and a stable least-significant-digit radix sort (four 8-bit passes, descending) of the
 // <= k survivors fixes the output order: the compaction leaves equal keys in ascending index order and
-// a stable sort keeps them so.
+// a stable sort keeps them so.  With ordered = 0 the sort is left out and the selected SET comes out in ascending index
+// order (what the sparse attention after the indexer needs, and the order in which its row gather is most local).
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -40,7 +41,7 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 template <int kMaxRounds>
 __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
                                                                      const int32_t* __restrict__ limits, int top_k, int kpow2,
-                                                                     int32_t* __restrict__ out_idx, float* __restrict__ out_val) {
+                                                                     int32_t* __restrict__ out_idx, float* __restrict__ out_val, int ordered) {
   using namespace topk;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const size_t front = max(static_cast<size_t>(kpow2) * 8, static_cast<size_t>(kWarps) * 256 * 4);
@@ -206,7 +207,9 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
   unsigned long long* src = sortbuf;
   unsigned long long* dst = reinterpret_cast<unsigned long long*>(keys);
   uint16_t* wcnt = reinterpret_cast<uint16_t*>(keys) + static_cast<size_t>(kpow2) * 4;  // [kWarps][256], behind the second buffer
-  if (kk <= 64u) {
+  if (!ordered) {
+    // the caller wants the index SET only: the survivors stay as the compaction left them, in ascending index order
+  } else if (kk <= 64u) {
     // up to 64 survivors: one warp sorts them in registers (two per lane, bitonic network, descending on the whole
     // 64-bit element = key, then lower index), no block barriers
     if (warp == 0) {
@@ -326,7 +329,7 @@ size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
 }
 
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
-                       int32_t* out_idx, float* out_val, cudaStream_t stream) {
+                       int32_t* out_idx, float* out_val, cudaStream_t stream, int ordered) {
   int kp = 0;
   const size_t smem = topk_smem_bytes(n, top_k, &kp);
   if (top_k > topk::kWarps * 32 * 16) return static_cast<int>(cudaErrorInvalidValue);
@@ -334,7 +337,7 @@ int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_str
   auto kern = small ? topk_select_kernel<4> : topk_select_kernel<16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx, out_val);
+  kern<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx, out_val, ordered);
   return static_cast<int>(cudaGetLastError());
 }
 

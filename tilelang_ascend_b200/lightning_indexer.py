@@ -39,8 +39,11 @@ def indexer_scores_raw(query, key, weights, *, sparse_mode: int = 3, q_len_b=Non
 
 def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode: int, q_len_b=None, k_len_b=None,
                           return_value: bool = False, workspace: Optional[torch.Tensor] = None, block_table=None,
-                          max_keys: Optional[int] = None):
+                          max_keys: Optional[int] = None, ordered: bool = True):
     """Fused scores + top-k of BSND inputs: indices int32 [B,S1,1,K] (+ fp32 values).
+
+    ``ordered=False`` leaves the selector's final sort out: the same index SETS, in ascending index order (enough for the
+    sparse attention that consumes them, which does not depend on the order of a query's list).
 
     With ``block_table`` [B, max_blocks] int32, ``key`` is a paged cache [num_blocks, block_size, 1, D] that the kernel
     addresses through the table (no dense copy); ``max_keys`` (default max_blocks * block_size) is the largest logical
@@ -72,12 +75,18 @@ def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode
     val = torch.empty((B, S1, 1, sparse_count), dtype=torch.float32, device=dev) if return_value else None
     with torch.cuda.device(dev):
         if block_table is not None:
+            if not ordered:
+                raise ValueError("ordered=False is not available with paged keys")
             _lib.check(lib.dsa_lightning_indexer_paged(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
                                                        int(sparse_mode), ptr(q_len_b), ptr(k_len_b), ptr(block_table), block_size, max_blocks,
                                                        num_blocks, int(sparse_count), ptr(idx), ptr(val), ptr(workspace), need,
                                                        current_stream(dev)))
         else:
-            _lib.check(lib.dsa_lightning_indexer(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
+            if block_table is None and not ordered:
+                entry = lib.dsa_lightning_indexer_unordered
+            else:
+                entry = lib.dsa_lightning_indexer
+            _lib.check(entry(ptr(query), ptr(key), ptr(weights), B, S1, S2, N1, D, dtype_code(query.dtype),
                                                  int(sparse_mode), ptr(q_len_b), ptr(k_len_b), int(sparse_count), ptr(idx), ptr(val),
                                                  ptr(workspace), need, current_stream(dev)))
     return idx, val

@@ -11,10 +11,12 @@ from . import _lib
 from .adapter import current_stream, ptr, torch_dtype
 
 
-def topk_select_raw(scores: torch.Tensor, top_k: int, limits: Optional[torch.Tensor] = None, return_values: bool = False):
+def topk_select_raw(scores: torch.Tensor, top_k: int, limits: Optional[torch.Tensor] = None, return_values: bool = False,
+                    ordered: bool = True):
     """scores fp32 [rows, n] (row stride may exceed n) -> int32 [rows, top_k] (+ fp32 values).
 
-    Descending score, equal scores by ascending index; -1 / -inf in unused slots."""
+    Descending score, equal scores by ascending index; -1 / -inf in unused slots.  ``ordered=False``: the same set of
+    indices per row (same tie rule at the threshold) in ascending index order, without the final sort."""
     if scores.dim() != 2 or scores.stride(1) != 1:
         raise ValueError("scores must be 2-dimensional with unit inner stride")
     dev = _check(scores, limits)
@@ -22,8 +24,9 @@ def topk_select_raw(scores: torch.Tensor, top_k: int, limits: Optional[torch.Ten
     idx = torch.empty((rows, top_k), dtype=torch.int32, device=dev)
     val = torch.empty((rows, top_k), dtype=torch.float32, device=dev) if return_values else None
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().dsa_topk_select(ptr(scores), rows, n, scores.stride(0), ptr(limits), int(top_k), ptr(idx),
-                                               ptr(val), current_stream(dev)))
+        entry = _lib.load().dsa_topk_select if ordered else _lib.load().dsa_topk_select_unordered
+        _lib.check(entry(ptr(scores), rows, n, scores.stride(0), ptr(limits), int(top_k), ptr(idx),
+                         ptr(val), current_stream(dev)))
     return (idx, val) if return_values else idx
 
 
