@@ -7,6 +7,7 @@
 #include <string>
 
 #include "../../include/dsa_b200.h"
+#include "launch_util.h"
 #include "params.h"
 
 namespace dsa {
@@ -82,6 +83,10 @@ int get_status_word(int** out) {
   return 0;
 }
 
+#ifdef DSA_TRACE
+long long* g_trace = nullptr;  // development builds only: device buffer the forward kernel's clock samples go to
+#endif
+
 bool dtype_ok(int dtype) { return dtype == DSA_DTYPE_BF16 || dtype == DSA_DTYPE_FP16; }
 
 int fill_fwd_params(dsa::FwdParams* p, const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B,
@@ -103,12 +108,19 @@ int fill_fwd_params(dsa::FwdParams* p, const void* q, const void* kv, const int3
   p->block_table = block_table; p->block_size = block_size; p->max_blocks = max_blocks;
   p->scale_log2 = sm_scale * 1.4426950408889634f;
   p->nsplit = 1; p->part_out = nullptr; p->part_lse = nullptr;
+#ifdef DSA_TRACE
+  p->trace = g_trace;
+#endif
   return get_status_word(&p->status);
 }
 
 }  // namespace
 
 extern "C" {
+
+#ifdef DSA_TRACE
+void dsa_set_trace(long long* device_buffer) { g_trace = device_buffer; }
+#endif
 
 int dsa_init(void) {
   int* s = nullptr;
@@ -273,7 +285,7 @@ int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, vo
 
 int dsa_sparse_mla_fwd_splitkv_nsplit(int32_t B, int32_t S, int32_t H, int32_t topk) {
   int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 1;
+  if (dsa::current_device_sms(&dev, &sms) != cudaSuccess) return 1;
   dsa::FwdParams p{};
   p.B = B; p.S = S; p.H = H; p.topk = topk;
   return dsa::sparse_mla_fwd_auto_nsplit(p, sms);

@@ -20,6 +20,7 @@
 #include <string.h>
 #include <type_traits>
 
+#include "launch_util.h"
 #include "params.h"
 #include "ptx.cuh"
 
@@ -374,8 +375,10 @@ static int launch_indexer_tc_n1(const IndexerParams& p_in, cudaStream_t stream) 
     for (int r = itc::kKeys; r >= 8; r >>= 1)
       if (p.block_size % r == 0) { p.box_rows = r; break; }
   auto kern = indexer_scores_tc_kernel<kBF16, N1>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(itc::kSmemBytes));
+  int dev = 0, sms = 0;
+  cudaError_t e = current_device_sms(&dev, &sms);
   if (e != cudaSuccess) return static_cast<int>(e);
+  if ((e = ensure_dynamic_smem(kern, dev, static_cast<int>(itc::kSmemBytes))) != cudaSuccess) return static_cast<int>(e);
   constexpr int QB = itc::kN / N1;
   const int nqb = (p.S1 + QB - 1) / QB;
   alignas(64) CUtensorMap kmap;

@@ -32,6 +32,9 @@ struct FwdParams {
   int nsplit;
   float* part_out;
   float* part_lse;
+#ifdef DSA_TRACE
+  long long* trace;            // development builds only: clock samples of cluster 0, [2 CTAs][16 events][64 tiles]
+#endif
 };
 
 // Sparse MLA backward: the forward's fields (out / lse hold the forward results) plus gradients.

@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "fwd_common.cuh"
+#include "launch_util.h"
 #include "params.h"
 #include "ptx.cuh"
 
@@ -764,7 +765,7 @@ bool sparse_mla_fwd_tc_supported(const FwdParams& p) {
 }
 
 bool sparse_mla_fwd_pair_supported(const FwdParams& p);
-int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, int sms, cudaStream_t stream);
+int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, cudaStream_t stream);
 
 static int launch_combine(const FwdParams& p, bool bf16, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(p.B) * p.S * p.H;
@@ -778,25 +779,21 @@ static int launch_combine(const FwdParams& p, bool bf16, cudaStream_t stream) {
 }
 
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream) {
-  // DSA_FWD_KERNEL=pair in the environment selects the kernel of sparse_mla_fwd_pair.cu (cta_group::2 MMAs)
+  // The kernel of sparse_mla_fwd_pair.cu (cta_group::2 MMAs) is the default; DSA_FWD_KERNEL=split in the environment selects
+  // the kernel below (each CTA all 128 heads and half of the dims), which the tests use as a cross-check.
   const char* which = getenv("DSA_FWD_KERNEL");
-  if (which && which[0] == 'p' && sparse_mla_fwd_pair_supported(p)) {
-    int dev = 0, sms = 0;
-    cudaError_t e0;
-    if ((e0 = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(e0);
-    if ((e0 = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e0);
-    int rc = launch_sparse_mla_fwd_pair(p, bf16, sms, stream);
+  if (!(which && which[0] == 's') && sparse_mla_fwd_pair_supported(p)) {
+    int rc = launch_sparse_mla_fwd_pair(p, bf16, stream);
     if (rc != 0 || p.nsplit <= 1) return rc;
     return launch_combine(p, bf16, stream);
   }
   const bool rope = p.D == tc::kD;
   auto kern = rope ? (bf16 ? sparse_mla_fwd_tc_kernel<true, true> : sparse_mla_fwd_tc_kernel<false, true>)
                    : (bf16 ? sparse_mla_fwd_tc_kernel<true, false> : sparse_mla_fwd_tc_kernel<false, false>);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tc::kSmemBytes));
-  if (e != cudaSuccess) return static_cast<int>(e);
   int dev = 0, sms = 0;
-  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(e);
-  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e);
+  cudaError_t e = current_device_sms(&dev, &sms);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if ((e = ensure_dynamic_smem(kern, dev, static_cast<int>(tc::kSmemBytes))) != cudaSuccess) return static_cast<int>(e);
   // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
   const long long items = static_cast<long long>(p.B) * p.S * ((p.H + tc::kM - 1) / tc::kM);
   long long clusters = sms / 2 > 0 ? sms / 2 : 1;

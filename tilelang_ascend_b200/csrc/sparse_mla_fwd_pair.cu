@@ -25,6 +25,7 @@
 // broadcast to the same barrier in both CTAs.  Every wait is bounded; a wait that gives up records status 1 and all roles
 // fall through to the teardown.
 #include "fwd_common.cuh"
+#include "launch_util.h"
 #include "params.h"
 #include "ptx.cuh"
 
@@ -36,7 +37,7 @@ constexpr int kM = 128;                                // heads per cluster
 constexpr int kHeads = 64;                             // heads per CTA
 constexpr int kBK = 64;                                // keys per tile
 constexpr int kKeys = 32;                              // keys per tile and CTA
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kMaxTiles = 128;                         // topk <= 8192
 constexpr uint32_t kChunk = kKeys * 128;               // 4096: 32 keys x 64 dims, 128-byte swizzle
 constexpr uint32_t kStageBytes = 9 * kChunk;           // 36864: 8 latent chunks + the rope chunk
@@ -45,51 +46,64 @@ constexpr int kQTmemDims = 384;                        // Q dims kept in tensor 
 constexpr uint32_t kQChunk = kHeads * 128;             // 8192: 64 heads x 64 dims
 constexpr uint32_t kQBytes = 3 * kQChunk;              // Q dims 384..575 in shared memory
 constexpr uint32_t kPBytes = kHeads * kBK * 2;         // 8192: P of one tile [64 heads x 64 keys]
-constexpr uint32_t kOffQ = kStages * kStageBytes;      // 110592
-constexpr uint32_t kOffP = kOffQ + kQBytes;            // 135168: two P buffers
-constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;      // 151552
+constexpr uint32_t kOffQ = kStages * kStageBytes;      // 147456
+constexpr uint32_t kOffP = kOffQ + 2 * kQBytes;        // two Q buffers (items alternate), then two P buffers
+constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
 constexpr uint32_t kOffRowMax = kOffBar + 1024;        // [2][4][64] floats: row maxima of the four threads of a row, by tile parity
 constexpr uint32_t kOffRowSum = kOffRowMax + 2 * 4 * 64 * 4;   // [4][64] floats
 constexpr uint32_t kOffMask = kOffRowSum + 4 * 64 * 4;         // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;    // [2][kMaxTiles] 16-bit tile ids
 constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;    // [2] {tile count, run flag}; scratch words of the warps behind it
-constexpr uint32_t kSmemBytes = kOffInfo + 256 + 1024;         // + slack to align the base to 1024 B
+constexpr uint32_t kOffXScratch = kOffInfo + 256;              // [4 exchange warps][32 rows x 64 bytes]: transposition of Q rows
+constexpr uint32_t kSmemBytes = kOffXScratch + 4 * 2048 + 1024;  // + slack to align the base to 1024 B
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 constexpr int kSoftmaxWarps = 8;                       // warp w: lanes 32 (w & 3) .. +31, score columns 16 (w >> 2) .. +15
 constexpr int kFirstGatherWarp = 8;
 constexpr int kFirstExchangeWarp = 12;                 // 12..15: (w & 3) is also the lane quarter of their tensor-memory stores
-constexpr int kQkWarp = 16;                            // even CTA: Q K^T issuer; odd CTA: forwards kv_full
+constexpr int kQkWarp = 16;                            // even CTA: Q K^T issuer of the even tiles; odd CTA: forwards kv_full
 constexpr int kPvWarp = 17;                            // even CTA: P V issuer; odd CTA: forwards v_full
-constexpr int kThreads = 576;
+constexpr int kQkWarpB = 18;                           // even CTA: Q K^T issuer of the odd tiles; odd CTA: forwards s_free
+constexpr int kRelayWarp = 19;                         // even CTA: idle; odd CTA: forwards p_ready
+constexpr int kThreads = 640;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 320;  // O 256 | S0 32 | S1 32 | Q 192
 constexpr float kRescaleThreshold = 8.0f;              // log2 units: P stays below 2^8
 constexpr uint32_t kGatherBarrier = 5;                 // named barrier of the 128 gather threads
-// barrier slots (8 bytes each)
-constexpr int kBarKvFull = 0;        // [3] count 128: cp.async completion of this CTA's gather threads
-constexpr int kBarPeerKvFull = 3;    // [3] count 1, even CTA: the odd CTA's gather of the stage landed
-constexpr int kBarKvEmpty = 6;       // [3] count 1: commit after the P V MMAs of the stage
-constexpr int kBarSFull = 9;         // [2] count 1: commit after the Q K^T MMAs
-constexpr int kBarSFree = 11;        // [2] count 24, even CTA: the softmax (and exchange) warps of both CTAs are past the scores
-constexpr int kBarPeerRead = 13;     // [3] count 4: the peer's exchange warps hold their swap region in registers
-constexpr int kBarVFull = 16;        // [3] count 1 + 16384 bytes: the peer's half of the swap landed here
-constexpr int kBarPeerVFull = 19;    // [3] count 1, even CTA: ... landed in the odd CTA
-constexpr int kBarPReady = 22;       // [2] count 16, even CTA: the softmax warps of both CTAs wrote P
-constexpr int kBarPFree = 24;        // [2] count 1: commit after the P V MMAs that read this P buffer
-constexpr int kBarQReady = 26;       // count 8, even CTA: the exchange warps of both CTAs loaded the item's Q
-constexpr int kBarQFree = 27;        // count 1: commit after the last Q K^T of an item
-constexpr int kBarOFree = 28;        // count 16, even CTA: the softmax warps drained the previous item's output
-constexpr int kBarInfoFull = 29;     // [2] count 1: tile list of an item published by the gather warps
-constexpr int kBarInfoEmpty = 31;    // [2] count 14: softmax, exchange, issuer / forwarding warps are done with the list
-constexpr int kBarCount = 33;
+// barrier slots (8 bytes each).  "even CTA" barriers receive one remote arrival per event from a forwarding thread of the odd CTA:
+// a remote arrive with release semantics costs its issuer about a thousand clocks, which the softmax warps cannot afford per
+// tile -- they arrive on barriers of their own CTA and a dedicated thread passes the completed phase on.
+constexpr int kBarKvFull = 0;        // [4] count 128: cp.async completion of this CTA's gather threads
+constexpr int kBarPeerKvFull = 4;    // [4] count 1, even CTA: the odd CTA's gather of the stage landed
+constexpr int kBarKvEmpty = 8;       // [4] count 1: commit after the P V MMAs of the stage
+constexpr int kBarSFull = 12;        // [2] count 1: commit after the Q K^T MMAs
+constexpr int kBarSFree = 14;        // [2] count 12: this CTA's softmax (and exchange) warps are past the scores
+constexpr int kBarPeerSFree = 16;    // [2] count 1, even CTA: ... the odd CTA's
+constexpr int kBarPeerRead = 18;     // [4] count 4: the peer's exchange warps hold their swap region in registers
+constexpr int kBarVFull = 22;        // [4] count 1 + 16384 bytes: the peer's half of the swap landed here
+constexpr int kBarPeerVFull = 26;    // [4] count 1, even CTA: ... landed in the odd CTA
+constexpr int kBarPReady = 30;       // [2] count 8: this CTA's softmax warps wrote P
+constexpr int kBarPeerPReady = 32;   // [2] count 1, even CTA: ... the odd CTA's
+constexpr int kBarPFree = 34;        // [2] count 1: commit after the P V MMAs that read this P buffer
+constexpr int kBarQReady = 36;       // count 8, even CTA: the exchange warps of both CTAs loaded the item's Q
+constexpr int kBarQFree = 37;        // count 2: both Q K^T issuers are done with the item's Q (commit after their last MMAs of the item)
+constexpr int kBarOFree = 38;        // count 16, even CTA: the softmax warps drained the previous item's output
+constexpr int kBarInfoFull = 39;     // [2] count 1: tile list of an item published by the gather warps
+constexpr int kBarInfoEmpty = 41;    // [2] count 16 (15 in the even CTA): softmax, exchange, issuer / forwarding warps are done with the list
+constexpr int kBarCount = 43;
 }  // namespace pr
 
+// Remote arrives in this kernel are RELAXED: an arrive with release semantics at cluster scope costs its thread about 1100
+// clocks here (measured), far too much per tile.  None of them publishes data that another SM reads through the memory
+// system: what they announce -- rows landed in this SM's shared memory, tensor-memory loads / stores of this SM finished,
+// shared-memory loads finished -- is complete on THIS SM before the arrive is issued (observed on a local barrier, or held
+// back by a dependent instruction), and the consumers are this SM's tensor core, started by the even CTA's issuing thread
+// only after it has seen the arrival, or the peer's st.async writes, issued only after it has seen the arrival.
 // Arrive (count 1) on the barrier at `local_addr` of CTA `target` of the cluster: a plain arrive when that is this CTA.
 __device__ __forceinline__ void arrive_at(uint32_t local_addr, uint32_t target, uint32_t my_rank) {
   if (target == my_rank) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(local_addr) : "memory");
   } else {
-    mbar_arrive_cluster(map_to_cta(local_addr, target));
+    mbar_arrive_cluster_relaxed(map_to_cta(local_addr, target));
   }
 }
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
@@ -134,6 +148,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   // k-th work unit of this cluster (late queries first), or negative; unit = (query, head block) * nsplit + share
   auto item_of = [&](int k) { return num_items - 1 - cluster_id - k * num_clusters; };
+#ifdef DSA_TRACE
+  auto tr = [&](int ev, int g) { if (cluster_id == 0 && g < 64 && p.trace) p.trace[(rank * 24 + ev) * 64 + g] = clock64(); };
+#else
+  auto tr = [&](int, int) {};
+#endif
   auto bar = [&](int slot) { return bars + slot; };
   auto bar_addr = [&](int slot) { return sBars + static_cast<uint32_t>(slot) * 8u; };
 
@@ -145,11 +164,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       mbar_init(bar(kBarPeerRead + i), 4); mbar_init(bar(kBarVFull + i), 1); mbar_init(bar(kBarPeerVFull + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarSFree + i), 2 * (kSoftmaxWarps + 4));
-      mbar_init(bar(kBarPReady + i), 2 * kSoftmaxWarps); mbar_init(bar(kBarPFree + i), 1);
-      mbar_init(bar(kBarInfoFull + i), 1); mbar_init(bar(kBarInfoEmpty + i), kSoftmaxWarps + 4 + 2);
+      mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarSFree + i), kSoftmaxWarps + 4); mbar_init(bar(kBarPeerSFree + i), 1);
+      mbar_init(bar(kBarPReady + i), kSoftmaxWarps); mbar_init(bar(kBarPeerPReady + i), 1); mbar_init(bar(kBarPFree + i), 1);
+      mbar_init(bar(kBarInfoFull + i), 1); mbar_init(bar(kBarInfoEmpty + i), kSoftmaxWarps + 4 + (rank == 0 ? 3 : 4));
     }
-    mbar_init(bar(kBarQReady), 8); mbar_init(bar(kBarQFree), 1); mbar_init(bar(kBarOFree), 2 * kSoftmaxWarps);
+    mbar_init(bar(kBarQReady), 8); mbar_init(bar(kBarQFree), 2); mbar_init(bar(kBarOFree), 2 * kSoftmaxWarps);
     for (int i = 0; i < 4; ++i) info[i] = 0;
     mbar_init_fence();
   }
@@ -193,12 +212,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         const int sb = g & 1;
         uint32_t sc[16];  // scores as raw bits (tensor-memory loads), used as floats below
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(kBarSFull + sb), (g >> 1) & 1, p.status));
+        if (tid == 0) tr(3, g);
         tc_fence_after();
         tmem_ld16(tS + sb * 32 + ch * 16 + lane_base, sc);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) arrive_at(bar_addr(kBarSFree + sb), 0, rank);  // the Q K^T of tile g+2 may overwrite the buffer
+        if (lane == 0) mbar_arrive(bar(kBarSFree + sb));  // the Q K^T of tile g+2 may overwrite the buffer
         const bool full = mask == 0xffffu;
         float mx;
         if (full) {
@@ -270,14 +290,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         }
         // P goes to shared memory as the K-major A operand of the P V MMAs: row m, keys 32 kh + 16 ch .. + 15 = two 16-byte
         // units.  The buffer was last read by the P V MMAs of tile g-2.
+        if (tid == 0) tr(11, g);
         if (g >= 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(kBarPFree + sb), ((g >> 1) + 1) & 1, p.status));
+        if (tid == 0) tr(12, g);
         const uint32_t prow = sBase + kOffP + sb * kPBytes;
         st_shared_v4(prow + sw128_offset(m, 4 * kh + 2 * ch), pk[0], pk[1], pk[2], pk[3]);
         st_shared_v4(prow + sw128_offset(m, 4 * kh + 2 * ch + 1), pk[4], pk[5], pk[6], pk[7]);
         fence_proxy_async_smem();  // read by the tensor cores (async proxy)
         __syncwarp();
-        if (lane == 0) arrive_at(bar_addr(kBarPReady + sb), 0, rank);
+        if (lane == 0) mbar_arrive(bar(kBarPReady + sb));
+        if (tid == 0) tr(4, g);
       }
+      if (tid == 0) tr(18, k);
       // ---- epilogue: each thread normalises and stores 128 of its head's 512 output dims ----
       if (nvt > 0) {  // row sum = sum over the four threads of the head
         rowsum[part * 64 + m] = l;
@@ -291,6 +315,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       const int64_t prow_index = (static_cast<int64_t>(share) * p.B * p.S + bt) * p.H + h;
       float* part_row = nsplit > 1 ? p.part_out + prow_index * kDV + dim0 : nullptr;
       const bool lse_writer = kh == 0 && ch == 0;
+      // scratch of this warp for the output transposition: inside the P rows of its own block of 32 heads (both P buffers), so
+      // that only warps of the same block -- which meet at a named barrier when they are done -- can write P over it
+      const uint32_t out_scratch = sBase + kOffP + (part < 2 ? 0u : kPBytes) + (q4 & 1) * 4096u + (part & 1) * 2048u;
       if (nsplit > 1 && nvt == 0) {
         if (h < p.H) {  // nothing to add from this share (also for queries that do not exist: the combine step writes zeros)
           for (int j = 0; j < 32; ++j) reinterpret_cast<float4*>(part_row)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -317,16 +344,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
               reinterpret_cast<float4*>(part_row + cc * 32)[gq] =
                   make_float4(__uint_as_float(v[4 * gq]) * inv_l, __uint_as_float(v[4 * gq + 1]) * inv_l, __uint_as_float(v[4 * gq + 2]) * inv_l,
                               __uint_as_float(v[4 * gq + 3]) * inv_l);
-          } else if (ok && h < p.H) {
+          } else if (nsplit <= 1) {
+            // A row per lane would make every store instruction touch 32 lines.  The warp's 32 rows x 64 bytes go through its
+            // scratch (a quarter of the P buffers, which are idle: the item's last P V is complete) and leave as 64 contiguous
+            // bytes of each of 8 rows per instruction.
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
-              uint4 w;
-              w.x = pack2<kBF16>(__uint_as_float(v[8 * gq + 0]) * inv_l, __uint_as_float(v[8 * gq + 1]) * inv_l);
-              w.y = pack2<kBF16>(__uint_as_float(v[8 * gq + 2]) * inv_l, __uint_as_float(v[8 * gq + 3]) * inv_l);
-              w.z = pack2<kBF16>(__uint_as_float(v[8 * gq + 4]) * inv_l, __uint_as_float(v[8 * gq + 5]) * inv_l);
-              w.w = pack2<kBF16>(__uint_as_float(v[8 * gq + 6]) * inv_l, __uint_as_float(v[8 * gq + 7]) * inv_l);
-              reinterpret_cast<uint4*>(orow + cc * 32)[gq] = w;
+              const uint32_t w0 = pack2<kBF16>(__uint_as_float(v[8 * gq + 0]) * inv_l, __uint_as_float(v[8 * gq + 1]) * inv_l);
+              const uint32_t w1 = pack2<kBF16>(__uint_as_float(v[8 * gq + 2]) * inv_l, __uint_as_float(v[8 * gq + 3]) * inv_l);
+              const uint32_t w2 = pack2<kBF16>(__uint_as_float(v[8 * gq + 4]) * inv_l, __uint_as_float(v[8 * gq + 5]) * inv_l);
+              const uint32_t w3 = pack2<kBF16>(__uint_as_float(v[8 * gq + 6]) * inv_l, __uint_as_float(v[8 * gq + 7]) * inv_l);
+              st_shared_v4(out_scratch + lane * 64 + ((gq ^ ((lane >> 1) & 3)) << 4), w0, w1, w2, w3);
             }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = 8 * i + (lane >> 2), u = lane & 3;
+              const uint4 x = ld_shared_v4(out_scratch + r * 64 + ((u ^ ((r >> 1) & 3)) << 4));
+              const int hr = h - lane + r;   // head of row r of this warp (the warp's rows are consecutive heads)
+              if (ok && hr < p.H) *reinterpret_cast<uint4*>(orow + static_cast<int64_t>(r - lane) * kDV + cc * 32 + u * 8) = x;
+            }
+            __syncwarp();
           }
         }
         if (ok && lse_writer && h < p.H) {
@@ -335,6 +373,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           else if (p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = lse_v;
         }
       }
+      if (tid == 0) tr(19, k);
+      if (nvt > 0 && nsplit <= 1) named_bar_sync(named, 128);  // the block's warps are done with their scratch: P may be written again
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -403,6 +443,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (lane == 0) { info[qp * 2] = n; info[qp * 2 + 1] = ctx.active ? 1 : 0; }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarInfoFull + qp));
+        if (lane == 0) tr(20, k);
       }
       named_bar_sync(kGatherBarrier, 128);
       const int nvt = info[qp * 2];
@@ -430,6 +471,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           for (int c = 0; c < kChunks; ++c) cp_async16(dst + c * kChunk, src + c * 128, nbytes);
         }
         cp_async_arrive_noinc(bar(kBarKvFull + s));
+        if (pw == 0 && lane == 0) tr(0, g);
       }
     }
     cp_async_wait<0>();
@@ -445,61 +487,115 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     const uint32_t dst_off = 4u * rank * kChunk;   // ... go where the peer keeps those dims of ITS keys that I need: its chunks [4 r, +4)
     const uint32_t peer_base = map_to_cta(sBase, peer);
     const uint32_t peer_bars = map_to_cta(sBars, peer);
-    // pulls this thread's Q row of an item towards L2
-    auto prefetch_q = [&](int it_unit) {
-      if (it_unit < 0) return;
-      const int it_item = it_unit / nsplit;
-      const int nbt = it_item / head_blocks, nh = (it_item - nbt * head_blocks) * kM + static_cast<int>(rank) * kHeads + m;
-      if (nh >= p.H) return;
-      const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh) * kRowBytes;
-      // the two threads of a row take alternate 128-byte lines
-      for (int j = (L >> 6); j < kRowBytes / 128; j += 2) prefetch_l2(nq + j * 128);
+    // First Q row (head 64 r of the unit's head block) of work unit `u` and the number of this CTA's 64 rows that exist
+    // (nullptr / 0 when the unit does not exist).  The 64 rows are contiguous in q: 64 x kRowBytes bytes.
+    auto q_rows_of = [&](int u, int* nrows) -> const uint8_t* {
+      *nrows = 0;
+      if (u < 0) return nullptr;
+      const int it_item = u / nsplit;
+      const int nbt = it_item / head_blocks, nh0 = (it_item - nbt * head_blocks) * kM + static_cast<int>(rank) * kHeads;
+      if (nh0 >= p.H) return nullptr;
+      *nrows = p.H - nh0 < kHeads ? p.H - nh0 : kHeads;
+      return reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh0) * kRowBytes;
     };
-    if (run_all) prefetch_q(item_of(0));
+    // Brings the tensor-memory part of a unit's Q rows (dims 0..383 = six 128-byte lines per row) into L2 ahead of time.
+    auto warm_q = [&](int u) {
+      int nrows;
+      const uint8_t* q0 = q_rows_of(u, &nrows);
+      for (int e = xt; e < nrows * 6; e += 128) prefetch_l2(q0 + (e / 6) * kRowBytes + (e % 6) * 128);
+    };
+    // Shared-memory part of a unit's Q (dims 384..) into Q buffer `buf`.  One instruction copies one 64-dim chunk (128 bytes,
+    // 8 lanes) of four rows: whole lines, unlike a row per lane.  One cp.async group.
+    auto load_q_smem = [&](int u, int buf) {
+      int nrows;
+      const uint8_t* q0 = q_rows_of(u, &nrows);
+#pragma unroll
+      for (int c = 0; c < kQSmemChunks; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = (xt >> 3) + 16 * i, unit16 = xt & 7;
+          const bool v = row < nrows;
+          cp_async16(sQ + buf * kQBytes + c * kQChunk + sw128_offset(row, unit16),
+                     v ? q0 + row * kRowBytes + (6 + c) * 128 + unit16 * 16 : reinterpret_cast<const uint8_t*>(p.q), v ? 16u : 0u);
+        }
+      cp_async_commit();
+    };
+    if (run_all) warm_q(item_of(0));
     int g = 0, ne = 0;
+    int q_smem_loaded_for = -1;  // item whose shared-memory part of Q was already requested (into buffer item & 1)
     for (int k = 0; run_all && ok; ++k) {
       const int unit = item_of(k);
       if (unit < 0) break;
-      const int item = unit / nsplit;
       const int qp = k & 1;
-      const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM + static_cast<int>(rank) * kHeads;
       if (!__all_sync(0xffffffffu, mbar_wait<true>(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status))) { ok = false; break; }
       const int nvt = info[qp * 2];
       if (nvt > 0) {
-        // all Q K^T MMAs of the previous non-empty item are complete: Q can be replaced
+        // all Q K^T MMAs of the previous non-empty item are complete: the tensor-memory part of Q can be replaced
         if (ne > 0 && !__all_sync(0xffffffffu, mbar_wait<true>(bar(kBarQFree), (ne - 1) & 1, p.status))) { ok = false; break; }
         ++ne;
-        const bool row_ok = h0 + m < p.H;
-        const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0 + (row_ok ? m : 0)) * kRowBytes;
-        // shared-memory part: chunk c (64 dims) of row m = eight 16-byte units; the two threads of a row split them
-#pragma unroll
-        for (int c = 0; c < kQSmemChunks; ++c)
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int unit16 = 4 * (L >> 6) + u;
-            cp_async16(sQ + c * kQChunk + sw128_offset(m, unit16), qrow + (6 + c) * 128 + unit16 * 16, row_ok ? 16u : 0u);
-          }
-        cp_async_commit();
+        if (q_smem_loaded_for != k) load_q_smem(unit, k & 1);  // not requested ahead (first item, or the item before was empty)
+        if (xt == 0) tr(16, k);
+        int nrows;
+        const uint8_t* q0 = q_rows_of(unit, &nrows);
         tc_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < kQTmemDims / 64; ++cc) {   // 64 dims = 32 columns at a time
-          uint32_t w[32];
+        // Tensor-memory part: this warp's 32 lanes hold rows mb .. mb + 31.  A row per lane would make every load instruction
+        // touch 32 lines; instead one instruction reads 64 contiguous bytes of each of 8 rows (lane l: row 8 i + l / 4, unit
+        // l % 4 of the half chunk), the 32 x 64-byte block is turned through the warp's scratch (XOR swizzle: conflict-free
+        // both ways) and each lane picks up its own row.  The loads of the next half chunk are in flight meanwhile.
+        const int mb = (xw & 1) * 32;
+        const uint32_t scratch = sBase + kOffXScratch + xw * 2048;
+        auto load_half = [&](int hc, uint4 (&v)[4]) {   // half chunk hc (0..11): dims 32 hc .. 32 hc + 31
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row_ok) v = __ldg(reinterpret_cast<const uint4*>(qrow + (cc * 8 + j) * 16));
-            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+          for (int i = 0; i < 4; ++i) {
+            const int row = mb + 8 * i + (lane >> 2);
+            v[i] = make_uint4(0, 0, 0, 0);
+#ifndef DSA_Q_NO_LOAD
+            if (row < nrows) v[i] = __ldg(reinterpret_cast<const uint4*>(q0 + row * kRowBytes + hc * 64 + (lane & 3) * 16));
+#endif
           }
-          tmem_st32(tQ + lane_base + cc * 32, w);
+        };
+        // four half chunks (16 loads per thread) are requested at once: three round trips per item instead of twelve
+#pragma unroll 1
+        for (int h0 = 0; h0 < kQTmemDims / 32; h0 += 4) {
+          uint4 v[4][4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) load_half(h0 + j, v[j]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = 8 * i + (lane >> 2);
+              st_shared_v4(scratch + r * 64 + (((lane & 3) ^ ((r >> 1) & 3)) << 4), v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w);
+            }
+            __syncwarp();
+            uint32_t w[16];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint4 x = ld_shared_v4(scratch + lane * 64 + ((u ^ ((lane >> 1) & 3)) << 4));
+              w[4 * u] = x.x; w[4 * u + 1] = x.y; w[4 * u + 2] = x.z; w[4 * u + 3] = x.w;
+            }
+            __syncwarp();
+            tmem_st16(tQ + lane_base + (h0 + j) * 16, w);
+          }
         }
         cp_async_wait<0>();
+        if (xt == 0) tr(22, k);
         fence_proxy_async_smem();
         tmem_wait_st();
+        if (xt == 0) tr(23, k);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) arrive_at(bar_addr(kBarQReady), 0, rank);
+        if (xt == 0) tr(17, k);
+        // the next unit's Q while this item is being worked on: its shared-memory part goes to the other buffer (free: the
+        // Q K^T of every earlier item is complete), the lines of its tensor-memory part are pulled into L2
+        const int next = item_of(k + 1);
+        if (next >= 0) {
+          load_q_smem(next, (k + 1) & 1);
+          q_smem_loaded_for = k + 1;
+          warm_q(next);
+        }
       }
-      prefetch_q(item_of(k + 1));  // the next item's rows, while this item is being worked on
       for (int it = 0; it < nvt; ++it, ++g) {
         const int sb = g & 1, s = g % kStages;
         const uint32_t ph = (g / kStages) & 1;
@@ -507,7 +603,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (!__all_sync(0xffffffffu, mbar_wait<true>(bar(kBarSFull + sb), (g >> 1) & 1, p.status))) { ok = false; break; }
         // these warps do not read the scores, but the buffer's "full" barrier must not complete another phase (tile g + 2)
         // before every waiter has seen this one: they are counted among the readers that free the buffer
-        if (lane == 0) arrive_at(bar_addr(kBarSFree + sb), 0, rank);
+        if (lane == 0) mbar_arrive(bar(kBarSFree + sb));
+        if (xt == 0) tr(5, g);
         const uint32_t region = sBase + s * kStageBytes + src_off;
         uint4 v[8];
 #pragma unroll
@@ -520,24 +617,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           for (int j = 0; j < 8; ++j) dep ^= v[j].x;
           st_shared_u32_volatile(sBase + kOffInfo + 64 + (warp - kFirstExchangeWarp) * 4, dep);
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(peer_bars + (kBarPeerRead + s) * 8);
+          if (lane == 0) mbar_arrive_cluster_relaxed(peer_bars + (kBarPeerRead + s) * 8);
         }
         // this CTA's receive barrier: armed once per tile (its previous use, three tiles ago, completed before that tile's P V)
         if (xt == 0) mbar_arrive_expect_tx(bar(kBarVFull + s), kSwapBytes);
         // the peer holds its region in registers: it may be overwritten
         if (!__all_sync(0xffffffffu, mbar_wait_cluster(bar(kBarPeerRead + s), ph, p.status))) { ok = false; break; }
+        if (xt == 0) tr(6, g);
         const uint32_t dst = peer_base + s * kStageBytes + dst_off, dst_bar = peer_bars + (kBarVFull + s) * 8;
 #pragma unroll
         for (int j = 0; j < 8; ++j) st_async_v4_b32(dst + (xt + 128 * j) * 16, dst_bar, v[j]);
+        if (xt == 0) tr(7, g);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarInfoEmpty + qp));
     }
-  } else if (warp == kQkWarp) {
+  } else if (warp == kQkWarp || warp == kQkWarpB) {
+    const int par = warp == kQkWarp ? 0 : 1;
     if (lane == 0 && rank == 0) {
-      // ================================ Q K^T issuer (even CTA) =====================================
+      // ================================ Q K^T issuers (even CTA) ====================================
       // S[128 heads x 64 keys] over 36 (32 without rope dims) steps of 16 dims: A = Q (tensor memory for dims < 384, shared
-      // memory beyond), B = the 32 gathered rows of each CTA.  Runs ahead of the P V issuer as far as the two score buffers allow.
+      // memory beyond), B = the 32 gathered rows of each CTA.  One thread issues an MMA about every 45 clocks whatever its
+      // size, and one of these takes 16: two threads, one for the even tiles (score buffer 0) and one for the odd tiles
+      // (buffer 1), keep the tensor cores fed.
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
       int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
@@ -546,19 +648,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         const int qp = k & 1;
         if (!mbar_wait(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
+        const int first = (g & 1) == par ? 0 : 1;            // this thread's first tile of the item
+        const int last = nvt - 1 - (((g + nvt - 1) & 1) == par ? 0 : 1);   // ... and its last one
         if (nvt > 0) {  // items without a key neither load Q nor touch O: their barriers are skipped on both sides
-          if (!mbar_wait_cluster(bar(kBarQReady), ne & 1, p.status)) { ok = false; break; }
+          if (first < nvt && !mbar_wait_cluster(bar(kBarQReady), ne & 1, p.status)) { ok = false; break; }
           ++ne;
+          if (first >= nvt) {  // no tile of this item is mine: I am done with its Q at once (both CTAs are told)
+            mbar_arrive(bar(kBarQFree));
+            mbar_arrive_cluster_relaxed(map_to_cta(bar_addr(kBarQFree), 1));
+          }
         }
-        for (int it = 0; ok && it < nvt; ++it, ++g) {
-          const int s = g % kStages, sb = g & 1;
+        for (int it = first; ok && it < nvt; it += 2) {
+          const int gg = g + it;
+          const int s = gg % kStages, sb = par;
           const uint32_t stage = sBase + s * kStageBytes;
-          if (!mbar_wait(bar(kBarKvFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
-          if (!mbar_wait_cluster(bar(kBarPeerKvFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
-          // the softmax warps of both CTAs must have read the scores of tile g-2 out of this buffer
-          if (g >= 2 && !mbar_wait_cluster(bar(kBarSFree + sb), ((g >> 1) + 1) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait(bar(kBarKvFull + s), (gg / kStages) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar(kBarPeerKvFull + s), (gg / kStages) & 1, p.status)) { ok = false; break; }
+          // the softmax warps of both CTAs must have read the scores of tile gg-2 out of this buffer
+          if (gg >= 2 && !mbar_wait(bar(kBarSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
+          if (gg >= 2 && !mbar_wait_cluster(bar(kBarPeerSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
           fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
           tc_fence_after();
+          tr(1, gg);
           const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int c = 0; c < 6; ++c) {
@@ -566,7 +677,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
             for (int kq = 0; kq < 4; ++kq)
               umma_pair_ts(tS + sb * 32, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunk + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
           }
-          const uint64_t da0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
+          const uint64_t da0 = make_smem_desc(sQ + (k & 1) * kQBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int c = 0; c < kQSmemChunks; ++c) {
 #pragma unroll
@@ -574,13 +685,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
               umma_pair_ss(tS + sb * 32, da0 + ((c * kQChunk + kq * 32) >> 4), db0 + (((6 + c) * kChunk + kq * 32) >> 4), idesc_qk, 1);
           }
           umma_pair_commit(bar(kBarSFull + sb), 3);
-          if (it == nvt - 1) umma_pair_commit(bar(kBarQFree), 3);  // the item's Q may be replaced
+          tr(2, gg);
+          if (it == last) umma_pair_commit(bar(kBarQFree), 3);  // this thread's share of "the item's Q may be replaced"
         }
         if (!ok) break;
+        g += nvt;
         mbar_arrive(bar(kBarInfoEmpty + qp));
       }
-    } else if (lane == 0) {
-      // ---- odd CTA: tell the even CTA when this CTA's rows of a tile have landed ----
+    } else if (lane == 0 && rank == 1) {
+      // ---- odd CTA: tell the even CTA when this CTA's rows of a tile have landed (warp 16) / when this CTA's softmax and
+      // exchange warps are past a score buffer (warp 18) ----
       const uint32_t target = map_to_cta(sBars, 0);
       int g = 0;
       for (int k = 0; run_all && ok; ++k) {
@@ -590,17 +704,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (!mbar_wait<true>(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
         for (int it = 0; ok && it < nvt; ++it, ++g) {
-          const int s = g % kStages;
-          if (!mbar_wait(bar(kBarKvFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
-          fence_proxy_async_smem();  // written by cp.async, read by the tensor cores
-          mbar_arrive_cluster(target + (kBarPeerKvFull + s) * 8);
+          if (par == 0) {
+            const int s = g % kStages;
+            if (!mbar_wait(bar(kBarKvFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+            fence_proxy_async_smem();  // written by cp.async, read by the tensor cores
+            mbar_arrive_cluster_relaxed(target + (kBarPeerKvFull + s) * 8);
+            tr(1, g);
+          } else {
+            const int sb = g & 1;
+            if (!mbar_wait(bar(kBarSFree + sb), (g >> 1) & 1, p.status)) { ok = false; break; }
+            mbar_arrive_cluster_relaxed(target + (kBarPeerSFree + sb) * 8);
+          }
         }
         if (!ok) break;
         mbar_arrive(bar(kBarInfoEmpty + qp));
       }
     }
-  } else if (warp == kPvWarp) {
-    if (lane == 0 && rank == 0) {
+  } else if (warp == kPvWarp || warp == kRelayWarp) {
+    if (lane == 0 && rank == 0 && warp == kPvWarp) {
       // ================================ P V issuer (even CTA) =======================================
       // O[128 heads x 512 dims] += P[128 x 64] . V[64 x 512] as two MMAs of N = 256 per 16 keys: P K-major in shared memory,
       // V MN-major: keys of half kh, dims of the CTA's half j at stage + (4 kh + 2 j) chunks (own rows or swapped-in rows).
@@ -614,9 +735,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         const int nvt = info[qp * 2];
         for (int it = 0; ok && it < nvt; ++it, ++g) {
           const int s = g % kStages, pb = g & 1;
-          if (!mbar_wait_cluster(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar(kBarPeerPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
+          tr(13, g);
           if (!mbar_wait_cluster(bar(kBarVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+          tr(8, g);
           if (!mbar_wait_cluster(bar(kBarPeerVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+          tr(9, g);
           // the first P V of an item overwrites O: the previous non-empty item's output must have been read out
           if (it == 0 && ne > 0 && !mbar_wait_cluster(bar(kBarOFree), (ne - 1) & 1, p.status)) { ok = false; break; }
           fence_proxy_async_smem();
@@ -633,13 +758,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           }
           umma_pair_commit(bar(kBarKvEmpty + s), 3);
           umma_pair_commit(bar(kBarPFree + pb), 3);
+          tr(10, g);
         }
         if (!ok) break;
         if (nvt > 0) ++ne;
         mbar_arrive(bar(kBarInfoEmpty + qp));
       }
-    } else if (lane == 0) {
-      // ---- odd CTA: tell the even CTA when the even CTA's half of the swap has landed here ----
+    } else if (lane == 0 && rank == 1) {
+      // ---- odd CTA: tell the even CTA when the even CTA's half of the swap has landed here (warp 17) / when this CTA's
+      // softmax warps have written P (warp 19) ----
+      const bool fwd_v = warp == kPvWarp;
       const uint32_t target = map_to_cta(sBars, 0);
       int g = 0;
       for (int k = 0; run_all && ok; ++k) {
@@ -649,10 +777,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (!mbar_wait<true>(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
         for (int it = 0; ok && it < nvt; ++it, ++g) {
-          const int s = g % kStages;
-          if (!mbar_wait_cluster(bar(kBarVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
-          fence_proxy_async_smem();  // written by st.async (generic proxy), read by the tensor cores
-          mbar_arrive_cluster(target + (kBarPeerVFull + s) * 8);
+          if (fwd_v) {
+            const int s = g % kStages;
+            if (!mbar_wait_cluster(bar(kBarVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+            fence_proxy_async_smem();  // written by st.async (generic proxy), read by the tensor cores
+            mbar_arrive_cluster_relaxed(target + (kBarPeerVFull + s) * 8);
+            tr(8, g);
+          } else {
+            const int pb = g & 1;
+            if (!mbar_wait(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
+            tr(14, g);
+            fence_proxy_async_smem();  // (the writers fenced their own stores; this orders the hand-over)
+            mbar_arrive_cluster_relaxed(target + (kBarPeerPReady + pb) * 8);
+            tr(15, g);
+          }
         }
         if (!ok) break;
         mbar_arrive(bar(kBarInfoEmpty + qp));
@@ -676,12 +814,14 @@ bool sparse_mla_fwd_pair_supported(const FwdParams& p) {
          static_cast<long long>(p.B) * p.S_kv <= 0x7fffffffLL;
 }
 
-int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, int sms, cudaStream_t stream) {
+int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  cudaError_t e = current_device_sms(&dev, &sms);
+  if (e != cudaSuccess) return static_cast<int>(e);
   const bool rope = p.D == pr::kD;
   auto kern = rope ? (bf16 ? sparse_mla_fwd_pair_kernel<true, true> : sparse_mla_fwd_pair_kernel<false, true>)
                    : (bf16 ? sparse_mla_fwd_pair_kernel<true, false> : sparse_mla_fwd_pair_kernel<false, false>);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pr::kSmemBytes));
-  if (e != cudaSuccess) return static_cast<int>(e);
+  if ((e = ensure_dynamic_smem(kern, dev, static_cast<int>(pr::kSmemBytes))) != cudaSuccess) return static_cast<int>(e);
   // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
   const long long items = static_cast<long long>(p.B) * p.S * ((p.H + pr::kM - 1) / pr::kM);
   long long clusters = sms / 2 > 0 ? sms / 2 : 1;

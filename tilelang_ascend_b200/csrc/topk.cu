@@ -17,6 +17,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch_util.h"
+
 namespace dsa {
 
 namespace topk {
@@ -335,8 +337,10 @@ int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_str
   if (top_k > topk::kWarps * 32 * 16) return static_cast<int>(cudaErrorInvalidValue);
   const bool small = top_k <= topk::kWarps * 32 * 4;
   auto kern = small ? topk_select_kernel<4> : topk_select_kernel<16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  int dev = 0, sms = 0;
+  cudaError_t e = current_device_sms(&dev, &sms);
   if (e != cudaSuccess) return static_cast<int>(e);
+  if ((e = ensure_dynamic_smem(kern, dev, static_cast<int>(smem))) != cudaSuccess) return static_cast<int>(e);
   kern<<<static_cast<unsigned>(rows), topk::kThreads, smem, stream>>>(scores, row_stride, n, limits, top_k, kp, out_idx, out_val, ordered);
   return static_cast<int>(cudaGetLastError());
 }

@@ -30,6 +30,21 @@ def _check_distinct_indices(indices: torch.Tensor, S_kv: int) -> None:
         raise ValueError(f"indices of query row {row} name a key more than once; the kernels would count it once per occurrence")
 
 
+# fp32 scratch of split-KV calls, kept per (device, stream) and grown on demand: a decode step runs every few tens of
+# microseconds and an allocation per call costs about as much as the kernel's host side.  Calls on one stream are ordered,
+# so they can share a buffer; calls on different streams get different buffers.
+_SPLIT_WORKSPACES = {}
+
+
+def _split_workspace(dev, nbytes: int) -> torch.Tensor:
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    buf = _SPLIT_WORKSPACES.get(key)
+    if buf is None or buf.numel() * 4 < nbytes:
+        buf = torch.empty(((nbytes + 3) // 4,), dtype=torch.float32, device=dev)
+        _SPLIT_WORKSPACES[key] = buf
+    return buf
+
+
 def _next_pow2(x: int) -> int:
     return 1 << (max(int(x), 1) - 1).bit_length()
 
@@ -42,8 +57,8 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
 
     nsplit: None = let the library decide whether the keys of every query are split over several work units (it does for
     D=576 / dv=512 calls with fewer queries than SM pairs, e.g. decode of a few sequences); 1 = never; n > 1 = n shares.
-    The fp32 workspace of a split call is allocated here, as the reference's adapter allocates its kernels' workspaces
-    (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137)."""
+    The fp32 workspace of a split call is owned here (one per device and stream, reused between calls), as the reference's
+    adapter owns its kernels' workspaces (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137)."""
     opt = [t for t in (q_start_b, kv_len_b, q_len_b, block_table) if t is not None]
     dev = check_inputs([q, kv, indices] + opt, [None, q.dtype, torch.int32] + [torch.int32] * len(opt),
                        ["q", "kv", "indices"] + ["int32 side input"] * len(opt))
@@ -77,7 +92,7 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
             if not tc_shape:
                 raise ValueError("nsplit > 1 needs D = 576, dv = 512, topk <= 8192 and the tensor-core kernel")
             nbytes = int(lib.dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, dv, nsplit))
-            workspace = torch.empty((nbytes // 4,), dtype=torch.float32, device=dev)
+            workspace = _split_workspace(dev, nbytes)
             _lib.check(lib.dsa_sparse_mla_fwd_splitkv(
                 ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
                 1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
