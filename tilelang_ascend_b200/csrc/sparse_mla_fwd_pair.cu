@@ -54,8 +54,7 @@ constexpr uint32_t kOffRowSum = kOffRowMax + 2 * 4 * 64 * 4;   // [4][64] floats
 constexpr uint32_t kOffMask = kOffRowSum + 4 * 64 * 4;         // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;    // [2][kMaxTiles] 16-bit tile ids
 constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;    // [2] {tile count, run flag}; scratch words of the warps behind it
-constexpr uint32_t kOffXScratch = kOffInfo + 256;              // [4 exchange warps][32 rows x 64 bytes]: transposition of Q rows
-constexpr uint32_t kSmemBytes = kOffXScratch + 4 * 2048 + 1024;  // + slack to align the base to 1024 B
+constexpr uint32_t kSmemBytes = kOffInfo + 256 + 1024;         // + slack to align the base to 1024 B
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 constexpr int kSoftmaxWarps = 8;                       // warp w: lanes 32 (w & 3) .. +31, score columns 16 (w >> 2) .. +15
 constexpr int kFirstGatherWarp = 8;
@@ -89,7 +88,8 @@ constexpr int kBarQFree = 37;        // count 2: both Q K^T issuers are done wit
 constexpr int kBarOFree = 38;        // count 16, even CTA: the softmax warps drained the previous item's output
 constexpr int kBarInfoFull = 39;     // [2] count 1: tile list of an item published by the gather warps
 constexpr int kBarInfoEmpty = 41;    // [2] count 16 (15 in the even CTA): softmax, exchange, issuer / forwarding warps are done with the list
-constexpr int kBarCount = 43;
+constexpr int kBarQRead = 43;        // count 4: the exchange warps have moved a Q slot of the ring to tensor memory
+constexpr int kBarCount = 44;
 }  // namespace pr
 
 // Remote arrives in this kernel are RELAXED: an arrive with release semantics at cluster scope costs its thread about 1100
@@ -156,6 +156,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   auto bar = [&](int slot) { return bars + slot; };
   auto bar_addr = [&](int slot) { return sBars + static_cast<uint32_t>(slot) * 8u; };
 
+  // First Q row (head 64 r of the unit's head block) of work unit `u` and the number of this CTA's 64 rows that exist
+  // (nullptr / 0 when the unit does not exist).  The 64 rows are contiguous in q: 64 x kRowBytes bytes.
+  auto q_rows_of = [&](int u, int* nrows) -> const uint8_t* {
+    *nrows = 0;
+    if (u < 0) return nullptr;
+    const int it_item = u / nsplit;
+    const int nbt = it_item / head_blocks, nh0 = (it_item - nbt * head_blocks) * kM + static_cast<int>(rank) * kHeads;
+    if (nh0 >= p.H) return nullptr;
+    *nrows = p.H - nh0 < kHeads ? p.H - nh0 : kHeads;
+    return reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh0) * kRowBytes;
+  };
+
   // ---- setup ------------------------------------------------------------------------------------------
   if (tid == 0) {
     *start_status = *reinterpret_cast<volatile int*>(p.status);
@@ -169,6 +181,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       mbar_init(bar(kBarInfoFull + i), 1); mbar_init(bar(kBarInfoEmpty + i), kSoftmaxWarps + 4 + (rank == 0 ? 3 : 4));
     }
     mbar_init(bar(kBarQReady), 8); mbar_init(bar(kBarQFree), 2); mbar_init(bar(kBarOFree), 2 * kSoftmaxWarps);
+    mbar_init(bar(kBarQRead), 4);
     for (int i = 0; i < 4; ++i) info[i] = 0;
     mbar_init_fence();
   }
@@ -388,7 +401,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     // list (it decides how many tiles every role of the pair walks); each gathers its own 32 keys of a tile.
     const int pw = warp - kFirstGatherWarp;  // keys [8 pw, 8 pw + 8) of the CTA's 32
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
-    int g = 0;
+    int g = 0, qslots = 0;  // tiles so far; ring slots so far that carried Q rows instead of a tile (two per non-empty item)
     for (int k = 0; run_all; ++k) {
       const int unit = item_of(k);
       if (unit < 0) break;
@@ -447,8 +460,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       }
       named_bar_sync(kGatherBarrier, 128);
       const int nvt = info[qp * 2];
+      if (nvt > 0) {
+        // The item's Q rows for tensor memory (dims 0..383) travel through the stage ring as two slots AHEAD of the item's
+        // tiles -- requested as soon as stages come free, i.e. while the previous item is still being worked on -- so that at
+        // the item boundary the exchange warps only move them from shared memory to tensor memory.  Slot j: dims 192 j ..
+        // 192 j + 191 as three chunks of [64 rows x 128 bytes] (128-byte swizzle); one instruction copies 128 bytes of four rows.
+        int nrows;
+        const uint8_t* q0 = q_rows_of(unit, &nrows);
+        const int gt = tid - kFirstGatherWarp * 32;
+#pragma unroll 1
+        for (int j = 0; j < 2; ++j) {
+          const int u = g + qslots + j, s = u % kStages;
+          if (u >= kStages && ok) ok = mbar_wait<true>(bar(kBarKvEmpty + s), ((u / kStages) + 1) & 1, p.status);
+          if (ok) {
+            const uint32_t stage = sBase + s * kStageBytes;
+#pragma unroll
+            for (int cj = 0; cj < 3; ++cj)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int row = (gt >> 3) + 16 * i, unit16 = gt & 7;
+                const bool v = row < nrows;
+                cp_async16(stage + cj * kQChunk + sw128_offset(row, unit16),
+                           v ? q0 + row * kRowBytes + (3 * j + cj) * 128 + unit16 * 16 : reinterpret_cast<const uint8_t*>(p.q), v ? 16u : 0u);
+              }
+            cp_async_arrive_noinc(bar(kBarKvFull + s));
+          }
+        }
+        qslots += 2;
+      }
       for (int it = 0; it < nvt; ++it, ++g) {
-        const int tile = tile_list[qp * kMaxTiles + it], s = g % kStages;
+        const int tile = tile_list[qp * kMaxTiles + it], s = (g + qslots) % kStages;
         // the row numbers are fetched before the wait for the stage, so their latency is hidden behind it: lane l looks up
         // key 8 pw + (l & 7) of this CTA's 32 keys
         const int slot = tile * kBK + static_cast<int>(rank) * kKeys + pw * 8 + (lane & 7);
@@ -456,7 +497,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         // row number inside kv, -1 for a key that does not take part: it is fetched with a source size of zero, which fills
         // the destination with zeros
         const int my_row = index_valid(ctx, my_idx) ? static_cast<int>(kv_row(p, ctx.b, my_idx)) : -1;
-        if (g >= kStages && ok) ok = mbar_wait<true>(bar(kBarKvEmpty + s), ((g / kStages) + 1) & 1, p.status);
+        if (g + qslots >= kStages && ok) ok = mbar_wait<true>(bar(kBarKvEmpty + s), (((g + qslots) / kStages) + 1) & 1, p.status);
         if (!ok) continue;
         const uint32_t stage = sBase + s * kStageBytes;
         // one instruction copies one 64-dim chunk (128 bytes, 8 lanes) of four keys
@@ -487,23 +528,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     const uint32_t dst_off = 4u * rank * kChunk;   // ... go where the peer keeps those dims of ITS keys that I need: its chunks [4 r, +4)
     const uint32_t peer_base = map_to_cta(sBase, peer);
     const uint32_t peer_bars = map_to_cta(sBars, peer);
-    // First Q row (head 64 r of the unit's head block) of work unit `u` and the number of this CTA's 64 rows that exist
-    // (nullptr / 0 when the unit does not exist).  The 64 rows are contiguous in q: 64 x kRowBytes bytes.
-    auto q_rows_of = [&](int u, int* nrows) -> const uint8_t* {
-      *nrows = 0;
-      if (u < 0) return nullptr;
-      const int it_item = u / nsplit;
-      const int nbt = it_item / head_blocks, nh0 = (it_item - nbt * head_blocks) * kM + static_cast<int>(rank) * kHeads;
-      if (nh0 >= p.H) return nullptr;
-      *nrows = p.H - nh0 < kHeads ? p.H - nh0 : kHeads;
-      return reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(nbt) * p.H + nh0) * kRowBytes;
-    };
-    // Brings the tensor-memory part of a unit's Q rows (dims 0..383 = six 128-byte lines per row) into L2 ahead of time.
-    auto warm_q = [&](int u) {
-      int nrows;
-      const uint8_t* q0 = q_rows_of(u, &nrows);
-      for (int e = xt; e < nrows * 6; e += 128) prefetch_l2(q0 + (e / 6) * kRowBytes + (e % 6) * 128);
-    };
     // Shared-memory part of a unit's Q (dims 384..) into Q buffer `buf`.  One instruction copies one 64-dim chunk (128 bytes,
     // 8 lanes) of four rows: whole lines, unlike a row per lane.  One cp.async group.
     auto load_q_smem = [&](int u, int buf) {
@@ -520,8 +544,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         }
       cp_async_commit();
     };
-    if (run_all) warm_q(item_of(0));
-    int g = 0, ne = 0;
+    int g = 0, ne = 0, qslots = 0, qslot_reads = 0;
     int q_smem_loaded_for = -1;  // item whose shared-memory part of Q was already requested (into buffer item & 1)
     for (int k = 0; run_all && ok; ++k) {
       const int unit = item_of(k);
@@ -535,49 +558,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         ++ne;
         if (q_smem_loaded_for != k) load_q_smem(unit, k & 1);  // not requested ahead (first item, or the item before was empty)
         if (xt == 0) tr(16, k);
-        int nrows;
-        const uint8_t* q0 = q_rows_of(unit, &nrows);
         tc_fence_after();
-        // Tensor-memory part: this warp's 32 lanes hold rows mb .. mb + 31.  A row per lane would make every load instruction
-        // touch 32 lines; instead one instruction reads 64 contiguous bytes of each of 8 rows (lane l: row 8 i + l / 4, unit
-        // l % 4 of the half chunk), the 32 x 64-byte block is turned through the warp's scratch (XOR swizzle: conflict-free
-        // both ways) and each lane picks up its own row.  The loads of the next half chunk are in flight meanwhile.
-        const int mb = (xw & 1) * 32;
-        const uint32_t scratch = sBase + kOffXScratch + xw * 2048;
-        auto load_half = [&](int hc, uint4 (&v)[4]) {   // half chunk hc (0..11): dims 32 hc .. 32 hc + 31
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int row = mb + 8 * i + (lane >> 2);
-            v[i] = make_uint4(0, 0, 0, 0);
-#ifndef DSA_Q_NO_LOAD
-            if (row < nrows) v[i] = __ldg(reinterpret_cast<const uint4*>(q0 + row * kRowBytes + hc * 64 + (lane & 3) * 16));
-#endif
-          }
-        };
-        // four half chunks (16 loads per thread) are requested at once: three round trips per item instead of twelve
+        // Tensor-memory part: the gather warps sent the rows through two slots of the stage ring (see there).  Lane L moves
+        // row L % 64: per 64-dim chunk eight 16-byte loads from the swizzled chunk (conflict-free) and one 32-column store.
 #pragma unroll 1
-        for (int h0 = 0; h0 < kQTmemDims / 32; h0 += 4) {
-          uint4 v[4][4];
+        for (int j = 0; j < 2; ++j) {
+          const int u = g + qslots + j, s = u % kStages;
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(kBarKvFull + s), (u / kStages) & 1, p.status))) { ok = false; break; }
+          const uint32_t stage = sBase + s * kStageBytes;
+#pragma unroll 1
+          for (int cj = 0; cj < 3; ++cj) {
+            uint32_t w[32];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) load_half(h0 + j, v[j]);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int r = 8 * i + (lane >> 2);
-              st_shared_v4(scratch + r * 64 + (((lane & 3) ^ ((r >> 1) & 3)) << 4), v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w);
+            for (int uu = 0; uu < 8; ++uu) {
+              const uint4 x = ld_shared_v4(stage + cj * kQChunk + sw128_offset(m, uu));
+              w[4 * uu] = x.x; w[4 * uu + 1] = x.y; w[4 * uu + 2] = x.z; w[4 * uu + 3] = x.w;
             }
-            __syncwarp();
-            uint32_t w[16];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const uint4 x = ld_shared_v4(scratch + lane * 64 + ((u ^ ((lane >> 1) & 3)) << 4));
-              w[4 * u] = x.x; w[4 * u + 1] = x.y; w[4 * u + 2] = x.z; w[4 * u + 3] = x.w;
-            }
-            __syncwarp();
-            tmem_st16(tQ + lane_base + (h0 + j) * 16, w);
+            tmem_st32(tQ + lane_base + (3 * j + cj) * 32, w);
           }
+          // The slot carried no tile: every barrier of the stage that a tile would have completed once is completed once here,
+          // so that the phases of all of them keep in step with the slot number.
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar(kBarPeerRead + s)); mbar_arrive(bar(kBarQRead)); }
+          if (xt == 0) {
+            // all four warps have read the stage (a bounded wait, not a named barrier: a warp that gave up never comes)
+            if (!mbar_wait(bar(kBarQRead), qslot_reads & 1, p.status)) ok = false;
+            mbar_arrive(bar(kBarVFull + s));
+            if (rank == 0) { mbar_arrive(bar(kBarPeerKvFull + s)); mbar_arrive(bar(kBarPeerVFull + s)); }
+            mbar_arrive(bar(kBarKvEmpty + s));   // the stage may be refilled
+          }
+          ++qslot_reads;
         }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        qslots += 2;
         cp_async_wait<0>();
         if (xt == 0) tr(22, k);
         fence_proxy_async_smem();
@@ -593,12 +607,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (next >= 0) {
           load_q_smem(next, (k + 1) & 1);
           q_smem_loaded_for = k + 1;
-          warm_q(next);
         }
       }
       for (int it = 0; it < nvt; ++it, ++g) {
-        const int sb = g & 1, s = g % kStages;
-        const uint32_t ph = (g / kStages) & 1;
+        const int sb = g & 1, s = (g + qslots) % kStages;
+        const uint32_t ph = ((g + qslots) / kStages) & 1;
         // the Q K^T of the tile is complete on both SMs: neither CTA reads the regions any more
         if (!__all_sync(0xffffffffu, mbar_wait<true>(bar(kBarSFull + sb), (g >> 1) & 1, p.status))) { ok = false; break; }
         // these warps do not read the scores, but the buffer's "full" barrier must not complete another phase (tile g + 2)
@@ -659,11 +672,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           }
         }
         for (int it = first; ok && it < nvt; it += 2) {
-          const int gg = g + it;
-          const int s = gg % kStages, sb = par;
+          const int gg = g + it, u = gg + 2 * ne;   // ring slot: two slots per non-empty item so far carried Q rows
+          const int s = u % kStages, sb = par;
           const uint32_t stage = sBase + s * kStageBytes;
-          if (!mbar_wait(bar(kBarKvFull + s), (gg / kStages) & 1, p.status)) { ok = false; break; }
-          if (!mbar_wait_cluster(bar(kBarPeerKvFull + s), (gg / kStages) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait(bar(kBarKvFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar(kBarPeerKvFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
           // the softmax warps of both CTAs must have read the scores of tile gg-2 out of this buffer
           if (gg >= 2 && !mbar_wait(bar(kBarSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
           if (gg >= 2 && !mbar_wait_cluster(bar(kBarPeerSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
@@ -696,17 +709,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       // ---- odd CTA: tell the even CTA when this CTA's rows of a tile have landed (warp 16) / when this CTA's softmax and
       // exchange warps are past a score buffer (warp 18) ----
       const uint32_t target = map_to_cta(sBars, 0);
-      int g = 0;
+      int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
         const int item = item_of(k);
         if (item < 0) break;
         const int qp = k & 1;
         if (!mbar_wait<true>(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
+        if (nvt > 0) ++ne;
         for (int it = 0; ok && it < nvt; ++it, ++g) {
           if (par == 0) {
-            const int s = g % kStages;
-            if (!mbar_wait(bar(kBarKvFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+            const int u = g + 2 * ne, s = u % kStages;
+            if (!mbar_wait(bar(kBarKvFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
             fence_proxy_async_smem();  // written by cp.async, read by the tensor cores
             mbar_arrive_cluster_relaxed(target + (kBarPeerKvFull + s) * 8);
             tr(1, g);
@@ -734,13 +748,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         if (!mbar_wait(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
         for (int it = 0; ok && it < nvt; ++it, ++g) {
-          const int s = g % kStages, pb = g & 1;
+          const int u = g + 2 * (ne + 1);   // ring slot (ne counts the non-empty items BEFORE this one)
+          const int s = u % kStages, pb = g & 1;
           if (!mbar_wait(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
           if (!mbar_wait_cluster(bar(kBarPeerPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
           tr(13, g);
-          if (!mbar_wait_cluster(bar(kBarVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar(kBarVFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
           tr(8, g);
-          if (!mbar_wait_cluster(bar(kBarPeerVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar(kBarPeerVFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
           tr(9, g);
           // the first P V of an item overwrites O: the previous non-empty item's output must have been read out
           if (it == 0 && ne > 0 && !mbar_wait_cluster(bar(kBarOFree), (ne - 1) & 1, p.status)) { ok = false; break; }
@@ -769,17 +784,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       // softmax warps have written P (warp 19) ----
       const bool fwd_v = warp == kPvWarp;
       const uint32_t target = map_to_cta(sBars, 0);
-      int g = 0;
+      int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
         const int item = item_of(k);
         if (item < 0) break;
         const int qp = k & 1;
         if (!mbar_wait<true>(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
         const int nvt = info[qp * 2];
+        if (nvt > 0) ++ne;
         for (int it = 0; ok && it < nvt; ++it, ++g) {
           if (fwd_v) {
-            const int s = g % kStages;
-            if (!mbar_wait_cluster(bar(kBarVFull + s), (g / kStages) & 1, p.status)) { ok = false; break; }
+            const int u = g + 2 * ne, s = u % kStages;
+            if (!mbar_wait_cluster(bar(kBarVFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
             fence_proxy_async_smem();  // written by st.async (generic proxy), read by the tensor cores
             mbar_arrive_cluster_relaxed(target + (kBarPeerVFull + s) * 8);
             tr(8, g);
