@@ -60,9 +60,9 @@ constexpr int kSoftmaxWarps = 8;                       // warp w: lanes 32 (w & 
 constexpr int kFirstGatherWarp = 8;
 constexpr int kFirstExchangeWarp = 12;                 // 12..15: (w & 3) is also the lane quarter of their tensor-memory stores
 constexpr int kQkWarp = 16;                            // even CTA: Q K^T issuer of the even tiles; odd CTA: forwards kv_full
-constexpr int kPvWarp = 17;                            // even CTA: P V issuer; odd CTA: forwards v_full
+constexpr int kPvWarp = 17;                            // even CTA: first P V issuer; odd CTA: forwards v_full
 constexpr int kQkWarpB = 18;                           // even CTA: Q K^T issuer of the odd tiles; odd CTA: forwards s_free
-constexpr int kRelayWarp = 19;                         // even CTA: idle; odd CTA: forwards p_ready
+constexpr int kRelayWarp = 19;                         // even CTA: second P V issuer; odd CTA: forwards p_ready
 constexpr int kThreads = 640;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256, kColQ = 320;  // O 256 | S0 32 | S1 32 | Q 192
@@ -73,7 +73,7 @@ constexpr uint32_t kGatherBarrier = 5;                 // named barrier of the 1
 // tile -- they arrive on barriers of their own CTA and a dedicated thread passes the completed phase on.
 constexpr int kBarKvFull = 0;        // [4] count 128: cp.async completion of this CTA's gather threads
 constexpr int kBarPeerKvFull = 4;    // [4] count 1, even CTA: the odd CTA's gather of the stage landed
-constexpr int kBarKvEmpty = 8;       // [4] count 1: commit after the P V MMAs of the stage
+constexpr int kBarKvEmpty = 8;       // [4] count 2: commits of the two P V issuers after their MMAs of the stage
 constexpr int kBarSFull = 12;        // [2] count 1: commit after the Q K^T MMAs
 constexpr int kBarSFree = 14;        // [2] count 12: this CTA's softmax (and exchange) warps are past the scores
 constexpr int kBarPeerSFree = 16;    // [2] count 1, even CTA: ... the odd CTA's
@@ -82,7 +82,7 @@ constexpr int kBarVFull = 22;        // [4] count 1 + 16384 bytes: the peer's ha
 constexpr int kBarPeerVFull = 26;    // [4] count 1, even CTA: ... landed in the odd CTA
 constexpr int kBarPReady = 30;       // [2] count 8: this CTA's softmax warps wrote P
 constexpr int kBarPeerPReady = 32;   // [2] count 1, even CTA: ... the odd CTA's
-constexpr int kBarPFree = 34;        // [2] count 1: commit after the P V MMAs that read this P buffer
+constexpr int kBarPFree = 34;        // [2] count 2: commits of the two P V issuers after their MMAs that read this P buffer
 constexpr int kBarQReady = 36;       // count 8, even CTA: the exchange warps of both CTAs loaded the item's Q
 constexpr int kBarQFree = 37;        // count 2: both Q K^T issuers are done with the item's Q (commit after their last MMAs of the item)
 constexpr int kBarOFree = 38;        // count 16, even CTA: the softmax warps drained the previous item's output
@@ -172,13 +172,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   if (tid == 0) {
     *start_status = *reinterpret_cast<volatile int*>(p.status);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar(kBarKvFull + i), 128); mbar_init(bar(kBarPeerKvFull + i), 1); mbar_init(bar(kBarKvEmpty + i), 1);
+      mbar_init(bar(kBarKvFull + i), 128); mbar_init(bar(kBarPeerKvFull + i), 1); mbar_init(bar(kBarKvEmpty + i), 2);
       mbar_init(bar(kBarPeerRead + i), 4); mbar_init(bar(kBarVFull + i), 1); mbar_init(bar(kBarPeerVFull + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kBarSFull + i), 1); mbar_init(bar(kBarSFree + i), kSoftmaxWarps + 4); mbar_init(bar(kBarPeerSFree + i), 1);
-      mbar_init(bar(kBarPReady + i), kSoftmaxWarps); mbar_init(bar(kBarPeerPReady + i), 1); mbar_init(bar(kBarPFree + i), 1);
-      mbar_init(bar(kBarInfoFull + i), 1); mbar_init(bar(kBarInfoEmpty + i), kSoftmaxWarps + 4 + (rank == 0 ? 3 : 4));
+      mbar_init(bar(kBarPReady + i), kSoftmaxWarps); mbar_init(bar(kBarPeerPReady + i), 1); mbar_init(bar(kBarPFree + i), 2);
+      mbar_init(bar(kBarInfoFull + i), 1); mbar_init(bar(kBarInfoEmpty + i), kSoftmaxWarps + 4 + 4);
     }
     mbar_init(bar(kBarQReady), 8); mbar_init(bar(kBarQFree), 2); mbar_init(bar(kBarOFree), 2 * kSoftmaxWarps);
     mbar_init(bar(kBarQRead), 4);
@@ -585,7 +585,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
             if (!mbar_wait(bar(kBarQRead), qslot_reads & 1, p.status)) ok = false;
             mbar_arrive(bar(kBarVFull + s));
             if (rank == 0) { mbar_arrive(bar(kBarPeerKvFull + s)); mbar_arrive(bar(kBarPeerVFull + s)); }
-            mbar_arrive(bar(kBarKvEmpty + s));   // the stage may be refilled
+            mbar_arrive(bar(kBarKvEmpty + s));   // the stage may be refilled (both arrivals that the two P V issuers
+            mbar_arrive(bar(kBarKvEmpty + s));   // would have supplied for a tile)
           }
           ++qslot_reads;
         }
@@ -735,7 +736,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       }
     }
   } else if (warp == kPvWarp || warp == kRelayWarp) {
-    if (lane == 0 && rank == 0 && warp == kPvWarp) {
+    if (lane == 0 && rank == 0) {
+      const int j = warp == kPvWarp ? 0 : 1;   // which of the two N = 256 MMAs per 16 keys this thread issues
       // ================================ P V issuer (even CTA) =======================================
       // O[128 heads x 512 dims] += P[128 x 64] . V[64 x 512] as two MMAs of N = 256 per 16 keys: P K-major in shared memory,
       // V MN-major: keys of half kh, dims of the CTA's half j at stage + (4 kh + 2 j) chunks (own rows or swapped-in rows).
@@ -764,12 +766,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           const uint32_t stage = sBase + s * kStageBytes;
           const uint64_t dp0 = make_smem_desc(sBase + kOffP + pb * kPBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t dv = make_smem_desc(stage + (4 * (ks >> 1) + 2 * j) * kChunk + (ks & 1) * 2048, kChunk, 1024, kSwizzle128B);
-              umma_pair_ss(tO + 128 * j, dp0 + ((ks * 32) >> 4), dv, idesc_pv, (it | ks) != 0);
-            }
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t dv = make_smem_desc(stage + (4 * (ks >> 1) + 2 * j) * kChunk + (ks & 1) * 2048, kChunk, 1024, kSwizzle128B);
+            umma_pair_ss(tO + 128 * j, dp0 + ((ks * 32) >> 4), dv, idesc_pv, (it | ks) != 0);
           }
           umma_pair_commit(bar(kBarKvEmpty + s), 3);
           umma_pair_commit(bar(kBarPFree + pb), 3);
