@@ -272,6 +272,7 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     wi = (torch.randn((1, S1, 64), generator=g, device=dev) / 8).float()
     t_sc = _time_ms(lambda: dsa.indexer_scores_raw(qi, ki, wi, sparse_mode=3, fill_masked=False))
     t_all = _time_ms(lambda: dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=K, sparse_mode=3))
+    t_all_set = _time_ms(lambda: dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=K, sparse_mode=3, ordered=False))
     pairs = int((np.arange(S1, dtype=np.int64) + (S2 - S1) + 1).sum())
     sc_tflops = pairs * 64 * 256 / (t_sc * 1e-3) / 1e12
     del qi, ki, wi
@@ -297,7 +298,8 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     kvm = torch.randn((1, S_kvp, 1, WORKLOAD["D"]), generator=g, device=dev).to(torch.bfloat16)
 
     def pipeline():
-        sel, _ = dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=WORKLOAD["topk"], sparse_mode=3)
+        # the attention does not depend on the order of a query's list: the selector's final sort is left out
+        sel, _ = dsa.lightning_indexer_raw(qi, ki, wi, sparse_count=WORKLOAD["topk"], sparse_mode=3, ordered=False)
         return dsa.sparse_mla_fwd_raw(qm, kvm, sel.view(1, Sp, 1, WORKLOAD["topk"]), sm_scale=WORKLOAD["D"] ** -0.5, q_start=S_kvp - Sp,
                                       causal=True, dv=WORKLOAD["DV"])
     t_pipe = _time_ms(pipeline)
@@ -314,10 +316,10 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
                                   "frac": pipe_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
                                   "algorithmic_flop": pipe_flop,
                                   "counts": "indexer 2*128*64 FLOP per candidate pair + forward 2176 FLOP per (selected pair, head); nothing for the selector"},
-                     "workload": f"indexer (64 x 128) -> top-2048 -> sparse MLA forward on the selected indices, S_q={Sp}, S_kv={S_kvp}, one stream"},
+                     "workload": f"indexer (64 x 128) -> top-2048 (index sets, ascending) -> sparse MLA forward on the selected indices, S_q={Sp}, S_kv={S_kvp}, one stream"},
         "indexer_scores": {"ms": t_sc, "tflops": sc_tflops, "frac_of_bf16_peak": sc_tflops / peaks["bf16_tflops"],
                            "workload": f"S_q={S1} S_kv=8192 64 heads x 128, causal"},
-        "indexer_plus_topk": {"ms": t_all, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
+        "indexer_plus_topk": {"ms": t_all, "ms_index_sets_only": t_all_set, "tokens_per_s": S1 / (t_all * 1e-3), "top_k": K},
         "decode": {"us": t_dec * 1e3, "us_one_unit_per_query": t_dec_one * 1e3, "tokens_per_s": B / (t_dec * 1e-3), "algorithmic_gb_per_s": dec_gbs,
                    "frac_of_hbm_peak": dec_gbs / peaks["hbm_gbs"], "algorithmic_bytes": decode_bytes(B),
                    "workload": f"B={B} x 1 token, S_kv=32768, H=128, topk=2048 (KV cache {B * 32768 * 1152 / 1e9:.1f} GB, larger than L2)"},
@@ -544,6 +546,7 @@ def main() -> None:
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
                          "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
     ap.add_argument("--cpu-sample", type=int, default=1, help="0 leaves the CPU baseline / parity sample out")
+    ap.add_argument("--sustained-seconds", type=float, default=2.5, help="length of the back-to-back run behind `sustained` (0 leaves it out)")
     ap.add_argument("--queries", type=int, default=0,
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
                          "the printed line is then not a benchmark result")
@@ -684,7 +687,7 @@ def main() -> None:
                      "traffic_source": f"ncu dram__bytes_read.sum + dram__bytes_write.sum of a {DRAM_CAPTURE['queries']}-query launch "
                                        f"({DRAM_CAPTURE['summary']}), scaled by the queries of one launch",
                      "peak_source": peaks["source"] + " (burst)",
-                     "kernel": "sparse_mla_fwd_tc_kernel", "algorithmic_flop_per_launch": flop / world},
+                     "kernel": "sparse_mla_fwd_pair_kernel", "algorithmic_flop_per_launch": flop / world},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
         "gpu_launches": args.steps * world,
@@ -705,9 +708,9 @@ def main() -> None:
             extras = {"error": f"{type(exc).__name__}: {exc}"}
         line["other_stages"] = extras
 
-    if rank == 0 and world == 1 and not args.queries:
+    if rank == 0 and world == 1 and not args.queries and args.sustained_seconds > 0:
         try:
-            line["sustained"] = measure_sustained(kernel, q, kv, idx, q0, flop, local_rank, peaks)
+            line["sustained"] = measure_sustained(kernel, q, kv, idx, q0, flop, local_rank, peaks, seconds=args.sustained_seconds)
             copy_peak = measure_copy_peak(dev)
             line["e2e"]["pinned_copy_peak"] = copy_peak
             # a step moves h2d bytes in and d2h bytes out concurrently: bound = the slower direction at the both-directions rate
