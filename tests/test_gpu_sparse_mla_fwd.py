@@ -201,6 +201,38 @@ def test_split_kv_matches_unsplit_and_oracle(nsplit):
     assert_close_fp(spl_l, ref_l, "lse vs oracle")
 
 
+def test_pair_kernel_agrees_with_split_kernel_and_repeats_bit_identically(monkeypatch):
+    """The default kernel (cta_group::2 MMAs, heads split over the SM pair) against the kernel it replaced (each CTA all
+    heads and half of the dims), on items of several tiles with causal (short) rows among them; and two launches of the
+    default kernel give the same bits: every accumulator has one issuing thread, so the summation order is fixed."""
+    q, kv, idx = orc.make_sparse_mla_inputs(1, 96, 2048, 128, 512, seed=21)
+    monkeypatch.delenv("DSA_FWD_KERNEL", raising=False)
+    a_o, a_l = _fwd(q, kv, idx, IMPL_TC)
+    b_o, b_l = _fwd(q, kv, idx, IMPL_TC)
+    assert torch.equal(a_o, b_o) and torch.equal(a_l, b_l)
+    monkeypatch.setenv("DSA_FWD_KERNEL", "split")
+    s_o, s_l = _fwd(q, kv, idx, IMPL_TC)
+    assert_close_fp(a_o, s_o, "pair vs split kernel out")
+    assert_close_fp(a_l, s_l, "pair vs split kernel lse")
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(a_o, ref_o, "out vs oracle")
+    assert_close_fp(a_l, ref_l, "lse vs oracle")
+
+
+def test_units_of_one_tile_between_empty_units_repeat_bit_identically():
+    """Many work units of a single tile with empty units between them (5 tiles over 16 shares): the two Q K^T issuing
+    threads alternate, each skipping every other unit, which is where a hand-over that lets a thread run a unit ahead would
+    show as a result that changes between launches."""
+    q, kv, idx = orc.make_sparse_mla_inputs(2, 40, 400, 128, 320, seed=13)
+    first_o, first_l = _fwd(q, kv, idx, IMPL_TC, nsplit=16)
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(first_o, ref_o, "out vs oracle")
+    assert_close_fp(first_l, ref_l, "lse vs oracle")
+    for _ in range(10):
+        o, l = _fwd(q, kv, idx, IMPL_TC, nsplit=16)
+        assert torch.equal(o, first_o) and torch.equal(l, first_l)
+
+
 def test_split_kv_is_chosen_for_a_few_sequences_and_handles_absent_queries():
     """Decode of 4 sequences: the library splits on its own (fewer queries than SM pairs); per-sequence lengths, one
     sequence without its query (q_len 0): out = 0 and lse = -inf there."""

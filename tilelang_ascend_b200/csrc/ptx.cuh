@@ -14,6 +14,7 @@ enum : int {
   kStatusOk = 0,
   kStatusBarrierTimeout = 1,  // a bounded mbarrier wait ran out
   kStatusBadIndex = 2,        // debug bounds check tripped
+  kStatusBadLayout = 3,       // a kernel found its shared memory window not aligned as it needs
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -73,15 +74,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 // Same bounded wait with acquire semantics at cluster scope (the arrivals come from the peer CTA).
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-#ifdef DSA_SPIN_CLUSTER
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -89,7 +81,6 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
-#endif
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, int* status) {

@@ -665,12 +665,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         const int first = (g & 1) == par ? 0 : 1;            // this thread's first tile of the item
         const int last = nvt - 1 - (((g + nvt - 1) & 1) == par ? 0 : 1);   // ... and its last one
         if (nvt > 0) {  // items without a key neither load Q nor touch O: their barriers are skipped on both sides
-          if (first < nvt && !mbar_wait_cluster(bar(kBarQReady), ne & 1, p.status)) { ok = false; break; }
+          // (waited for also when no tile of the item is mine: a thread that skipped a phase of this barrier would find its
+          // next parity test satisfied by the phase before and run an item ahead of its Q)
+          if (!mbar_wait_cluster(bar(kBarQReady), ne & 1, p.status)) { ok = false; break; }
           ++ne;
-          if (first >= nvt) {  // no tile of this item is mine: I am done with its Q at once (both CTAs are told)
-            mbar_arrive(bar(kBarQFree));
-            mbar_arrive_cluster_relaxed(map_to_cta(bar_addr(kBarQFree), 1));
-          }
+          // No tile of this item is mine: I am done with its Q at once.  Said with a commit, not a plain arrive: a plain arrive
+          // could overtake the commit that ended this thread's previous item and complete THAT item's phase while its MMAs
+          // still read Q; a commit arrives only after everything this thread issued before.
+          if (first >= nvt) umma_pair_commit(bar(kBarQFree), 3);
         }
         for (int it = first; ok && it < nvt; it += 2) {
           const int gg = g + it, u = gg + 2 * ne;   // ring slot: two slots per non-empty item so far carried Q rows
