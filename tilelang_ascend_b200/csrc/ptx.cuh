@@ -253,6 +253,43 @@ __device__ __forceinline__ void umma_pair_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same three instructions guarded by `go` INSIDE the statement, for an issuing warp that stays converged: all 32 lanes
+// execute the surrounding code (loops, waits, descriptor arithmetic) and the one lane with go != 0 issues.  Measured on
+// sm_100a: a lone lane running the loop in divergent code issues one MMA every ~45 clocks whatever its size, a converged warp
+// with a predicated issue one every ~19 clocks (N = 64 on an SM pair, i.e. at the rate of the tensor cores).
+__device__ __forceinline__ uint32_t elect_one_lane() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void umma_pair_ss_if(uint32_t go, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair_ts_if(uint32_t go, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair_commit_if(uint32_t go, uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(smem_u32(bar)),
+      "h"(cta_mask), "r"(go)
+      : "memory");
+}
 // The mbarrier at shared-memory offset `bar` of EVERY CTA named in cta_mask (bit i = CTA i of the cluster) receives one
 // arrival once all tcgen05 operations this thread issued so far have completed on both SMs.  (An mbarrier arrive that is
 // broadcast to the CTAs of the cluster -- not a load.)

@@ -648,67 +648,72 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     }
   } else if (warp == kQkWarp || warp == kQkWarpB) {
     const int par = warp == kQkWarp ? 0 : 1;
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
       // ================================ Q K^T issuers (even CTA) ====================================
       // S[128 heads x 64 keys] over 36 (32 without rope dims) steps of 16 dims: A = Q (tensor memory for dims < 384, shared
-      // memory beyond), B = the 32 gathered rows of each CTA.  One thread issues an MMA about every 45 clocks whatever its
-      // size, and one of these takes 16: two threads, one for the even tiles (score buffer 0) and one for the odd tiles
-      // (buffer 1), keep the tensor cores fed.
+      // memory beyond), B = the 32 gathered rows of each CTA.  The WHOLE warp walks the loops and waits, converged, and one
+      // elected lane issues through predicated instructions (see umma_pair_ss_if for why).  Two such warps, one for the even
+      // tiles (score buffer 0) and one for the odd tiles (buffer 1), so that the next tile's MMAs are queued while this
+      // tile's hand-overs are in flight.
       constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, kM, kBK, 0, 0);
+      const uint32_t go = elect_one_lane();
+      auto wait_all = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar(slot), parity, p.status)); };
+      auto wait_all_cluster = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait_cluster(bar(slot), parity, p.status)); };
       int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
         const int item = item_of(k);
         if (item < 0) break;
         const int qp = k & 1;
-        if (!mbar_wait(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
+        if (!wait_all(kBarInfoFull + qp, (k >> 1) & 1)) { ok = false; break; }
         const int nvt = info[qp * 2];
-        const int first = (g & 1) == par ? 0 : 1;            // this thread's first tile of the item
+        const int first = (g & 1) == par ? 0 : 1;            // this warp's first tile of the item
         const int last = nvt - 1 - (((g + nvt - 1) & 1) == par ? 0 : 1);   // ... and its last one
         if (nvt > 0) {  // items without a key neither load Q nor touch O: their barriers are skipped on both sides
-          // (waited for also when no tile of the item is mine: a thread that skipped a phase of this barrier would find its
+          // (waited for also when no tile of the item is mine: a warp that skipped a phase of this barrier would find its
           // next parity test satisfied by the phase before and run an item ahead of its Q)
-          if (!mbar_wait_cluster(bar(kBarQReady), ne & 1, p.status)) { ok = false; break; }
+          if (!wait_all_cluster(kBarQReady, ne & 1)) { ok = false; break; }
           ++ne;
           // No tile of this item is mine: I am done with its Q at once.  Said with a commit, not a plain arrive: a plain arrive
-          // could overtake the commit that ended this thread's previous item and complete THAT item's phase while its MMAs
-          // still read Q; a commit arrives only after everything this thread issued before.
-          if (first >= nvt) umma_pair_commit(bar(kBarQFree), 3);
+          // could overtake the commit that ended this warp's previous item and complete THAT item's phase while its MMAs
+          // still read Q; a commit arrives only after everything this lane issued before.
+          if (first >= nvt) umma_pair_commit_if(go, bar(kBarQFree), 3);
         }
-        for (int it = first; ok && it < nvt; it += 2) {
+        for (int it = first; it < nvt; it += 2) {
           const int gg = g + it, u = gg + 2 * ne;   // ring slot: two slots per non-empty item so far carried Q rows
           const int s = u % kStages, sb = par;
           const uint32_t stage = sBase + s * kStageBytes;
-          if (!mbar_wait(bar(kBarKvFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
-          if (!mbar_wait_cluster(bar(kBarPeerKvFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
+          if (!wait_all(kBarKvFull + s, (u / kStages) & 1)) { ok = false; break; }
+          if (!wait_all_cluster(kBarPeerKvFull + s, (u / kStages) & 1)) { ok = false; break; }
           // the softmax warps of both CTAs must have read the scores of tile gg-2 out of this buffer
-          if (gg >= 2 && !mbar_wait(bar(kBarSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
-          if (gg >= 2 && !mbar_wait_cluster(bar(kBarPeerSFree + sb), ((gg >> 1) + 1) & 1, p.status)) { ok = false; break; }
+          if (gg >= 2 && !wait_all(kBarSFree + sb, ((gg >> 1) + 1) & 1)) { ok = false; break; }
+          if (gg >= 2 && !wait_all_cluster(kBarPeerSFree + sb, ((gg >> 1) + 1) & 1)) { ok = false; break; }
           fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
           tc_fence_after();
-          tr(1, gg);
+          if (go) tr(1, gg);
           const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int c = 0; c < 6; ++c) {
 #pragma unroll
             for (int kq = 0; kq < 4; ++kq)
-              umma_pair_ts(tS + sb * 32, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunk + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
+              umma_pair_ts_if(go, tS + sb * 32, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunk + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
           }
           const uint64_t da0 = make_smem_desc(sQ + (k & 1) * kQBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int c = 0; c < kQSmemChunks; ++c) {
 #pragma unroll
             for (int kq = 0; kq < 4; ++kq)
-              umma_pair_ss(tS + sb * 32, da0 + ((c * kQChunk + kq * 32) >> 4), db0 + (((6 + c) * kChunk + kq * 32) >> 4), idesc_qk, 1);
+              umma_pair_ss_if(go, tS + sb * 32, da0 + ((c * kQChunk + kq * 32) >> 4), db0 + (((6 + c) * kChunk + kq * 32) >> 4), idesc_qk, 1);
           }
-          umma_pair_commit(bar(kBarSFull + sb), 3);
-          tr(2, gg);
-          if (it == last) umma_pair_commit(bar(kBarQFree), 3);  // this thread's share of "the item's Q may be replaced"
+          umma_pair_commit_if(go, bar(kBarSFull + sb), 3);
+          if (go) tr(2, gg);
+          if (it == last) umma_pair_commit_if(go, bar(kBarQFree), 3);  // this warp's share of "the item's Q may be replaced"
         }
         if (!ok) break;
         g += nvt;
-        mbar_arrive(bar(kBarInfoEmpty + qp));
+        if (go) mbar_arrive(bar(kBarInfoEmpty + qp));
+        __syncwarp();
       }
-    } else if (lane == 0 && rank == 1) {
+    } else if (lane == 0) {
       // ---- odd CTA: tell the even CTA when this CTA's rows of a tile have landed (warp 16) / when this CTA's softmax and
       // exchange warps are past a score buffer (warp 18) ----
       const uint32_t target = map_to_cta(sBars, 0);
@@ -738,31 +743,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       }
     }
   } else if (warp == kPvWarp || warp == kRelayWarp) {
-    if (lane == 0 && rank == 0) {
-      const int j = warp == kPvWarp ? 0 : 1;   // which of the two N = 256 MMAs per 16 keys this thread issues
-      // ================================ P V issuer (even CTA) =======================================
+    if (rank == 0) {
+      const int j = warp == kPvWarp ? 0 : 1;   // which of the two N = 256 MMAs per 16 keys this warp issues
+      // ================================ P V issuers (even CTA) ======================================
       // O[128 heads x 512 dims] += P[128 x 64] . V[64 x 512] as two MMAs of N = 256 per 16 keys: P K-major in shared memory,
       // V MN-major: keys of half kh, dims of the CTA's half j at stage + (4 kh + 2 j) chunks (own rows or swapped-in rows).
+      // Converged warps with one issuing lane, like the Q K^T issuers.
       constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, kM, 256, 0, 1);
+      const uint32_t go = elect_one_lane();
+      auto wait_all = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar(slot), parity, p.status)); };
+      auto wait_all_cluster = [&](int slot, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait_cluster(bar(slot), parity, p.status)); };
       int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
         const int item = item_of(k);
         if (item < 0) break;
         const int qp = k & 1;
-        if (!mbar_wait(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status)) { ok = false; break; }
+        if (!wait_all(kBarInfoFull + qp, (k >> 1) & 1)) { ok = false; break; }
         const int nvt = info[qp * 2];
-        for (int it = 0; ok && it < nvt; ++it, ++g) {
+        for (int it = 0; it < nvt; ++it, ++g) {
           const int u = g + 2 * (ne + 1);   // ring slot (ne counts the non-empty items BEFORE this one)
           const int s = u % kStages, pb = g & 1;
-          if (!mbar_wait(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
-          if (!mbar_wait_cluster(bar(kBarPeerPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
-          tr(13, g);
-          if (!mbar_wait_cluster(bar(kBarVFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
-          tr(8, g);
-          if (!mbar_wait_cluster(bar(kBarPeerVFull + s), (u / kStages) & 1, p.status)) { ok = false; break; }
-          tr(9, g);
+          if (!wait_all(kBarPReady + pb, (g >> 1) & 1)) { ok = false; break; }
+          if (!wait_all_cluster(kBarPeerPReady + pb, (g >> 1) & 1)) { ok = false; break; }
+          if (go) tr(13, g);
+          if (!wait_all_cluster(kBarVFull + s, (u / kStages) & 1)) { ok = false; break; }
+          if (go) tr(8, g);
+          if (!wait_all_cluster(kBarPeerVFull + s, (u / kStages) & 1)) { ok = false; break; }
+          if (go) tr(9, g);
           // the first P V of an item overwrites O: the previous non-empty item's output must have been read out
-          if (it == 0 && ne > 0 && !mbar_wait_cluster(bar(kBarOFree), (ne - 1) & 1, p.status)) { ok = false; break; }
+          if (it == 0 && ne > 0 && !wait_all_cluster(kBarOFree, (ne - 1) & 1)) { ok = false; break; }
           fence_proxy_async_smem();
           tc_fence_after();
           const uint32_t stage = sBase + s * kStageBytes;
@@ -770,17 +779,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t dv = make_smem_desc(stage + (4 * (ks >> 1) + 2 * j) * kChunk + (ks & 1) * 2048, kChunk, 1024, kSwizzle128B);
-            umma_pair_ss(tO + 128 * j, dp0 + ((ks * 32) >> 4), dv, idesc_pv, (it | ks) != 0);
+            umma_pair_ss_if(go, tO + 128 * j, dp0 + ((ks * 32) >> 4), dv, idesc_pv, (it | ks) != 0);
           }
-          umma_pair_commit(bar(kBarKvEmpty + s), 3);
-          umma_pair_commit(bar(kBarPFree + pb), 3);
-          tr(10, g);
+          umma_pair_commit_if(go, bar(kBarKvEmpty + s), 3);
+          umma_pair_commit_if(go, bar(kBarPFree + pb), 3);
+          if (go) tr(10, g);
         }
         if (!ok) break;
         if (nvt > 0) ++ne;
-        mbar_arrive(bar(kBarInfoEmpty + qp));
+        if (go) mbar_arrive(bar(kBarInfoEmpty + qp));
+        __syncwarp();
       }
-    } else if (lane == 0 && rank == 1) {
+    } else if (lane == 0) {
       // ---- odd CTA: tell the even CTA when the even CTA's half of the swap has landed here (warp 17) / when this CTA's
       // softmax warps have written P (warp 19) ----
       const bool fwd_v = warp == kPvWarp;
