@@ -221,6 +221,45 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The same three instructions guarded by `go` INSIDE the statement, for an issuing warp that stays converged: all 32 lanes
+// execute the surrounding code (loops, waits, descriptor arithmetic) and the one lane with go != 0 (elect_one_lane) issues.
+// Measured on sm_100a: a lone lane running the loop in divergent code issues one MMA every ~45 clocks whatever its size; a
+// converged warp with a predicated issue keeps up with the tensor cores down to the smallest shapes (~19 clocks for N = 64
+// on an SM pair).
+__device__ __forceinline__ uint32_t elect_one_lane() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void umma_ss_if(uint32_t go, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_if(uint32_t go, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(go)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_if(uint32_t go, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
+      "r"(go)
+      : "memory");
+}
+
 // ---- the same for a pair of CTAs (cta_group::2): ONE thread of the even CTA of a 2-CTA cluster issues an MMA that runs on
 // both SMs.  Each CTA supplies its half of the rows of A (from its own shared memory or tensor memory) and its half of the
 // rows of B (the N dimension) at the SAME shared-memory offsets / tensor-memory addresses, and receives the rows of D that
@@ -253,15 +292,7 @@ __device__ __forceinline__ void umma_pair_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// The same three instructions guarded by `go` INSIDE the statement, for an issuing warp that stays converged: all 32 lanes
-// execute the surrounding code (loops, waits, descriptor arithmetic) and the one lane with go != 0 issues.  Measured on
-// sm_100a: a lone lane running the loop in divergent code issues one MMA every ~45 clocks whatever its size, a converged warp
-// with a predicated issue one every ~19 clocks (N = 64 on an SM pair, i.e. at the rate of the tensor cores).
-__device__ __forceinline__ uint32_t elect_one_lane() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred;
-}
+// Predicated forms for a converged issuing warp (see umma_ss_if).
 __device__ __forceinline__ void umma_pair_ss_if(uint32_t go, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"

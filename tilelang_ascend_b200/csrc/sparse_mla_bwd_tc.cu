@@ -246,16 +246,18 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
     cp_async_wait<0>();
   } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ====================================================
-    if (lane == 0 && run) {
+    // the whole warp walks the loop and waits, converged; one elected lane issues through predicated instructions
+    if (run) {
       constexpr uint32_t idesc = make_idesc_f16(kBF16, kM, kBK, 0, 0);
+      const uint32_t go = elect_one_lane();
       int g = 0;
-      ok = mbar_wait(a_ready, 0, p.status);
+      ok = __all_sync(0xffffffffu, mbar_wait(a_ready, 0, p.status));
       for (int tile = 0; ok && tile < ps.ntiles; ++tile) {
         if (smask[tile] == 0ull) continue;
         const int s = g % kStages, sb = g % kSBufs;
         const uint32_t stage = sBase + s * Cfg::kStageBytes;
-        if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
-        if (g >= kSBufs && !mbar_wait(&s_free[sb], ((g / kSBufs) + 1) & 1, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[s], (g / kStages) & 1, p.status))) { ok = false; break; }
+        if (g >= kSBufs && !__all_sync(0xffffffffu, mbar_wait(&s_free[sb], ((g / kSBufs) + 1) & 1, p.status))) { ok = false; break; }
         fence_proxy_async_smem();  // the gathered rows were written by cp.async of other threads
         tc_fence_after();
         const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
@@ -263,10 +265,10 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 1) sparse_mla_bwd_scores_kern
         for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
           for (int kq = 0; kq < 4; ++kq)
-            umma_ts(tS + sb * kBK, tA + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc, (c | kq) != 0);
+            umma_ts_if(go, tS + sb * kBK, tA + (c * 4 + kq) * 8, db0 + ((c * kChunkBytes + kq * 32) >> 4), idesc, (c | kq) != 0);
         }
-        umma_commit(&s_full[sb]);
-        umma_commit(&kv_empty[s]);
+        umma_commit_if(go, &s_full[sb]);
+        umma_commit_if(go, &kv_empty[s]);
         ++g;
       }
     }
@@ -458,26 +460,27 @@ __global__ void __launch_bounds__(bwdtc::kThreads, 2) sparse_mla_bwd_dq_kernel(c
   } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ====================================================
     // D[128 heads x 192 dims] += dS[128 x 64 keys] (K-major, 16 keys = 32 bytes per step) . rows[64 keys x 192 dims] (MN-major)
-    if (lane == 0 && run) {
+    if (run) {  // converged warp, one elected lane issues
       constexpr uint32_t idesc = make_idesc_f16(kBF16, kM, kDimsPerCta, 0, 1);
+      const uint32_t go = elect_one_lane();
       int g = 0;
       for (int tile = 0; ok && tile < ps.ntiles; ++tile) {
         if (smask[tile] == 0ull) continue;
         const int s = g % kStages;
         const uint32_t stage = sBase + s * kStageBytes;
-        if (!mbar_wait(&a_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
-        if (!mbar_wait(&kv_full[s], (g / kStages) & 1, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&a_full[s], (g / kStages) & 1, p.status))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[s], (g / kStages) & 1, p.status))) { ok = false; break; }
         fence_proxy_async_smem();
         tc_fence_after();
         const uint64_t da0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
         const uint64_t db0 = make_smem_desc(stage + kTileBytes, kChunkBytes, 1024, kSwizzle128B);
 #pragma unroll
         for (int ks = 0; ks < kBK / 16; ++ks)
-          umma_ss(tD, da0 + ((ks * 32) >> 4), db0 + ((ks * 2048) >> 4), idesc, (g | ks) != 0);
-        umma_commit(&empty[s]);
+          umma_ss_if(go, tD, da0 + ((ks * 32) >> 4), db0 + ((ks * 2048) >> 4), idesc, (g | ks) != 0);
+        umma_commit_if(go, &empty[s]);
         ++g;
       }
-      if (ok && g > 0) umma_commit(done);
+      if (ok && g > 0) umma_commit_if(go, done);
     }
   } else {
     // ================================ epilogue ======================================================
@@ -606,33 +609,34 @@ __global__ void __launch_bounds__(bwdtc::dkv::kThreadsDkv, 1) sparse_mla_bwd_dkv
     // ================================ MMA issuer ====================================================
     // acc[128 keys x 192 dims] = dS^T[128 keys x 128 heads] . Q[128 heads x 192 dims] + P^T . dO[128 heads x its dims]:
     // both operands MN-major (contraction over heads = rows of the shared-memory images), 16 heads = 2048 bytes per step.
-    if (lane == 0 && run) {
+    if (run) {  // converged warp, one elected lane issues
       constexpr uint32_t idesc_q = make_idesc_f16(kBF16, kM, kDimsPerCta, 1, 1);
       constexpr uint32_t idesc_o2 = make_idesc_f16(kBF16, kM, 128, 1, 1);
       const uint32_t idesc_o = do_chunks == 3 ? idesc_q : idesc_o2;
-      ok = mbar_wait(b_ready, 0, p.status);
+      const uint32_t go = elect_one_lane();
+      ok = __all_sync(0xffffffffu, mbar_wait(b_ready, 0, p.status));
       const uint64_t dq0 = make_smem_desc(sQ, kTileBytes, 1024, kSwizzle128B);
       const uint64_t do0 = make_smem_desc(sDO, kTileBytes, 1024, kSwizzle128B);
       int g = 0, j = 0;
       for (int tp = 0; ok && tp < npairs; ++tp) {
         if ((smask[2 * tp] | smask[2 * tp + 1]) == 0ull) continue;
         const int ab = g & 1;
-        if (g >= 2 && !mbar_wait(&acc_free[ab], ((g >> 1) + 1) & 1, p.status)) { ok = false; break; }
+        if (g >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_free[ab], ((g >> 1) + 1) & 1, p.status))) { ok = false; break; }
 #pragma unroll 1
         for (int which = 0; which < 2; ++which, ++j) {
           const int s = j % kStages;
-          if (!mbar_wait(&full[s], (j / kStages) & 1, p.status)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (j / kStages) & 1, p.status))) { ok = false; break; }
           tc_fence_after();
           const uint64_t da0 = make_smem_desc(sBase + s * kPairBytes, kTileBytes, 1024, kSwizzle128B);
           const uint64_t db0 = which == 0 ? dq0 : do0;
           const uint32_t idesc = which == 0 ? idesc_q : idesc_o;
 #pragma unroll
           for (int ks = 0; ks < kM / 16; ++ks)
-            umma_ss(tAcc + ab * kDimsPerCta, da0 + ((ks * 2048) >> 4), db0 + ((ks * 2048) >> 4), idesc, (which | ks) != 0);
-          umma_commit(&empty[s]);
+            umma_ss_if(go, tAcc + ab * kDimsPerCta, da0 + ((ks * 2048) >> 4), db0 + ((ks * 2048) >> 4), idesc, (which | ks) != 0);
+          umma_commit_if(go, &empty[s]);
         }
         if (!ok) break;
-        umma_commit(&acc_full[ab]);
+        umma_commit_if(go, &acc_full[ab]);
         ++g;
       }
     }
