@@ -37,25 +37,29 @@ constexpr int kM = 128;                                // heads per cluster
 constexpr int kHeads = 64;                             // heads per CTA
 constexpr int kBK = 64;                                // keys per tile
 constexpr int kKeys = 32;                              // keys per tile and CTA
-constexpr int kStages = 4;
+constexpr int kStages = 5;
 constexpr int kMaxTiles = 128;                         // topk <= 8192
 constexpr uint32_t kChunk = kKeys * 128;               // 4096: 32 keys x 64 dims, 128-byte swizzle
 constexpr uint32_t kStageBytes = 9 * kChunk;           // 36864: 8 latent chunks + the rope chunk
 constexpr uint32_t kSwapBytes = 4 * kChunk;            // 16384: four chunks trade places with the peer's
-constexpr int kQTmemDims = 384;                        // Q dims kept in tensor memory (6 chunks of 64)
 constexpr uint32_t kQChunk = kHeads * 128;             // 8192: 64 heads x 64 dims
 constexpr uint32_t kQBytes = 3 * kQChunk;              // Q dims 384..575 in shared memory
+constexpr uint32_t kQPiece = kHeads * 64;              // 4096: 64 heads x 32 dims, the unit in which those dims ride the stage ring
+constexpr uint32_t kQPieceOff = 3 * kQChunk;           // pieces sit behind the three tensor-memory chunks of a ring slot
 constexpr uint32_t kPBytes = kHeads * kBK * 2;         // 8192: P of one tile [64 heads x 64 keys]
-constexpr uint32_t kOffQ = kStages * kStageBytes;      // 147456
-constexpr uint32_t kOffP = kOffQ + 2 * kQBytes;        // two Q buffers (items alternate), then two P buffers
+constexpr uint32_t kOffQ = kStages * kStageBytes;      // 184320
+constexpr uint32_t kOffP = kOffQ + kQBytes;            // the Q buffer, then two P buffers
 constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
-constexpr uint32_t kOffRowMax = kOffBar + 1024;        // [2][4][64] floats: row maxima of the four threads of a row, by tile parity
+constexpr uint32_t kOffRowMax = kOffBar + 512;         // [2][4][64] floats: row maxima of the four threads of a row, by tile parity
 constexpr uint32_t kOffRowSum = kOffRowMax + 2 * 4 * 64 * 4;   // [4][64] floats
 constexpr uint32_t kOffMask = kOffRowSum + 4 * 64 * 4;         // [2][kMaxTiles] 64-bit validity masks (per item parity)
 constexpr uint32_t kOffList = kOffMask + 2 * kMaxTiles * 8;    // [2][kMaxTiles] 16-bit tile ids
 constexpr uint32_t kOffInfo = kOffList + 2 * kMaxTiles * 2;    // [2] {tile count, run flag}; scratch words of the warps behind it
-constexpr uint32_t kSmemBytes = kOffInfo + 256 + 1024;         // + slack to align the base to 1024 B
+// No slack to align the base: the kernel's only shared memory is this dynamic array, declared with 1024-byte alignment (the
+// swizzled operand tiles need it); the kernel checks the base and reports kStatusBadLayout instead of running misaligned.
+constexpr uint32_t kSmemBytes = kOffInfo + 256;
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
+static_assert(kQPieceOff + 3 * kQPiece <= kStageBytes, "a ring slot holds half of Q");
 constexpr int kSoftmaxWarps = 8;                       // warp w: lanes 32 (w & 3) .. +31, score columns 16 (w >> 2) .. +15
 constexpr int kFirstGatherWarp = 8;
 constexpr int kFirstExchangeWarp = 12;                 // 12..15: (w & 3) is also the lane quarter of their tensor-memory stores
@@ -71,25 +75,26 @@ constexpr uint32_t kGatherBarrier = 5;                 // named barrier of the 1
 // barrier slots (8 bytes each).  "even CTA" barriers receive one remote arrival per event from a forwarding thread of the odd CTA:
 // a remote arrive with release semantics costs its issuer about a thousand clocks, which the softmax warps cannot afford per
 // tile -- they arrive on barriers of their own CTA and a dedicated thread passes the completed phase on.
-constexpr int kBarKvFull = 0;        // [4] count 128: cp.async completion of this CTA's gather threads
-constexpr int kBarPeerKvFull = 4;    // [4] count 1, even CTA: the odd CTA's gather of the stage landed
-constexpr int kBarKvEmpty = 8;       // [4] count 2: commits of the two P V issuers after their MMAs of the stage
-constexpr int kBarSFull = 12;        // [2] count 1: commit after the Q K^T MMAs
-constexpr int kBarSFree = 14;        // [2] count 12: this CTA's softmax (and exchange) warps are past the scores
-constexpr int kBarPeerSFree = 16;    // [2] count 1, even CTA: ... the odd CTA's
-constexpr int kBarPeerRead = 18;     // [4] count 4: the peer's exchange warps hold their swap region in registers
-constexpr int kBarVFull = 22;        // [4] count 1 + 16384 bytes: the peer's half of the swap landed here
-constexpr int kBarPeerVFull = 26;    // [4] count 1, even CTA: ... landed in the odd CTA
-constexpr int kBarPReady = 30;       // [2] count 8: this CTA's softmax warps wrote P
-constexpr int kBarPeerPReady = 32;   // [2] count 1, even CTA: ... the odd CTA's
-constexpr int kBarPFree = 34;        // [2] count 2: commits of the two P V issuers after their MMAs that read this P buffer
-constexpr int kBarQReady = 36;       // count 8, even CTA: the exchange warps of both CTAs loaded the item's Q
-constexpr int kBarQFree = 37;        // count 2: both Q K^T issuers are done with the item's Q (commit after their last MMAs of the item)
-constexpr int kBarOFree = 38;        // count 16, even CTA: the softmax warps drained the previous item's output
-constexpr int kBarInfoFull = 39;     // [2] count 1: tile list of an item published by the gather warps
-constexpr int kBarInfoEmpty = 41;    // [2] count 16 (15 in the even CTA): softmax, exchange, issuer / forwarding warps are done with the list
-constexpr int kBarQRead = 43;        // count 4: the exchange warps have moved a Q slot of the ring to tensor memory
-constexpr int kBarCount = 44;
+constexpr int kBarKvFull = 0;                     // [kStages] count 128: cp.async completion of this CTA's gather threads
+constexpr int kBarPeerKvFull = kStages;           // [kStages] count 1, even CTA: the odd CTA's gather of the stage landed
+constexpr int kBarKvEmpty = 2 * kStages;          // [kStages] count 2: commits of the two P V issuers after their MMAs of the stage
+constexpr int kBarPeerRead = 3 * kStages;         // [kStages] count 4: the peer's exchange warps hold their swap region in registers
+constexpr int kBarVFull = 4 * kStages;            // [kStages] count 1 + 16384 bytes: the peer's half of the swap landed here
+constexpr int kBarPeerVFull = 5 * kStages;        // [kStages] count 1, even CTA: ... landed in the odd CTA
+constexpr int kBarSFull = 6 * kStages;            // [2] count 1: commit after the Q K^T MMAs
+constexpr int kBarSFree = kBarSFull + 2;          // [2] count 12: this CTA's softmax (and exchange) warps are past the scores
+constexpr int kBarPeerSFree = kBarSFull + 4;      // [2] count 1, even CTA: ... the odd CTA's
+constexpr int kBarPReady = kBarSFull + 6;         // [2] count 8: this CTA's softmax warps wrote P
+constexpr int kBarPeerPReady = kBarSFull + 8;     // [2] count 1, even CTA: ... the odd CTA's
+constexpr int kBarPFree = kBarSFull + 10;         // [2] count 2: commits of the two P V issuers after their MMAs that read this P buffer
+constexpr int kBarQReady = kBarSFull + 12;        // count 8, even CTA: the exchange warps of both CTAs loaded the item's Q
+constexpr int kBarQFree = kBarSFull + 13;         // count 2: both Q K^T issuers are done with the item's Q (commit after their last MMAs of the item)
+constexpr int kBarOFree = kBarSFull + 14;         // count 16, even CTA: the softmax warps drained the previous item's output
+constexpr int kBarInfoFull = kBarSFull + 15;      // [2] count 1: tile list of an item published by the gather warps
+constexpr int kBarInfoEmpty = kBarSFull + 17;     // [2] count 16: softmax, exchange, issuer / forwarding warps are done with the list
+constexpr int kBarQRead = kBarSFull + 19;         // count 4: the exchange warps have emptied a Q slot of the ring
+constexpr int kBarCount = kBarSFull + 20;
+static_assert(kBarCount * 8 + 16 <= 512, "barrier region");
 }  // namespace pr
 
 // Remote arrives in this kernel are RELAXED: an arrive with release semantics at cluster scope costs its thread about 1100
@@ -123,9 +128,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   constexpr int kRowBytes = kRope ? kD * 2 : kDV * 2;
   constexpr int kChunks = kRope ? 9 : 8;               // 64-dim chunks of a key row
   constexpr int kQSmemChunks = kChunks - 6;            // Q chunks 6.. in shared memory
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kQPiecesPerSlot = kQSmemChunks;        // ... as 2 kQSmemChunks pieces of 32 dims, half of them in each of the two ring slots
+  extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sBase = smem_u32(smem);
+  if (sBase & 1023u) {  // same in every CTA of the launch: nobody runs, nobody waits
+    if (threadIdx.x == 0) atomicCAS(p.status, kStatusOk, kStatusBadLayout);
+    return;
+  }
   const uint32_t sQ = sBase + kOffQ;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
   const uint32_t sBars = sBase + kOffBar;
@@ -461,7 +470,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       named_bar_sync(kGatherBarrier, 128);
       const int nvt = info[qp * 2];
       if (nvt > 0) {
-        // The item's Q rows for tensor memory (dims 0..383) travel through the stage ring as two slots AHEAD of the item's
+        // The item's Q rows travel through the stage ring as two slots AHEAD of the item's
         // tiles -- requested as soon as stages come free, i.e. while the previous item is still being worked on -- so that at
         // the item boundary the exchange warps only move them from shared memory to tensor memory.  Slot j: dims 192 j ..
         // 192 j + 191 as three chunks of [64 rows x 128 bytes] (128-byte swizzle); one instruction copies 128 bytes of four rows.
@@ -482,6 +491,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
                 const bool v = row < nrows;
                 cp_async16(stage + cj * kQChunk + sw128_offset(row, unit16),
                            v ? q0 + row * kRowBytes + (3 * j + cj) * 128 + unit16 * 16 : reinterpret_cast<const uint8_t*>(p.q), v ? 16u : 0u);
+              }
+            // ... and behind them half of the dims that stay in shared memory (384..), as pieces of [64 rows x 32 dims]: 64
+            // bytes per row, the four 16-byte units of a row permuted by (row / 2) % 4, so that both these copies (64 bytes of
+            // eight rows per instruction) and the row-per-lane reads of the exchange warps are free of bank conflicts
+#pragma unroll
+            for (int pc = 0; pc < kQPiecesPerSlot; ++pc)
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int row = (gt >> 2) + 32 * i, u16 = gt & 3;
+                const bool v = row < nrows;
+                cp_async16(stage + kQPieceOff + pc * kQPiece + row * 64 + ((u16 ^ ((row >> 1) & 3)) << 4),
+                           v ? q0 + row * kRowBytes + 768 + (kQPiecesPerSlot * j + pc) * 64 + u16 * 16 : reinterpret_cast<const uint8_t*>(p.q),
+                           v ? 16u : 0u);
               }
             cp_async_arrive_noinc(bar(kBarKvFull + s));
           }
@@ -518,8 +540,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     cp_async_wait<0>();
   } else if (warp < kQkWarp) {
     // ================================ Q loader + swap of the value halves ===========================
-    // Q of an item: row m of the CTA's 64 heads; dims 0..383 go to tensor memory (lane L holds row L % 64: the A operand of
-    // a 64-row half must be present in both lane halves), dims 384.. to shared memory.  Then, per tile, the swap (see top).
+    // Q of an item arrives in two slots of the stage ring; these warps move it on: row m of the CTA's 64 heads, dims 0..383 to
+    // tensor memory (lane L holds row L % 64: the A operand of a 64-row half must be present in both lane halves), dims 384..
+    // to the Q buffer in shared memory.  Then, per tile, the swap (see top).
     const int xw = warp - kFirstExchangeWarp;  // = lane quarter of the tensor-memory stores
     const int L = xw * 32 + lane, m = L & 63;
     const int xt = tid - kFirstExchangeWarp * 32;  // 0..127
@@ -528,24 +551,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     const uint32_t dst_off = 4u * rank * kChunk;   // ... go where the peer keeps those dims of ITS keys that I need: its chunks [4 r, +4)
     const uint32_t peer_base = map_to_cta(sBase, peer);
     const uint32_t peer_bars = map_to_cta(sBars, peer);
-    // Shared-memory part of a unit's Q (dims 384..) into Q buffer `buf`.  One instruction copies one 64-dim chunk (128 bytes,
-    // 8 lanes) of four rows: whole lines, unlike a row per lane.  One cp.async group.
-    auto load_q_smem = [&](int u, int buf) {
-      int nrows;
-      const uint8_t* q0 = q_rows_of(u, &nrows);
-#pragma unroll
-      for (int c = 0; c < kQSmemChunks; ++c)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = (xt >> 3) + 16 * i, unit16 = xt & 7;
-          const bool v = row < nrows;
-          cp_async16(sQ + buf * kQBytes + c * kQChunk + sw128_offset(row, unit16),
-                     v ? q0 + row * kRowBytes + (6 + c) * 128 + unit16 * 16 : reinterpret_cast<const uint8_t*>(p.q), v ? 16u : 0u);
-        }
-      cp_async_commit();
-    };
     int g = 0, ne = 0, qslots = 0, qslot_reads = 0;
-    int q_smem_loaded_for = -1;  // item whose shared-memory part of Q was already requested (into buffer item & 1)
     for (int k = 0; run_all && ok; ++k) {
       const int unit = item_of(k);
       if (unit < 0) break;
@@ -556,7 +562,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         // all Q K^T MMAs of the previous non-empty item are complete: the tensor-memory part of Q can be replaced
         if (ne > 0 && !__all_sync(0xffffffffu, mbar_wait<true>(bar(kBarQFree), (ne - 1) & 1, p.status))) { ok = false; break; }
         ++ne;
-        if (q_smem_loaded_for != k) load_q_smem(unit, k & 1);  // not requested ahead (first item, or the item before was empty)
         if (xt == 0) tr(16, k);
         tc_fence_after();
         // Tensor-memory part: the gather warps sent the rows through two slots of the stage ring (see there).  Lane L moves
@@ -576,6 +581,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
             }
             tmem_st32(tQ + lane_base + (3 * j + cj) * 32, w);
           }
+          // the pieces behind them go to the Q buffer in the layout of the MMA's A operand; the two threads of a row copy two
+          // 16-byte units of every piece each
+#pragma unroll
+          for (int pc = 0; pc < kQPiecesPerSlot; ++pc) {
+            const int piece = kQPiecesPerSlot * j + pc;   // 32-dim piece of dims 384..
+#pragma unroll
+            for (int uu = 2 * (xw >> 1); uu < 2 * (xw >> 1) + 2; ++uu) {
+              const uint4 x = ld_shared_v4(stage + kQPieceOff + pc * kQPiece + m * 64 + ((uu ^ ((m >> 1) & 3)) << 4));
+              st_shared_v4(sQ + (piece >> 1) * kQChunk + sw128_offset(m, 4 * (piece & 1) + uu), x.x, x.y, x.z, x.w);
+            }
+          }
           // The slot carried no tile: every barrier of the stage that a tile would have completed once is completed once here,
           // so that the phases of all of them keep in step with the slot number.
           __syncwarp();
@@ -593,22 +609,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         qslots += 2;
-        cp_async_wait<0>();
         if (xt == 0) tr(22, k);
-        fence_proxy_async_smem();
+        fence_proxy_async_smem();  // the Q buffer is read by the tensor cores
         tmem_wait_st();
         if (xt == 0) tr(23, k);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) arrive_at(bar_addr(kBarQReady), 0, rank);
         if (xt == 0) tr(17, k);
-        // the next unit's Q while this item is being worked on: its shared-memory part goes to the other buffer (free: the
-        // Q K^T of every earlier item is complete), the lines of its tensor-memory part are pulled into L2
-        const int next = item_of(k + 1);
-        if (next >= 0) {
-          load_q_smem(next, (k + 1) & 1);
-          q_smem_loaded_for = k + 1;
-        }
       }
       for (int it = 0; it < nvt; ++it, ++g) {
         const int sb = g & 1, s = (g + qslots) % kStages;
@@ -697,7 +705,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
             for (int kq = 0; kq < 4; ++kq)
               umma_pair_ts_if(go, tS + sb * 32, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunk + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
           }
-          const uint64_t da0 = make_smem_desc(sQ + (k & 1) * kQBytes, 16, 1024, kSwizzle128B);
+          const uint64_t da0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int c = 0; c < kQSmemChunks; ++c) {
 #pragma unroll
