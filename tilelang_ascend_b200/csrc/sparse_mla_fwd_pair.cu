@@ -360,13 +360,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         for (int cc = 0; cc < 4; ++cc) {
           tmem_ld32(tO + lane_base + (4 * ch + cc) * 32, v);
           tmem_wait_ld();
-          if (ok && h < p.H && nsplit > 1) {
+          if (nsplit > 1) {
+            // fp32 partial rows: the same detour through the warp's scratch as below, 16 columns (64 bytes per row) at a time
 #pragma unroll
-            for (int gq = 0; gq < 8; ++gq)
-              reinterpret_cast<float4*>(part_row + cc * 32)[gq] =
-                  make_float4(__uint_as_float(v[4 * gq]) * inv_l, __uint_as_float(v[4 * gq + 1]) * inv_l, __uint_as_float(v[4 * gq + 2]) * inv_l,
-                              __uint_as_float(v[4 * gq + 3]) * inv_l);
-          } else if (nsplit <= 1) {
+            for (int hq = 0; hq < 2; ++hq) {
+#pragma unroll
+              for (int gq = 0; gq < 4; ++gq)
+                st_shared_v4(out_scratch + lane * 64 + ((gq ^ ((lane >> 1) & 3)) << 4), __float_as_uint(__uint_as_float(v[16 * hq + 4 * gq]) * inv_l),
+                             __float_as_uint(__uint_as_float(v[16 * hq + 4 * gq + 1]) * inv_l), __float_as_uint(__uint_as_float(v[16 * hq + 4 * gq + 2]) * inv_l),
+                             __float_as_uint(__uint_as_float(v[16 * hq + 4 * gq + 3]) * inv_l));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int r = 8 * i + (lane >> 2), u = lane & 3;
+                const uint4 x = ld_shared_v4(out_scratch + r * 64 + ((u ^ ((r >> 1) & 3)) << 4));
+                if (ok && h - lane + r < p.H) *reinterpret_cast<uint4*>(part_row + static_cast<int64_t>(r - lane) * kDV + cc * 32 + hq * 16 + u * 4) = x;
+              }
+              __syncwarp();
+            }
+          } else {
             // A row per lane would make every store instruction touch 32 lines.  The warp's 32 rows x 64 bytes go through its
             // scratch (a quarter of the P buffers, which are idle: the item's last P V is complete) and leave as 64 contiguous
             // bytes of each of 8 rows per instruction.
@@ -396,7 +408,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         }
       }
       if (tid == 0) tr(19, k);
-      if (nvt > 0 && nsplit <= 1) named_bar_sync(named, 128);  // the block's warps are done with their scratch: P may be written again
+      if (nvt > 0) named_bar_sync(named, 128);  // the block's warps are done with their scratch: P may be written again
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
