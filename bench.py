@@ -34,8 +34,8 @@ FLOP_PER_PAIR_HEAD = 2 * 576 + 2 * 512  # QK^T over 576 dims + PV over 512 dims
 METRIC, UNIT = "dsa_prefill_tokens_per_s", "tokens/s"
 # DRAM bytes per query of the forward kernel, from the ncu capture summarised in profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch divided by its queries); re-derived whenever the kernel changes
-DRAM_CAPTURE = {"read": 96945664, "write": 33952256, "queries": 592,
-                "summary": "profiles/sparse_mla_fwd_tc_kernel__prefill_592q.md"}
+DRAM_CAPTURE = {"read": 96943360, "write": 38995200, "queries": 592,
+                "summary": "profiles/sparse_mla_fwd_pair_kernel__prefill_592q.md"}
 CPU_SAMPLE_BLOCKS, CPU_SAMPLE_BLOCK = 16, 16   # the CPU arm's step: 16 evenly spaced blocks of 16 queries of the workload
 
 
@@ -573,9 +573,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "v4", "hisa"],
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "decode", "v4", "hisa"],
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
-                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'decode' three eager decode steps of --queries sequences (default 64), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
     ap.add_argument("--cpu-sample", type=int, default=1, help="0 leaves the CPU baseline / parity sample out")
     ap.add_argument("--sustained-seconds", type=float, default=2.5, help="length of the back-to-back run behind `sustained` (0 leaves it out)")
     ap.add_argument("--queries", type=int, default=0,
@@ -619,6 +619,14 @@ def main() -> None:
     if args.stage == "backward":
         if rank == 0:
             print(json.dumps({"backward": measure_backward(dev, peaks, w["S"], reps=1, warm=1)}), flush=True)
+        return
+    if args.stage == "decode":
+        if rank == 0:
+            g = torch.Generator(device=dev).manual_seed(7)
+            Bd = args.queries or 64
+            qd, kvd, idxd = decode_inputs(dev, Bd, g)
+            t = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd, kvd, idxd, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=2, warm=1)
+            print(json.dumps({"decode_eager": {"us": t * 1e3, "sequences": Bd, "algorithmic_bytes": decode_bytes(Bd)}}), flush=True)
         return
     if args.stage == "others":
         if rank == 0:
