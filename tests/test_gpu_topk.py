@@ -108,3 +108,28 @@ def test_unordered_mode_returns_the_same_sets_in_index_order(rows, n, k):
         assert np.array_equal(sel, np.sort(ref[r][ref[r] >= 0]))           # same set, ascending
         assert (b[r][len(sel):] == -1).all() and np.isneginf(bv[r][len(sel):]).all()
         assert np.array_equal(bv[r][: len(sel)], x.numpy()[r, sel])
+
+
+@pytest.mark.parametrize("rows,n,k", [(6, 131072, 2048), (3, 60000, 2048), (2, 131072, 8192), (3, 100003, 100)])
+def test_rows_longer_than_shared_memory_are_streamed(rows, n, k):
+    """Rows whose keys do not fit in shared memory (more than about 52 k candidates, e.g. the 131072 keys of a long decode
+    cache): every pass reads the scores again from global memory.  Same arrays as the oracle, with heavy ties (values
+    rounded to 1/8), per-row limits, masked entries, and in the mode without the final sort."""
+    import tilelang_ascend_b200 as dsa
+    rng = np.random.default_rng(rows * 7 + n)
+    x = rng.standard_normal((rows, n)).astype(np.float32)
+    x[0] = np.round(x[0] * 8) / 8                      # a few hundred distinct values: the threshold bin is full of ties
+    x[1, ::3] = -np.inf
+    limits = np.full(rows, n, dtype=np.int32)
+    limits[-1] = n - 12345
+    idx, val = _run(x, k, limits=limits, values=True)
+    ref_i, ref_v = orc.topk_select(x, k, limits=limits, return_values=True)
+    assert np.array_equal(idx, ref_i)
+    assert np.array_equal(val, ref_v)
+    sets = dsa.topk_select_raw(torch.from_numpy(x).cuda(), k, torch.from_numpy(limits).cuda(), ordered=False)
+    check_status()
+    sets = sets.cpu().numpy()
+    for r in range(rows):
+        want = np.sort(ref_i[r][ref_i[r] >= 0])
+        got = sets[r][sets[r] >= 0]
+        assert np.array_equal(got, want)

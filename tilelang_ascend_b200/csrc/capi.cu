@@ -160,8 +160,7 @@ static int topk_select_impl(const float* scores, int64_t rows, int64_t n, int64_
   if (rows == 0) return 0;
   if (rows > 0x7fffffffLL) return fail("too many rows");
   if (top_k > 8192) return fail("top_k must be at most 8192");
-  if (dsa::topk_smem_bytes(static_cast<int>(n), top_k, nullptr) > 220 * 1024)
-    return fail("row too long for the shared-memory selector (n * 4 + pow2(top_k) * 8 must fit 220 KB)");
+  if (n > 0x7fffffffLL) return fail("row too long");
   int err = dsa::launch_topk_select(scores, rows, static_cast<int>(n), row_stride, limits, top_k, out_idx, out_val,
                                     static_cast<cudaStream_t>(stream), ordered);
   return err ? fail_cuda("topk_select launch", err) : 0;

@@ -83,7 +83,6 @@ int dsa_lightning_indexer_noalloc(const void* q, const void* k, const float* w, 
     return fail("problem too large for the built-in scratch: " + std::to_string(need) + " bytes needed, " +
                 std::to_string(static_cast<size_t>(DSA_NOALLOC_SCRATCH_BYTES)) +
                 " available (use dsa_lightning_indexer with a caller-provided workspace)");
-  if (dsa::topk_smem_bytes(S2, top_k, nullptr) > 220 * 1024) return fail("row too long for the shared-memory selector");
   unsigned char* base = nullptr;
   if (scratch_address(&base)) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

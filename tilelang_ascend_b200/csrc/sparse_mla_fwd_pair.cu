@@ -18,9 +18,13 @@
 //   Per CTA: O = 64 heads x 512 dims fp32 in 128 lanes x 256 columns of tensor memory (lanes 0..63: dims 0..255, lanes 64..127:
 //   dims 256..511), two score buffers of 32 columns (lanes 0..63: keys 0..31, lanes 64..127: keys 32..63), Q dims 0..383 as the
 //   tensor-memory A operand (192 columns, the same row in lanes m and m + 64), Q dims 384..575 in shared memory.
-// Warp roles (18 warps): 8 softmax warps (two per 32 lanes: 16 score columns each), 4 gather warps (they also build the items'
-// tile lists), 4 exchange warps (they also load Q), the Q K^T issuer and the P V issuer (lane 0 of two warps of the EVEN CTA;
-// in the odd CTA those warps forward "my gather landed" / "my half of the swap landed" to the even CTA), and no more.
+// A unit's Q rows travel through two slots of the stage ring ahead of the unit's tiles (see the gather warps).
+// Warp roles (20 warps): 8 softmax warps (two per 32 lanes: 16 score columns each), 4 gather warps (they also build the units'
+// tile lists and send Q), 4 exchange warps (the swap; they also move Q from its ring slots to tensor memory and the Q buffer),
+// and four issuing warps in the EVEN CTA: Q K^T of the even tiles, Q K^T of the odd tiles, and one P V issuer per N = 256
+// half.  Issuing warps stay converged -- all lanes walk the loops and waits, one elected lane issues through predicated
+// instructions.  In the odd CTA lane 0 of the same four warps forwards "my gather landed" / "my softmax warps are past the
+// scores" / "my half of the swap landed" / "my P is written" to the even CTA.
 // Barriers the issuers wait for live in the even CTA and count arrivals from both CTAs; completions (tcgen05.commit) are
 // broadcast to the same barrier in both CTAs.  Every wait is bounded; a wait that gives up records status 1 and all roles
 // fall through to the teardown.

@@ -24,6 +24,7 @@ namespace dsa {
 namespace topk {
 constexpr int kThreads = 512;                     // 4 rows (CTAs) per SM hide each other's barrier phases
 constexpr int kWarps = kThreads / 32;
+constexpr size_t kMaxSmemBytes = 220 * 1024;       // rows whose keys do not fit are streamed from global memory
 }  // namespace topk
 
 __device__ __forceinline__ uint32_t float_to_key(float f) {
@@ -40,7 +41,11 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 // Dynamic shared memory: max(kpow2 * 8 (sort buffer), kWarps * 256 * 4 (per-warp first-digit histograms, used before the
 // sort buffer)) + max(n * 4 (keys), kpow2 * 8 + kWarps * 256 * 2 (second sort buffer + digit counters, used after the keys)).
 // kMaxRounds: 32-element rounds per warp in the sort, top_k <= kWarps * 32 * kMaxRounds.
-template <int kMaxRounds>
+// kStream: rows too long for shared memory (more than about 52 k candidates).  The keys are not kept: every pass -- the
+// first-digit histogram, the three further select passes, the two passes of the compaction -- converts the scores again
+// from global memory (six reads of a row that stays in L2 instead of one); the shared memory then holds the sort buffers
+// only.  Same results bit for bit.
+template <int kMaxRounds, bool kStream>
 __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_select_kernel(const float* __restrict__ scores, int64_t row_stride, int n,
                                                                      const int32_t* __restrict__ limits, int top_k, int kpow2,
                                                                      int32_t* __restrict__ out_idx, float* __restrict__ out_val, int ordered) {
@@ -61,6 +66,15 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
   int lim = limits ? limits[row] : n;
   lim = lim < 0 ? 0 : (lim > n ? n : lim);
   n = lim;  // entries at or beyond the limit are not candidates: none of the passes below looks at them
+  // key of candidate i (0 = not a candidate), from shared memory or again from the scores
+  auto key_at = [&](int i) -> uint32_t {
+    if constexpr (kStream) {
+      const float f = __ldg(x + i);
+      return f > -1e30f ? float_to_key(f) : 0u;
+    } else {
+      return keys[i];
+    }
+  };
 
   if (tid == 0) s_nvalid = 0;
   for (int i = tid; i < kWarps * 256; i += kThreads) whist[i] = 0;
@@ -71,7 +85,7 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
   auto take = [&](int i, float f) {
     uint32_t k = 0;
     if (i < lim && f > -1e30f) { k = float_to_key(f); ++my_valid; }
-    if (i < n) keys[i] = k;  // 0 marks "not a candidate" (a real key is never 0 for a score > -1e30)
+    if (!kStream && i < n) keys[i] = k;  // 0 marks "not a candidate" (a real key is never 0 for a score > -1e30)
     // sign + exponent bits crowd into a few bins: a private histogram per warp keeps the atomics apart
     if (k) atomicAdd(&whist[warp * 256 + (k >> 24)], 1u);
   };
@@ -127,7 +141,7 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
         const uint32_t pmask = 0xffffffffu << (shift + 8);
         for (int base = 0; base < n; base += kThreads) {
           const int i = base + tid;
-          const uint32_t k = i < n ? keys[i] : 0u;
+          const uint32_t k = i < n ? key_at(i) : 0u;
           if (k && (k & pmask) == prefix) atomicAdd(&hist[(k >> shift) & 0xffu], 1u);  // few survivors, spread digits
         }
         __syncthreads();
@@ -171,7 +185,7 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
     uint32_t n_gt = 0, n_eq = 0;
     for (int base = beg; base < end; base += 32) {
       const int i = base + lane;
-      const uint32_t k = i < end ? keys[i] : 0u;
+      const uint32_t k = i < end ? key_at(i) : 0u;
       n_gt += __popc(__ballot_sync(0xffffffffu, k != 0 && (take_all || k > thresh)));
       n_eq += __popc(__ballot_sync(0xffffffffu, !take_all && k != 0 && k == thresh));
     }
@@ -186,7 +200,7 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
     }
     for (int base = beg; base < end; base += 32) {
       const int i = base + lane;
-      const uint32_t k = i < end ? keys[i] : 0u;
+      const uint32_t k = i < end ? key_at(i) : 0u;
       const bool gt = k != 0 && (take_all || k > thresh);
       const bool eq = !take_all && k != 0 && k == thresh;
       const uint32_t bal_eq = __ballot_sync(0xffffffffu, eq);
@@ -320,6 +334,7 @@ __global__ void __launch_bounds__(topk::kThreads, kMaxRounds <= 4 ? 4 : 1) topk_
   }
 }
 
+// Shared memory of the kernel that keeps a row's keys (n > 0) or of the streaming kernel (n = 0).
 size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
   int kp = 32;  // buffer length: top_k rounded up to a multiple of 32 (name kept from the power-of-two days of a bitonic sort)
   while (kp < top_k) kp += 32;
@@ -333,10 +348,12 @@ size_t topk_smem_bytes(int n, int top_k, int* kpow2_out) {
 int launch_topk_select(const float* scores, int64_t rows, int n, int64_t row_stride, const int32_t* limits, int top_k,
                        int32_t* out_idx, float* out_val, cudaStream_t stream, int ordered) {
   int kp = 0;
-  const size_t smem = topk_smem_bytes(n, top_k, &kp);
+  const bool stream_rows = topk_smem_bytes(n, top_k, nullptr) > topk::kMaxSmemBytes;
+  const size_t smem = topk_smem_bytes(stream_rows ? 0 : n, top_k, &kp);
   if (top_k > topk::kWarps * 32 * 16) return static_cast<int>(cudaErrorInvalidValue);
   const bool small = top_k <= topk::kWarps * 32 * 4;
-  auto kern = small ? topk_select_kernel<4> : topk_select_kernel<16>;
+  auto kern = stream_rows ? (small ? topk_select_kernel<4, true> : topk_select_kernel<16, true>)
+                          : (small ? topk_select_kernel<4, false> : topk_select_kernel<16, false>);
   int dev = 0, sms = 0;
   cudaError_t e = current_device_sms(&dev, &sms);
   if (e != cudaSuccess) return static_cast<int>(e);
