@@ -39,6 +39,28 @@ DRAM_CAPTURE = {"read": 96943360, "write": 38995200, "queries": 592,
 CPU_SAMPLE_BLOCKS, CPU_SAMPLE_BLOCK = 16, 16   # the CPU arm's step: 16 evenly spaced blocks of 16 queries of the workload
 
 
+_RESULT_FD = None
+
+
+def claim_stdout() -> None:
+    """Keeps the process's standard output for the one result line: everything else that writes to it -- Python prints, and
+    libraries that print from C (NCCL's version banner) -- goes to standard error from here on."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj) -> None:
+    data = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def valid_pairs(S: int, S_kv: int, topk: int, lo: int = 0, hi: int | None = None) -> int:
     p = np.arange(S, dtype=np.int64) + (S_kv - S) + 1
     return int(np.minimum(p, topk)[lo:hi].sum())
@@ -492,7 +514,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------- multi-GPU extras
@@ -582,6 +604,7 @@ def main() -> None:
                     help="profiling aid: run only the LAST n queries of the workload (a small case for ncu captures); "
                          "the printed line is then not a benchmark result")
     args = ap.parse_args()
+    claim_stdout()
     if args.queries:
         WORKLOAD["S"] = args.queries
     else:
@@ -610,15 +633,15 @@ def main() -> None:
     peaks = load_peaks()
     if args.stage == "hisa":
         if rank == 0:
-            print(json.dumps({"hisa_block_sparse_logits": measure_hisa(dev)}), flush=True)
+            emit({"hisa_block_sparse_logits": measure_hisa(dev)})
         return
     if args.stage == "v4":
         if rank == 0:
-            print(json.dumps({"sparse_flash_mla_v4": measure_v4(dev)}), flush=True)
+            emit({"sparse_flash_mla_v4": measure_v4(dev)})
         return
     if args.stage == "backward":
         if rank == 0:
-            print(json.dumps({"backward": measure_backward(dev, peaks, w["S"], reps=1, warm=1)}), flush=True)
+            emit({"backward": measure_backward(dev, peaks, w["S"], reps=1, warm=1)})
         return
     if args.stage == "decode":
         if rank == 0:
@@ -626,11 +649,11 @@ def main() -> None:
             Bd = args.queries or 64
             qd, kvd, idxd = decode_inputs(dev, Bd, g)
             t = _time_ms(lambda: dsa.sparse_mla_fwd_raw(qd, kvd, idxd, sm_scale=576 ** -0.5, q_start=0, causal=False, dv=512), reps=2, warm=1)
-            print(json.dumps({"decode_eager": {"us": t * 1e3, "sequences": Bd, "algorithmic_bytes": decode_bytes(Bd)}}), flush=True)
+            emit({"decode_eager": {"us": t * 1e3, "sequences": Bd, "algorithmic_bytes": decode_bytes(Bd)}})
         return
     if args.stage == "others":
         if rank == 0:
-            print(json.dumps({"other_stages": measure_other_stages(dev, peaks, small=bool(args.queries))}), flush=True)
+            emit({"other_stages": measure_other_stages(dev, peaks, small=bool(args.queries))})
         return
 
     # every rank builds the same tensors (same seed, same generator, same GPU model) and keeps its block of the queries
@@ -783,7 +806,7 @@ def main() -> None:
                                 "sample": cpu_sample_text(len(rows), len(starts), kind) + f", {sec:.1f} s"}
         line["parity_sample"] = par
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

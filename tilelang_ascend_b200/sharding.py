@@ -16,9 +16,11 @@ def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
 
 
 # Cost of one query of the causal prefill forward in key tiles: the tiles of 64 keys it gathers plus a fixed part (loading
-# its 128 x 576 Q block, draining and storing its 128 x 512 output) worth about two tiles.
+# its 128 x 576 Q block, draining and storing its 128 x 512 output, the hand-over between two queries) worth about three
+# tiles -- fitted to the per-rank times of a 4-GPU run, where the rank with the many short queries was 4 % slower than
+# the others under a fixed part of two.
 KEYS_PER_TILE = 64
-FIXED_TILES_PER_QUERY = 2
+FIXED_TILES_PER_QUERY = 3
 
 
 def causal_query_costs(S: int, s_kv: int, topk: int):
