@@ -715,14 +715,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           tc_fence_after();
           if (go) tr(1, gg);
           const uint64_t db0 = make_smem_desc(stage, 16, 1024, kSwizzle128B);
-#pragma unroll
+          // (loops over the 64-dim chunks left rolled: the issue rate does not need the unrolling and the smaller loop
+          // body measurably helps the other roles that share the SM's instruction caches)
+#pragma unroll 1
           for (int c = 0; c < 6; ++c) {
 #pragma unroll
             for (int kq = 0; kq < 4; ++kq)
               umma_pair_ts_if(go, tS + sb * 32, tQ + (c * 4 + kq) * 8, db0 + ((c * kChunk + kq * 32) >> 4), idesc_qk, (c | kq) != 0);
           }
           const uint64_t da0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
-#pragma unroll
+#pragma unroll 1
           for (int c = 0; c < kQSmemChunks; ++c) {
 #pragma unroll
             for (int kq = 0; kq < 4; ++kq)
