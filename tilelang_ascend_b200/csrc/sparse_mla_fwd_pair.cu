@@ -162,7 +162,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   // k-th work unit of this cluster (late queries first), or negative; unit = (query, head block) * nsplit + share
   auto item_of = [&](int k) { return num_items - 1 - cluster_id - k * num_clusters; };
 #ifdef DSA_TRACE
-  auto tr = [&](int ev, int g) { if (cluster_id == 0 && g < 64 && p.trace) p.trace[(rank * 24 + ev) * 64 + g] = clock64(); };
+#ifndef DSA_TRACE_MASK
+#define DSA_TRACE_MASK 0xffffffu   // which events are compiled in: every sample point slows its role, a build with few is closer to the product
+#endif
+  auto tr = [&](int ev, int g) {
+    if (((DSA_TRACE_MASK >> ev) & 1u) && cluster_id == 0 && g < 64 && p.trace) p.trace[(rank * 24 + ev) * 64 + g] = clock64();
+  };
 #else
   auto tr = [&](int, int) {};
 #endif
