@@ -16,8 +16,11 @@ pytestmark = pytest.mark.gpu
     (33, 1000, 64, 128, 64, 12, torch.bfloat16, torch.float32),    # S_kv not a multiple of the block: the last block is cut
     (5, 300, 7, 64, 48, 4, torch.bfloat16, torch.bfloat16),        # block size that is not a multiple of 32, odd head count
 ])
-def test_block_sparse_logits_match_oracle(S, S_kv, H, D, bs, topk, dtype, wdtype):
+@pytest.mark.parametrize("loader", ["tma", "cp_async"])
+def test_block_sparse_logits_match_oracle(S, S_kv, H, D, bs, topk, dtype, wdtype, loader, monkeypatch):
     import tilelang_ascend_b200 as dsa
+    # the tensor-core kernel fetches a block with two TMA tile loads; DSA_HISA_NO_TMA=1 selects its cp.async loaders
+    monkeypatch.setenv("DSA_HISA_NO_TMA", "1" if loader == "cp_async" else "0")
     g = torch.Generator().manual_seed(S)
     q = (torch.rand((S, H, D), generator=g) - 0.5).to(dtype)
     k = (torch.rand((S_kv, D), generator=g) - 0.5).to(dtype)
@@ -25,6 +28,7 @@ def test_block_sparse_logits_match_oracle(S, S_kv, H, D, bs, topk, dtype, wdtype
     ks = torch.randint(0, S_kv // 8, (S,), generator=g, dtype=torch.int32)
     ke = (torch.arange(1, S + 1, dtype=torch.int32) * (S_kv // S)).clamp(max=S_kv)
     blk = torch.randint(0, (S_kv + bs - 1) // bs, (S, topk), generator=g, dtype=torch.int32)
+    blk[0, 0] = -1                                    # an empty slot: the block is not fetched, all its logits are -inf
     kernel = dsa.block_sparse_mqa_attn_return_logits(S, S_kv, bs, topk, H, D, block_N=8 if bs % 8 == 0 else 1)
     out = kernel(q.cuda(), k.cuda(), blk.cuda(), w.cuda(), ks.cuda(), ke.cuda()).cpu()
     check_status()

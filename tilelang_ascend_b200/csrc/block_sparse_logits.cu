@@ -117,11 +117,16 @@ int launch_block_sparse_logits(const BlockSparseLogitsParams& p, bool bf16, cuda
 // tcgen05 kernel: blocks of 128 keys, index_dim 128, up to 64 heads
 // -------------------------------------------------------------------------------------------------
 // One CTA per query (two resident per SM).  A selected block is one UMMA tile: A = its 128 keys x 128 dims (two
-// K-major chunks of 64 dims in the 128-byte swizzle, fetched row by row with cp.async into a 2-stage ring), B = the
+// K-major chunks of 64 dims in the 128-byte swizzle, fetched with two TMA tile loads per block -- a selected block is 128
+// consecutive rows of k -- into a 2-stage ring; row by row with cp.async when no tensor map can be made), B = the
 // query's heads x 128 dims (loaded once, rows beyond the head count are zero), D = 128 keys x 64 heads fp32 in one of two
 // tensor-memory buffers.  The epilogue thread of a key reads its 64 head scores, applies ReLU and the head weights and
 // writes one logit; a warp writes 32 consecutive logits.
+#include <stdlib.h>
+#include <string.h>
+
 #include "ptx.cuh"
+#include "tensor_map.h"
 
 namespace dsa {
 namespace bsltc {
@@ -136,7 +141,8 @@ static_assert(2 * kSmemBytes <= 232448 - 2048, "two CTAs per SM");
 }  // namespace bsltc
 
 template <bool kBF16>
-__global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_kernel(const BlockSparseLogitsParams p) {
+__global__ void __launch_bounds__(bsltc::kThreads, 2)
+    block_sparse_logits_tc_kernel(const __grid_constant__ BlockSparseLogitsParams p, const __grid_constant__ CUtensorMap kmap, const int use_tma) {
   using namespace bsltc;
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   extern __shared__ uint8_t smem_raw[];
@@ -157,7 +163,7 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
   __syncthreads();
   if (s_start_status != kStatusOk) return;
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 128); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], use_tma ? 1 : 128); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&d_full[i], 1); mbar_init(&d_free[i], 4); }
     mbar_init(q_ready, 128);
     mbar_init_fence();
@@ -198,6 +204,35 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
       fence_proxy_async_smem();
       mbar_arrive(q_ready);
     }
+    if (use_tma) {
+      // One thread: a block of which at least one logit is kept is fetched whole with two tile loads (rows outside [ks, ke)
+      // or beyond the key tensor -- which read as zeros -- only produce logits that the epilogue replaces by -inf); a block
+      // of which nothing is kept is not fetched at all (its stage holds stale data, all its logits are -inf).
+      if (r == 0) {
+        prefetch_tensormap(&kmap);
+        for (int j = 0; j < p.topk; ++j) {
+          const int s = j % kStages;
+          const int blk = blocks[j];
+          const int64_t first = static_cast<int64_t>(blk) * kKeys;
+          bool fetch = blk >= 0 && (p.block_table ? blk < p.max_blocks : first < p.S_kv) && first + kKeys > lo && first < hi;
+          int64_t row0 = first;
+          if (fetch && p.block_table) {
+            const int phys = p.block_table[static_cast<int64_t>(qi / p.tokens_per_seq) * p.max_blocks + blk];
+            fetch = phys >= 0 && (static_cast<int64_t>(phys) + 1) * kKeys <= p.S_kv;
+            row0 = static_cast<int64_t>(phys) * kKeys;
+          }
+          if (j >= kStages && !mbar_wait(&empty[s], ((j / kStages) + 1) & 1, p.status)) { ok = false; break; }
+          if (fetch) {
+            const uint32_t stage = sBase + s * kStageBytes, fb = smem_u32(&full[s]);
+            mbar_arrive_expect_tx(&full[s], kStageBytes);
+            tma_load_2d(stage, &kmap, fb, 0, static_cast<int>(row0));
+            tma_load_2d(stage + kChunk, &kmap, fb, 64, static_cast<int>(row0));
+          } else {
+            mbar_arrive(&full[s]);
+          }
+        }
+      }
+    } else {
     for (int j = 0; j < p.topk && ok; ++j) {
       const int s = j % kStages;
       const int blk = blocks[j];
@@ -230,27 +265,30 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2) block_sparse_logits_tc_ker
       fence_proxy_async_smem();
       mbar_arrive(&full[(p.topk - 1) % kStages]);
     }
+    }
   } else if (warp == 8) {
     // ================================ MMA issuer ====================================================
-    if (lane == 0) {
+    // the whole warp walks the loop and waits, converged; one elected lane issues through predicated instructions
+    {
       // UMMA N = the head count rounded up to 16 (rows of the B image beyond the head count are zero)
       const uint32_t idesc = make_idesc_f16(kBF16, kKeys, static_cast<uint32_t>((p.H + 15) & ~15), 0, 0);
-      ok = mbar_wait(q_ready, 0, p.status);
+      const uint32_t go = elect_one_lane();
+      ok = __all_sync(0xffffffffu, mbar_wait(q_ready, 0, p.status));
       const uint64_t db0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
       for (int j = 0; j < p.topk && ok; ++j) {
         const int s = j % kStages, db = j & 1;
-        if (!mbar_wait(&full[s], (j / kStages) & 1, p.status)) { ok = false; break; }
-        if (j >= 2 && !mbar_wait(&d_free[db], ((j >> 1) + 1) & 1, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], (j / kStages) & 1, p.status))) { ok = false; break; }
+        if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&d_free[db], ((j >> 1) + 1) & 1, p.status))) { ok = false; break; }
         tc_fence_after();
         const uint64_t da0 = make_smem_desc(sBase + s * kStageBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int kq = 0; kq < 4; ++kq)
-            umma_ss(tD + db * kHeads, da0 + ((c * kChunk + kq * 32) >> 4), db0 + ((c * (kHeads * 128) + kq * 32) >> 4), idesc, (c | kq) != 0);
+            umma_ss_if(go, tD + db * kHeads, da0 + ((c * kChunk + kq * 32) >> 4), db0 + ((c * (kHeads * 128) + kq * 32) >> 4), idesc, (c | kq) != 0);
         }
-        umma_commit(&d_full[db]);
-        umma_commit(&empty[s]);
+        umma_commit_if(go, &d_full[db]);
+        umma_commit_if(go, &empty[s]);
       }
     }
   } else {
@@ -297,7 +335,13 @@ int launch_block_sparse_logits_tc(const BlockSparseLogitsParams& p, bool bf16, c
   auto kern = bf16 ? block_sparse_logits_tc_kernel<true> : block_sparse_logits_tc_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bsltc::kSmemBytes));
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<static_cast<unsigned>(p.S), bsltc::kThreads, bsltc::kSmemBytes, stream>>>(p);
+  // k as a tensor map with a box of one block half (64 dims x 128 keys); DSA_HISA_NO_TMA=1 in the environment forces the
+  // cp.async loaders (used by the tests to cover that path)
+  alignas(64) CUtensorMap kmap;
+  memset(&kmap, 0, sizeof(kmap));
+  const char* no_tma = getenv("DSA_HISA_NO_TMA");
+  const int use_tma = (!(no_tma && no_tma[0] == '1') && encode_rows_map(p.k, p.S_kv, bsltc::kDim, bf16, bsltc::kKeys, &kmap)) ? 1 : 0;
+  kern<<<static_cast<unsigned>(p.S), bsltc::kThreads, bsltc::kSmemBytes, stream>>>(p, kmap, use_tma);
   return static_cast<int>(cudaGetLastError());
 }
 }  // namespace dsa

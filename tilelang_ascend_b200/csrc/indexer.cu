@@ -23,6 +23,7 @@
 #include "launch_util.h"
 #include "params.h"
 #include "ptx.cuh"
+#include "tensor_map.h"
 
 namespace dsa {
 
@@ -335,34 +336,13 @@ bool indexer_tc_supported(const IndexerParams& p) {
 }
 
 namespace {
-// cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link against the driver library.
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
-      ptr = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
 // k [B * S2, 128] as a tensor map with a box of 64 dims x 128 keys in the 128-byte swizzle; false when that is not
 // possible (then the kernel's cp.async producers fetch the tiles)
 bool make_k_map(const IndexerParams& p, bool bf16, CUtensorMap* map) {
-  EncodeTiledFn encode = encode_tiled_fn();
   // paged cache: all rows of the pool; a box must lie inside one block, so its row count has to divide the block size
   const long long rows = p.block_table ? static_cast<long long>(p.num_blocks) * p.block_size : static_cast<long long>(p.B) * p.S2;
-  if (!encode || (reinterpret_cast<uintptr_t>(p.k) & 15u) || rows <= 0 || rows > 0x7fffffffLL) return false;
   if (p.block_table && (p.box_rows < 8 || itc::kKeys % p.box_rows != 0 || p.block_size % p.box_rows != 0)) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(itc::kD), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(itc::kD) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(p.block_table ? p.box_rows : itc::kKeys)}, estr[2] = {1, 1};
-  return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(p.k), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_rows_map(p.k, rows, itc::kD, bf16, p.block_table ? p.box_rows : itc::kKeys, map);
 }
 }  // namespace
 

@@ -103,7 +103,10 @@ def sparse_flash_mla(
     if scenario == 2:
         # every compressed token below the threshold: the list is as wide as the longest sequence needs (the reference's
         # front door reads seqused_kv on the host for the same purpose, sparse_flash_mla_api.py:176-180)
-        K = max(-(-(int(seqused_kv.max().item()) // cmp_ratio) // 64) * 64, 64)
+        # A caller that knows an upper bound of the compressed tokens per sequence passes it as topk_cmp: no host read, and
+        # the call can then be captured in a CUDA graph (tokens beyond a sequence's own threshold are masked on the device).
+        longest = int(topk_cmp) if topk_cmp is not None else int(seqused_kv.max().item()) // cmp_ratio
+        K = max(-(-longest // 64) * 64, 64)
 
     def i32(t):
         return None if t is None else t.to(device=dev, dtype=torch.int32).contiguous()
