@@ -81,7 +81,7 @@ def workload_config(world: int) -> dict:
     w = WORKLOAD
     return {"workload": f"sparse_mla_fwd prefill B=1 S_q={w['S']} S_kv={w['S_kv']} H=128 D=576 dv=512 topk=2048 (DeepSeek-V3.2), "
                         "causal index lists, bf16 N(0,1), seed 1000",
-            "partition": f"the {w['S']} queries cut into {world} contiguous block(s) of equal cost (key tiles + a fixed part per query), "
+            "partition": f"the {w['S']} queries cut into {world} contiguous block(s) that take equal time in rounds of one query per SM pair (key tiles + a fixed part per query), "
                          "one per GPU; latent KV replicated; no collective in the timed region",
             "l2": "every rank's inputs and outputs of one step (1.18 GB / N, 148 MB at N=8) exceed the 126 MB L2; no extra flush"}
 
@@ -669,7 +669,9 @@ def main() -> None:
     # every rank builds the same tensors (same seed, same generator, same GPU model) and keeps its block of the queries
     q, kv, idx = make_inputs_cuda(1000, dev)
     costs = dsa.causal_query_costs(w["S"], w["S_kv"], w["topk"])
-    spans = [dsa.shard_range_balanced(costs, r, world) for r in range(world)]
+    # one (query, 128 heads) unit per SM pair and round: blocks are cut so that the slowest rank's rounds take least time
+    sm_pairs = max(1, torch.cuda.get_device_properties(dev).multi_processor_count // 2)
+    spans = dsa.shard_ranges_by_rounds(costs, world, sm_pairs)
     lo, hi = spans[rank]
     q_s, idx_s = (q, idx) if world == 1 else (q[:, lo:hi].contiguous(), idx[:, lo:hi].contiguous())
     q0 = (w["S_kv"] - w["S"]) + lo

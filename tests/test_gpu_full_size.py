@@ -202,17 +202,21 @@ def test_cost_balanced_query_shards_reassemble_bit_exactly(world):
     kernel = dsa.sparse_attention_fwd(H, 512, 64, topk, 1, return_softmax_lse=True)
     out, lse = kernel(q, kv, idx)
     costs = dsa.causal_query_costs(S, S_kv, topk)
-    outs, lses, loads, prev = [], [], [], 0
-    for r in range(world):
-        qs, ix, q0 = dsa.shard_queries(q, idx, r, world, s_kv=S_kv, balance=True)
-        s, e = dsa.shard_range_balanced(costs, r, world)
-        assert s == prev and q0 == s and qs.shape[1] == e - s
-        prev = e
-        loads.append(int(costs[s:e].sum()))
-        o, l = kernel(qs, kv, ix, q_start_index_s=q0)
-        outs.append(o)
-        lses.append(l)
-    check_status()
-    assert prev == S
-    assert max(loads) <= 1.01 * sum(loads) / world
-    assert torch.equal(torch.cat(outs, 1), out) and torch.equal(torch.cat(lses, 1), lse)
+    # the partition by summed cost, and the one the bench uses (equal time in rounds of one query per SM pair)
+    for pairs in (0, 74):
+        spans = dsa.shard_ranges_by_rounds(costs, world, pairs) if pairs else [dsa.shard_range_balanced(costs, r, world) for r in range(world)]
+        outs, lses, loads, prev = [], [], [], 0
+        for r in range(world):
+            qs, ix, q0 = dsa.shard_queries(q, idx, r, world, s_kv=S_kv, balance=True, units_per_round=pairs)
+            s, e = spans[r]
+            assert s == prev and q0 == s and qs.shape[1] == e - s
+            prev = e
+            loads.append(int(costs[s:e].sum()))
+            o, l = kernel(qs, kv, ix, q_start_index_s=q0)
+            outs.append(o)
+            lses.append(l)
+        check_status()
+        assert prev == S
+        if not pairs:
+            assert max(loads) <= 1.01 * sum(loads) / world
+        assert torch.equal(torch.cat(outs, 1), out) and torch.equal(torch.cat(lses, 1), lse)

@@ -95,3 +95,21 @@ def test_balanced_shards_cover_everything_once_and_equalise_cost():
     assert [dsa.shard_range_balanced([1.0] * 5, r, 5) for r in range(5)] == [(i, i + 1) for i in range(5)]
     with pytest.raises(ValueError):
         dsa.shard_range_balanced(costs, 3, 2)
+
+
+def test_partition_by_rounds_beats_the_cost_sum_partition_and_covers_everything():
+    """Blocks cut for a kernel that walks its items in rounds of one per SM pair: contiguous, complete, never slower (in
+    the round model) than the partition by summed cost, and better where the latter leaves a rank with a partial round."""
+    import tilelang_ascend_b200 as dsa
+    costs = dsa.causal_query_costs(4096, 4096, 2048)
+    for world in (1, 2, 3, 4, 8):
+        spans = dsa.shard_ranges_by_rounds(costs, world, 74)
+        assert spans[0][0] == 0 and spans[-1][1] == 4096 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        t_new = max(dsa.block_time_in_rounds(costs, s, e, 74) for s, e in spans)
+        t_sum = max(dsa.block_time_in_rounds(costs, *dsa.shard_range_balanced(costs, r, world), 74) for r in range(world))
+        assert t_new <= t_sum
+    spans = dsa.shard_ranges_by_rounds(costs, 4, 74)
+    assert max(dsa.block_time_in_rounds(costs, s, e, 74) for s, e in spans) < \
+        max(dsa.block_time_in_rounds(costs, *dsa.shard_range_balanced(costs, r, 4), 74) for r in range(4))
+    assert dsa.shard_ranges_by_rounds([], 2, 74) == [(0, 0), (0, 0)]
+    assert dsa.shard_ranges_by_rounds([5, 5, 5], 5, 2) [:2] == [(0, 2), (2, 3)] or sum(e - s for s, e in dsa.shard_ranges_by_rounds([5, 5, 5], 5, 2)) == 3

@@ -51,13 +51,70 @@ def shard_range_balanced(costs, rank: int, world: int) -> Tuple[int, int]:
     return bounds[rank], bounds[rank + 1]
 
 
-def shard_queries(q, indices, rank: int, world: int, s_kv: int, balance: bool = False):
+def block_time_in_rounds(costs, start: int, end: int, units_per_round: int) -> int:
+    """Time (in the unit of ``costs``) a persistent kernel needs for items [start, end) when it walks them from the last
+    item backwards in rounds of ``units_per_round`` (one item per SM pair and round; every round lasts as long as its most
+    expensive item): the sum over rounds of the largest cost in the round."""
+    import numpy as np
+    c = np.asarray(costs)
+    t = 0
+    for hi in range(end, start, -units_per_round):
+        t += int(c[max(start, hi - units_per_round):hi].max())
+    return t
+
+
+def shard_ranges_by_rounds(costs, world: int, units_per_round: int):
+    """Contiguous [start, end) blocks of ``len(costs)`` items for all ``world`` ranks that minimise the slowest rank's
+    :func:`block_time_in_rounds`.  Cutting by the plain sum of costs ignores that a GPU works in rounds of
+    ``units_per_round`` items: a block of 5.4 rounds takes as long as one of 6, which at 8 GPUs (about 400 long queries per
+    rank on 74 SM pairs) is a tenth of the step.  Found by bisection on the time limit, each rank taking as many items as
+    fit (the time of a block is non-decreasing in its end)."""
+    import numpy as np
+    c = np.asarray(costs, dtype=np.int64)
+    n = int(c.shape[0])
+    if world <= 0:
+        raise ValueError(f"bad world {world}")
+    if n == 0:
+        return [(0, 0)] * world
+
+    def cut(limit: int):
+        spans, s = [], 0
+        for _ in range(world):
+            # largest e with time(s, e) <= limit: grow in whole rounds first, then item by item
+            e = s
+            while e < n and block_time_in_rounds(c, s, min(n, e + units_per_round), units_per_round) <= limit:
+                e = min(n, e + units_per_round)
+            lo, hi = e, min(n, e + units_per_round)
+            while lo < hi:  # binary search inside the last partial round
+                mid = (lo + hi + 1) // 2
+                if block_time_in_rounds(c, s, mid, units_per_round) <= limit:
+                    lo = mid
+                else:
+                    hi = mid - 1
+            spans.append((s, lo))
+            s = lo
+        return spans if s == n else None
+
+    lo_t, hi_t = 1, block_time_in_rounds(c, 0, n, units_per_round)
+    while lo_t < hi_t:
+        mid = (lo_t + hi_t) // 2
+        if cut(mid) is not None:
+            hi_t = mid
+        else:
+            lo_t = mid + 1
+    return cut(lo_t)
+
+
+def shard_queries(q, indices, rank: int, world: int, s_kv: int, balance: bool = False, units_per_round: int = 0):
     """Query block of this rank for a BSND prefill call: (q_shard, indices_shard, q_start_index_s).
 
     The causal position of local query t is ``q_start_index_s + t`` with ``q_start_index_s = (s_kv - S) + start``.
-    ``balance``: cut by the cost model of :func:`causal_query_costs` instead of by query count."""
+    ``balance``: cut by the cost model of :func:`causal_query_costs` instead of by query count; with ``units_per_round``
+    (the GPU's SM pairs: one (query, 128 heads) unit per pair and round) by :func:`shard_ranges_by_rounds`."""
     S = q.shape[1]
-    if balance:
+    if balance and units_per_round > 0:
+        s, e = shard_ranges_by_rounds(causal_query_costs(S, s_kv, indices.shape[-1]), world, units_per_round)[rank]
+    elif balance:
         s, e = shard_range_balanced(causal_query_costs(S, s_kv, indices.shape[-1]), rank, world)
     else:
         s, e = shard_range(S, rank, world)
