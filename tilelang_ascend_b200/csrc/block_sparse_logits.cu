@@ -315,9 +315,17 @@ __global__ void __launch_bounds__(bsltc::kThreads, 2)
       __syncwarp();
       if (lane == 0) mbar_arrive(&d_free[db]);
       float total = 0.f;
+      const float4* sw4 = reinterpret_cast<const float4*>(sw);   // four weights per (broadcast) load
 #pragma unroll
-      for (int h = 0; h < kHeads; ++h)   // columns at or beyond the head count hold stale tensor memory (or were not loaded): skipped
-        if (h < p.H) total += sw[h] * fmaxf(__uint_as_float(v[h]), 0.f);
+      for (int h4 = 0; h4 < kHeads / 4; ++h4) {   // columns at or beyond the head count hold stale tensor memory (or were not loaded): skipped
+        if (4 * h4 < p.H) {
+          const float4 wv = sw4[h4];
+          total += wv.x * fmaxf(__uint_as_float(v[4 * h4]), 0.f);
+          if (4 * h4 + 1 < p.H) total += wv.y * fmaxf(__uint_as_float(v[4 * h4 + 1]), 0.f);
+          if (4 * h4 + 2 < p.H) total += wv.z * fmaxf(__uint_as_float(v[4 * h4 + 2]), 0.f);
+          if (4 * h4 + 3 < p.H) total += wv.w * fmaxf(__uint_as_float(v[4 * h4 + 3]), 0.f);
+        }
+      }
       p.logits[(static_cast<int64_t>(qi) * p.topk + j) * kKeys + r] = valid ? total : -INFINITY;
     }
   }
