@@ -327,7 +327,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         const uint32_t prow = sBase + kOffP + sb * kPBytes;
         st_shared_v4(prow + sw128_offset(m, 4 * kh + 2 * ch), pk[0], pk[1], pk[2], pk[3]);
         st_shared_v4(prow + sw128_offset(m, 4 * kh + 2 * ch + 1), pk[4], pk[5], pk[6], pk[7]);
-        fence_proxy_async_smem();  // read by the tensor cores (async proxy)
+        // (No proxy fence here: the P V issuers -- and in the odd CTA the thread that forwards this barrier -- execute it after
+        // they have seen the barrier, as the Q K^T issuers do for the gathered rows.  A fence issued from these warps waits
+        // behind the tensor-core work queued on this SM: 800 clocks per tile in the even CTA, measured.)
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarPReady + sb));
         if (tid == 0) tr(4, g);
