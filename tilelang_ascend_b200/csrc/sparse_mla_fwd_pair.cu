@@ -847,7 +847,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
             const int pb = g & 1;
             if (!mbar_wait(bar(kBarPReady + pb), (g >> 1) & 1, p.status)) { ok = false; break; }
             tr(14, g);
-            fence_proxy_async_smem();  // (the writers fenced their own stores; this orders the hand-over)
+            fence_proxy_async_smem();  // the P stores of this CTA's softmax warps (generic proxy) are read by the tensor cores
             mbar_arrive_cluster_relaxed(target + (kBarPeerPReady + pb) * 8);
             tr(15, g);
           }
