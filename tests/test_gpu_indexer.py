@@ -257,3 +257,37 @@ def test_reference_layout_scenarios():
     ip[0, :96], ip[1] = idx[:96], idx[96:]
     check(ip, qp, k, wp, act_q, act_k, K, 0)
     check_status()
+
+
+@pytest.mark.parametrize("B,S1,S2,K,mode", [(2, 50, 300, 64, 3), (1, 33, 200, 16, 0), (1, 64, 64, 32, 3)])
+def test_fused_call_over_query_blocks_gives_the_same_arrays(B, S1, S2, K, mode):
+    """A fused scores + top-k call whose score matrix exceeds the workspace limit runs over blocks of queries, each with the
+    lengths that keep its queries' causal limits: index and value arrays equal the one-piece call's bit for bit."""
+    import tilelang_ascend_b200 as dsa
+    q, k, w = orc.make_indexer_inputs(B, S1, S2, seed=S1)
+    whole_i, whole_v = dsa.lightning_indexer_raw(q.cuda(), k.cuda(), w.cuda(), sparse_count=K, sparse_mode=mode, return_value=True)
+    for limit in (B * S2 * 4 * 7, B * S2 * 4):            # blocks of 7 queries / of a single query
+        part_i, part_v = dsa.lightning_indexer_raw(q.cuda(), k.cuda(), w.cuda(), sparse_count=K, sparse_mode=mode, return_value=True,
+                                                   max_workspace_bytes=limit)
+        check_status()
+        assert torch.equal(part_i, whole_i) and torch.equal(part_v, whole_v)
+
+
+def test_long_key_cache_131072_keys():
+    """The token-level indexer at the key count of HISA's default shape: 131072 keys per row do not fit the selector's shared
+    memory (rows are streamed) and 256 x 131072 scores are 128 MB; sampled rows against the CPU oracle (index sets; the scores
+    of the kept keys to rtol 2e-5)."""
+    import tilelang_ascend_b200 as dsa
+    B, S1, S2, K = 1, 256, 131072, 2048
+    q, k, w = orc.make_indexer_inputs(B, S1, S2, seed=77)
+    idx, val = dsa.lightning_indexer_raw(q.cuda(), k.cuda(), w.cuda(), sparse_count=K, sparse_mode=3, return_value=True,
+                                         max_workspace_bytes=64 << 20)   # forces two blocks of queries
+    check_status()
+    idx, val = idx.cpu(), val.cpu()
+    for t in (0, 100, 255):
+        sc = orc.indexer_scores(q[:, t:t + 1], k, w[:, t:t + 1])[0, 0]               # [S2] fp32 of this query
+        lim = S2 - S1 + t + 1
+        ref_i, ref_v = orc.topk_select(sc[None, :].numpy(), K, limits=np.array([lim], dtype=np.int32), return_values=True)
+        got = idx[0, t, 0].numpy()
+        assert set(got.tolist()) == set(ref_i[0].tolist())
+        np.testing.assert_allclose(val[0, t, 0].numpy(), ref_v[0], rtol=2e-5, atol=2e-4)

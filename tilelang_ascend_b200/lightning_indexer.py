@@ -37,10 +37,19 @@ def indexer_scores_raw(query, key, weights, *, sparse_mode: int = 3, q_len_b=Non
     return (scores, limits) if return_limits else scores
 
 
+# Largest score workspace (B * S1 * S2 fp32) a fused call allocates at once; calls that need more are run over blocks of
+# queries (4096 queries against 131072 keys would otherwise materialise 2 GB of scores).
+MAX_WORKSPACE_BYTES = 1 << 30
+
+
 def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode: int, q_len_b=None, k_len_b=None,
                           return_value: bool = False, workspace: Optional[torch.Tensor] = None, block_table=None,
-                          max_keys: Optional[int] = None, ordered: bool = True):
+                          max_keys: Optional[int] = None, ordered: bool = True, max_workspace_bytes: Optional[int] = None):
     """Fused scores + top-k of BSND inputs: indices int32 [B,S1,1,K] (+ fp32 values).
+
+    A call whose score matrix would exceed ``max_workspace_bytes`` (default MAX_WORKSPACE_BYTES) runs over blocks of
+    queries, each with the per-sequence lengths that give its queries the causal limits they have in the whole call
+    (dense keys, no caller-owned workspace or lengths, at least as many keys as queries); results are identical.
 
     ``ordered=False`` leaves the selector's final sort out: the same index SETS, in ascending index order (enough for the
     sparse attention that consumes them, which does not depend on the order of a query's list).
@@ -67,6 +76,23 @@ def lightning_indexer_raw(query, key, weights, *, sparse_count: int, sparse_mode
         raise ValueError(f"shape mismatch: query {tuple(query.shape)}, weights {tuple(weights.shape)}")
     lib = _lib.load()
     need = lib.dsa_lightning_indexer_workspace_bytes(B, S1, S2)
+    limit = MAX_WORKSPACE_BYTES if max_workspace_bytes is None else int(max_workspace_bytes)
+    if (need > limit and S1 > 1 and workspace is None and block_table is None and q_len_b is None and k_len_b is None and S2 >= S1):
+        rows = max(1, min(S1 - 1, limit // max(1, B * S2 * 4)))
+        idx = torch.empty((B, S1, 1, sparse_count), dtype=torch.int32, device=dev)
+        val = torch.empty((B, S1, 1, sparse_count), dtype=torch.float32, device=dev) if return_value else None
+        for s0 in range(0, S1, rows):
+            e0 = min(S1, s0 + rows)
+            # queries [s0, e0) of S1 against S2 keys have the limits of e0 - s0 queries against S2 - (S1 - e0) keys
+            ql = torch.full((B,), e0 - s0, dtype=torch.int32, device=dev)
+            kl = torch.full((B,), S2 - (S1 - e0) if sparse_mode == 3 else S2, dtype=torch.int32, device=dev)
+            i_c, v_c = lightning_indexer_raw(query[:, s0:e0].contiguous(), key, weights[:, s0:e0].contiguous(), sparse_count=sparse_count,
+                                             sparse_mode=sparse_mode, q_len_b=ql, k_len_b=kl, return_value=return_value, ordered=ordered,
+                                             max_workspace_bytes=1 << 62)
+            idx[:, s0:e0] = i_c
+            if return_value:
+                val[:, s0:e0] = v_c
+        return idx, val
     if workspace is None:
         workspace = torch.empty((need,), dtype=torch.uint8, device=dev)
     elif workspace.numel() * workspace.element_size() < need or workspace.device != dev:
