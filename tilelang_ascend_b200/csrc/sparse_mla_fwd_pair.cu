@@ -115,11 +115,6 @@ __device__ __forceinline__ void arrive_at(uint32_t local_addr, uint32_t target, 
     mbar_arrive_cluster_relaxed(map_to_cta(local_addr, target));
   }
 }
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
 __device__ __forceinline__ void st_async_v4_b32(uint32_t cluster_addr, uint32_t cluster_mbar, uint4 v) {
   asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr), "r"(v.x),
                "r"(v.y), "r"(v.z), "r"(v.w), "r"(cluster_mbar)
