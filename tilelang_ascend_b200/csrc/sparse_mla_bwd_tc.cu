@@ -653,25 +653,26 @@ __global__ void __launch_bounds__(bwdtc::dkv::kThreadsDkv, 1) sparse_mla_bwd_dkv
     }
   } else if (warp < kEpilogueWarps) {
     // ================================ operand columns + epilogue ====================================
-    // thread r of the first four warps copies head row r's 192 Q dims and its dO dims into the [128 heads x 128 B] chunk
+    // the first four warps copy the 128 head rows' 192 Q dims and dO dims into the [128 heads x 128 B] chunk
     // images.  Then thread (r, half) owns key r of every pair: tensor-memory lane r holds that key's 192 gradient values,
     // of which this thread takes columns [96 half, 96 half + 96).
     const int q4 = warp & 3, half = warp >> 2;
-    const int r = q4 * 32 + lane, h = h0 + r;
+    const int r = q4 * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     if (half == 0) {
-      const bool row_ok = h < p.H;
-      const int64_t hrow = static_cast<int64_t>(bt) * p.H + (row_ok ? h : 0);
-      const uint8_t* qrow = reinterpret_cast<const uint8_t*>(p.q) + hrow * (kD * 2) + part * (kDimsPerCta * 2);
-      const uint8_t* dorow = reinterpret_cast<const uint8_t*>(bp.d_out) + hrow * (kDV * 2) + part * (kDimsPerCta * 2);
-#pragma unroll
-      for (int c = 0; c < 3; ++c) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          cp_async16(sQ + c * kTileBytes + sw128_offset(r, u), qrow + c * 128 + u * 16, row_ok ? 16u : 0u);
-          // (the last CTA's third dO chunk would be dims 512 .. 575, which do not exist: zero fill)
-          cp_async16(sDO + c * kTileBytes + sw128_offset(r, u), c < do_chunks ? dorow + c * 128 + u * 16 : dorow, (row_ok && c < do_chunks) ? 16u : 0u);
-        }
+      // whole 128-byte lines: eight lanes copy one row's 64 dims of a chunk, a warp instruction covers four rows (a row per
+      // lane would make every instruction touch 32 rows)
+      const int nrows = p.H - h0 < kM ? p.H - h0 : kM;
+      const uint8_t* qbase = reinterpret_cast<const uint8_t*>(p.q) + (static_cast<int64_t>(bt) * p.H + h0) * (kD * 2) + part * (kDimsPerCta * 2);
+      const uint8_t* dobase = reinterpret_cast<const uint8_t*>(bp.d_out) + (static_cast<int64_t>(bt) * p.H + h0) * (kDV * 2) + part * (kDimsPerCta * 2);
+#pragma unroll 4
+      for (int i = r; i < 3 * 1024; i += 128) {
+        const int u = i & 7, row = (i >> 3) & 127, c = i >> 10;
+        const bool row_ok = row < nrows;
+        cp_async16(sQ + c * kTileBytes + sw128_offset(row, u), row_ok ? qbase + static_cast<int64_t>(row) * (kD * 2) + c * 128 + u * 16 : qbase, row_ok ? 16u : 0u);
+        // (the last CTA's third dO chunk would be dims 512 .. 575, which do not exist: zero fill)
+        const bool do_ok = row_ok && c < do_chunks;
+        cp_async16(sDO + c * kTileBytes + sw128_offset(row, u), do_ok ? dobase + static_cast<int64_t>(row) * (kDV * 2) + c * 128 + u * 16 : dobase, do_ok ? 16u : 0u);
       }
       cp_async_commit();
       cp_async_wait<0>();
