@@ -34,7 +34,7 @@ FLOP_PER_PAIR_HEAD = 2 * 576 + 2 * 512  # QK^T over 576 dims + PV over 512 dims
 METRIC, UNIT = "dsa_prefill_tokens_per_s", "tokens/s"
 # DRAM bytes per query of the forward kernel, from the ncu capture summarised in profiles/ (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch divided by its queries); re-derived whenever the kernel changes
-DRAM_CAPTURE = {"read": 96943360, "write": 38995200, "queries": 592,
+DRAM_CAPTURE = {"read": 96940032, "write": 39233536, "queries": 592,
                 "summary": "profiles/sparse_mla_fwd_pair_kernel__prefill_592q.md"}
 CPU_SAMPLE_BLOCKS, CPU_SAMPLE_BLOCK = 16, 16   # the CPU arm's step: 16 evenly spaced blocks of 16 queries of the workload
 
