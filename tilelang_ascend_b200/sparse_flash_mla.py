@@ -32,6 +32,17 @@ def sink_combine_raw(out_a, lse_a, out_b, lse_b, sinks, H: int):
     return out, lse
 
 
+_CONCURRENT_MAX_TOKENS = 64     # calls of at most this many query tokens run their two attention parts side by side
+_SIDE_STREAMS = {}
+
+
+def _side_stream(dev):
+    key = (dev.type, dev.index)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=dev)
+    return _SIDE_STREAMS[key]
+
+
 def sparse_flash_mla(
     q: torch.Tensor,
     *,
@@ -125,11 +136,25 @@ def sparse_flash_mla(
                                             current_stream(dev)))
     q4 = q_flat.reshape(1, T, N1, D)
     pool = ori_kv.reshape(1, ori_kv.shape[0] * ori_bs, 1, D)
-    out_a, lse_a = sparse_mla_fwd_raw(q4, pool, ori_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
     out_b = lse_b = None
+    side = None
     if scenario != 1:
         cpool = cmp_kv.reshape(1, cmp_kv.shape[0] * cmp_bs, 1, D)
-        out_b, lse_b = sparse_mla_fwd_raw(q4, cpool, cmp_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
+        if T <= _CONCURRENT_MAX_TOKENS:
+            # a decode-sized call: each of the two attention launches occupies a few SM pairs only, so the compressed-token
+            # part runs beside the window part on a second stream (forked from and joined to the caller's stream; inside a
+            # CUDA graph capture this becomes two parallel branches)
+            cur = torch.cuda.current_stream(dev)
+            side = _side_stream(dev)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                out_b, lse_b = sparse_mla_fwd_raw(q4, cpool, cmp_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
+    out_a, lse_a = sparse_mla_fwd_raw(q4, pool, ori_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
+    if scenario != 1:
+        if side is not None:
+            torch.cuda.current_stream(dev).wait_stream(side)
+        else:
+            out_b, lse_b = sparse_mla_fwd_raw(q4, cpool, cmp_rows, sm_scale=softmax_scale, q_start=0, causal=False, dv=D)
         out_b, lse_b = out_b.reshape(T, N1, D), lse_b.reshape(T, N1)
 
     out, lse = sink_combine_raw(out_a.reshape(T, N1, D), lse_a.reshape(T, N1), out_b, lse_b, sinks_dev, N1)
