@@ -288,6 +288,27 @@ def measure_v4(dev) -> dict:
     return res
 
 
+def measure_mla_decode(dev, peaks) -> dict:
+    """Dense MLA decode behind the reference's `mla_decode` factory on the largest shape of its layered test
+    (examples_experiment/deepseek_mla/example_mla_decode/test_mla_decode.py: B=132, 128 heads, 8192 keys, dim 512 + 64):
+    every key of every sequence is read once, kv and k_pe in place; timed as CUDA graph replays."""
+    import tilelang_ascend_b200 as dsa
+    g = torch.Generator(device=dev).manual_seed(17)
+    B, H, N, dim, pe = 132, 128, 8192, 512, 64
+    q = torch.randn((B, H, dim), generator=g, device=dev).to(torch.bfloat16)
+    q_pe = torch.randn((B, H, pe), generator=g, device=dev).to(torch.bfloat16)
+    kv = torch.randn((B, N, 1, dim), generator=g, device=dev).to(torch.bfloat16)
+    k_pe = torch.randn((B, N, 1, pe), generator=g, device=dev).to(torch.bfloat16)
+    kernel = dsa.mla_decode(B, H, 1, N, dim, pe)
+    t = _time_graph_ms(lambda: kernel(q, q_pe, kv, k_pe), calls=4, reps=5)
+    assert dsa.kernel_status() == 0
+    nbytes = B * (N * (dim + pe) * 2 + H * (dim + pe) * 2 + H * dim * 2)
+    flop = B * N * H * FLOP_PER_PAIR_HEAD
+    return {"us": t * 1e3, "algorithmic_gb_per_s": nbytes / (t * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (t * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "tflops": flop / (t * 1e-3) / 1e12, "frac_of_bf16_peak": flop / (t * 1e-3) / 1e12 / peaks["bf16_tflops"], "timing": "CUDA graph replay",
+            "workload": f"mla_decode B={B} heads={H} keys={N} dim={dim}+{pe}, bf16 (KV cache {B * N * (dim + pe) * 2 / 1e9:.2f} GB, read in place)"}
+
+
 def measure_hisa(dev) -> dict:
     """HISA block-sparse indexer logits on the default shape of the reference's test script
     (examples/HISA/block_sparse_mqa_attn_expert_test.py:670-680: 1024 queries, 128 K keys, 32 heads x 128 dims, 64 selected
@@ -373,6 +394,7 @@ def measure_other_stages(dev, peaks, small: bool = False) -> dict:
     assert dsa.kernel_status() == 0
     return {
         "backward": backward,
+        **({} if small else {"mla_decode": measure_mla_decode(dev, peaks)}),
         "pipeline": {"ms": t_pipe, "tokens_per_s": Sp / (t_pipe * 1e-3), "tflops": pipe_tflops, "frac_of_bf16_peak": pipe_tflops / peaks["bf16_tflops"],
                      "roofline": {"bound": "tensor", "achieved": pipe_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                   "frac": pipe_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
@@ -605,9 +627,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=16, help="query blocks of the host-buffer pipeline")
-    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "decode", "v4", "hisa"],
+    ap.add_argument("--stage", default="all", choices=["all", "prefill", "others", "backward", "decode", "mla", "v4", "hisa"],
                     help="'all' (default): the headline measurement plus the other stages of the path; profiling aids: 'prefill' "
-                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'decode' three eager decode steps of --queries sequences (default 64), 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
+                         "leaves the other stages out, 'others' runs only the indexer / top-k / decode / backward measurements, 'backward' only the backward (two calls), 'decode' three eager decode steps of --queries sequences (default 64), 'mla' the dense MLA decode factory on the reference test's largest shape, 'v4' the DeepSeek-V4 sparse_flash_mla front door on the reference's benchmark shapes, 'hisa' the block-sparse indexer logits")
     ap.add_argument("--cpu-sample", type=int, default=1, help="0 leaves the CPU baseline / parity sample out")
     ap.add_argument("--sustained-seconds", type=float, default=2.5, help="length of the back-to-back run behind `sustained` (0 leaves it out)")
     ap.add_argument("--queries", type=int, default=0,
@@ -644,6 +666,10 @@ def main() -> None:
     if args.stage == "hisa":
         if rank == 0:
             emit({"hisa_block_sparse_logits": measure_hisa(dev)})
+        return
+    if args.stage == "mla":
+        if rank == 0:
+            emit({"mla_decode": measure_mla_decode(dev, peaks)})
         return
     if args.stage == "v4":
         if rank == 0:

@@ -14,6 +14,8 @@ namespace dsa {
 // launchers defined in the kernel translation units
 bool sparse_mla_fwd_tc_supported(const FwdParams& p);
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream);
+bool sparse_mla_fwd_pair_supported(const FwdParams& p);
+int launch_sparse_mla_fwd_pair_combined(const FwdParams& p, bool bf16, cudaStream_t stream);
 int launch_sparse_mla_fwd_generic(const FwdParams& p, bool bf16, cudaStream_t stream);
 int sparse_mla_fwd_auto_nsplit(const FwdParams& p, int sms);
 size_t topk_smem_bytes(int n, int top_k, int* kpow2_out);
@@ -107,7 +109,7 @@ int fill_fwd_params(dsa::FwdParams* p, const void* q, const void* kv, const int3
   p->q_start_b = q_start_b; p->kv_len_b = kv_len_b; p->q_len_b = q_len_b;
   p->block_table = block_table; p->block_size = block_size; p->max_blocks = max_blocks;
   p->scale_log2 = sm_scale * 1.4426950408889634f;
-  p->nsplit = 1; p->part_out = nullptr; p->part_lse = nullptr;
+  p->nsplit = 1; p->part_out = nullptr; p->part_lse = nullptr; p->kv_rope = nullptr;
 #ifdef DSA_TRACE
   p->trace = g_trace;
 #endif
@@ -280,6 +282,33 @@ int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, vo
   int err = use_tc ? dsa::launch_sparse_mla_fwd_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream))
                    : dsa::launch_sparse_mla_fwd_generic(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("sparse_mla_fwd launch", err) : 0;
+}
+
+int dsa_sparse_mla_fwd_two_part(const void* q, const void* kv_latent, const void* kv_rope, const int32_t* indices, void* out, float* lse,
+                                int32_t B, int32_t S, int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale,
+                                int32_t q_start, int32_t causal, int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b,
+                                const int32_t* q_len_b, const int32_t* block_table, int32_t block_size, int32_t max_blocks, int32_t nsplit,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!kv_rope) return fail("null tensor pointer");
+  if (D != 576 || DV != 512) return fail("key rows in two parts need D = 576 and DV = 512");
+  if ((reinterpret_cast<uintptr_t>(kv_latent) | reinterpret_cast<uintptr_t>(kv_rope)) & 15u) return fail("key tensors must be 16-byte aligned");
+  dsa::FwdParams p;
+  if (fill_fwd_params(&p, q, kv_latent, indices, out, lse, B, S, S_kv, H, D, DV, topk, sm_scale, q_start, causal, dtype, q_start_b,
+                      kv_len_b, q_len_b, block_table, block_size, max_blocks))
+    return 1;
+  if (!dsa::sparse_mla_fwd_pair_supported(p)) return fail("key rows in two parts need topk <= 8192");
+  p.kv_rope = kv_rope;
+  if (nsplit < 1 || nsplit > 64) return fail("nsplit must be in [1, 64]");
+  if (nsplit > 1) {
+    const size_t need = dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, DV, nsplit);
+    if (!workspace || workspace_bytes < need) return fail("workspace too small (see dsa_sparse_mla_fwd_splitkv_workspace_bytes)");
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u) return fail("workspace must be 16-byte aligned");
+    p.nsplit = nsplit;
+    p.part_out = static_cast<float*>(workspace);
+    p.part_lse = p.part_out + static_cast<size_t>(nsplit) * B * S * H * DV;
+  }
+  int err = dsa::launch_sparse_mla_fwd_pair_combined(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sparse_mla_fwd_two_part launch", err) : 0;
 }
 
 int dsa_sparse_mla_fwd_splitkv_nsplit(int32_t B, int32_t S, int32_t H, int32_t topk) {

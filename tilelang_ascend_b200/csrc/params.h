@@ -32,6 +32,10 @@ struct FwdParams {
   int nsplit;
   float* part_out;
   float* part_lse;
+  // Key rows in two parts (SM-pair kernel, D = 576 / DV = 512 only): when kv_rope is set, kv holds rows of DV values (the
+  // latent part) and kv_rope rows of D - DV values (the rope part), both addressed by the same row number -- the layout of
+  // the dense MLA decode kernels' KV / K_pe tensors, which are then used in place instead of being concatenated first.
+  const void* kv_rope;
 #ifdef DSA_TRACE
   long long* trace;            // development builds only: clock samples of cluster 0, [2 CTAs][16 events][64 tiles]
 #endif

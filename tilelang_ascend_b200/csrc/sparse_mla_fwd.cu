@@ -778,6 +778,13 @@ static int launch_combine(const FwdParams& p, bool bf16, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+// The SM-pair kernel followed, for a split call, by the combine kernel (for callers that need that kernel and no other).
+int launch_sparse_mla_fwd_pair_combined(const FwdParams& p, bool bf16, cudaStream_t stream) {
+  int rc = launch_sparse_mla_fwd_pair(p, bf16, stream);
+  if (rc != 0 || p.nsplit <= 1) return rc;
+  return launch_combine(p, bf16, stream);
+}
+
 int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream) {
   // The kernel of sparse_mla_fwd_pair.cu (cta_group::2 MMAs) is the default; DSA_FWD_KERNEL=split in the environment selects
   // the kernel below (each CTA all 128 heads and half of the dims), which the tests use as a cross-check.

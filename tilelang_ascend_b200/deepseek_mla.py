@@ -55,9 +55,14 @@ class MlaDecodeKernel:
                 or tuple(kv.shape) != (B, N, 1, self.dim) or tuple(k_pe.shape) != (B, N, 1, self.pe_dim):
             raise ValueError("input shapes differ from the factory arguments")
         qq = torch.cat((q, q_pe), dim=-1).unsqueeze(1).contiguous()
-        kk = torch.cat((kv, k_pe), dim=-1).contiguous()
-        out, _ = sparse_mla_fwd_raw(qq, kk, _identity_indices(self._idx, dev, B, self.actual), sm_scale=(self.dim + self.pe_dim) ** -0.5,
-                                    q_start=0, causal=False, dv=self.dim, return_lse=False)
+        idx = _identity_indices(self._idx, dev, B, self.actual)
+        scale = (self.dim + self.pe_dim) ** -0.5
+        if self.dim == 512 and self.pe_dim == 64:
+            # kv and k_pe are read in place (rows in two parts): no concatenated copy of the cache per call
+            out, _ = sparse_mla_fwd_raw(qq, kv, idx, sm_scale=scale, q_start=0, causal=False, dv=self.dim, return_lse=False, kv_rope=k_pe)
+        else:
+            kk = torch.cat((kv, k_pe), dim=-1).contiguous()
+            out, _ = sparse_mla_fwd_raw(qq, kk, idx, sm_scale=scale, q_start=0, causal=False, dv=self.dim, return_lse=False)
         return out.squeeze(1)
 
 
@@ -93,12 +98,19 @@ class MlaDecodePagedKernel:
                 or tuple(K_pe.shape) != (rows, 1, self.dpe) or tuple(block_table.shape) != (B, nb):
             raise ValueError("input shapes differ from the factory arguments")
         qq = torch.cat((Q, Q_pe), dim=-1).unsqueeze(1).contiguous()
-        pool = torch.cat((KV, K_pe), dim=-1).view(rows // self.block_size, self.block_size, 1, self.dv + self.dpe)
         if dev not in self._len:
             self._len[dev] = torch.full((B,), self.cache_seqlen, dtype=torch.int32, device=dev)
-        out, _ = sparse_mla_fwd_raw(qq, pool, _identity_indices(self._idx, dev, B, self.cache_seqlen), sm_scale=1.0, q_start=0,
-                                    causal=False, dv=self.dv, return_lse=False, kv_len_b=self._len[dev], block_table=block_table,
-                                    block_size=self.block_size)
+        idx = _identity_indices(self._idx, dev, B, self.cache_seqlen)
+        common = dict(sm_scale=1.0, q_start=0, causal=False, dv=self.dv, return_lse=False, kv_len_b=self._len[dev], block_table=block_table,
+                      block_size=self.block_size)
+        nblk = rows // self.block_size
+        if self.dv == 512 and self.dpe == 64:
+            # the two pools are read in place through the same block table (rows in two parts)
+            out, _ = sparse_mla_fwd_raw(qq, KV.view(nblk, self.block_size, 1, self.dv), idx, kv_rope=K_pe.view(nblk, self.block_size, 1, self.dpe),
+                                        **common)
+        else:
+            pool = torch.cat((KV, K_pe), dim=-1).view(nblk, self.block_size, 1, self.dv + self.dpe)
+            out, _ = sparse_mla_fwd_raw(qq, pool, idx, **common)
         return out.squeeze(1)
 
 
@@ -136,9 +148,14 @@ class MlaDecodePersistentKernel:
                 or tuple(K_pe.shape) != (B, N, self.pe_dim):
             raise ValueError("input shapes differ from the factory arguments")
         qq = torch.cat((Q, Q_pe), dim=-1).unsqueeze(1).contiguous()
-        kk = torch.cat((KV, K_pe), dim=-1).unsqueeze(2).contiguous()
-        out, _ = sparse_mla_fwd_raw(qq, kk, _identity_indices(self._idx, dev, B, N), sm_scale=(self.dim + self.pe_dim) ** -0.5, q_start=0,
-                                    causal=False, dv=self.dim, return_lse=False)
+        idx = _identity_indices(self._idx, dev, B, N)
+        scale = (self.dim + self.pe_dim) ** -0.5
+        if self.dim == 512 and self.pe_dim == 64:   # KV and K_pe read in place (rows in two parts)
+            out, _ = sparse_mla_fwd_raw(qq, KV.unsqueeze(2), idx, sm_scale=scale, q_start=0, causal=False, dv=self.dim, return_lse=False,
+                                        kv_rope=K_pe.unsqueeze(2))
+        else:
+            kk = torch.cat((KV, K_pe), dim=-1).unsqueeze(2).contiguous()
+            out, _ = sparse_mla_fwd_raw(qq, kk, idx, sm_scale=scale, q_start=0, causal=False, dv=self.dim, return_lse=False)
         return out.squeeze(1)
 
 

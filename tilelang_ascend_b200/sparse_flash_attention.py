@@ -51,14 +51,22 @@ def _next_pow2(x: int) -> int:
 
 def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal: bool, dv: int, out=None,
                        return_lse: bool = True, q_start_b=None, kv_len_b=None, q_len_b=None, block_table=None,
-                       block_size: int = 0, impl: int = _lib.IMPL_AUTO, nsplit=None):
+                       block_size: int = 0, impl: int = _lib.IMPL_AUTO, nsplit=None, kv_rope=None):
     """One launch of the forward through the C ABI.  q [B,S,H,D], kv [B,S_kv,1,D] (or paged blocks),
     indices [B,S,1,topk] int32.  Returns (out, lse-or-None).
 
     nsplit: None = let the library decide whether the keys of every query are split over several work units (it does for
     D=576 / dv=512 calls with fewer queries than SM pairs, e.g. decode of a few sequences); 1 = never; n > 1 = n shares.
     The fp32 workspace of a split call is owned here (one per device and stream, reused between calls), as the reference's
-    adapter owns its kernels' workspaces (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137)."""
+    adapter owns its kernels' workspaces (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137).
+
+    ``kv_rope``: key rows in two parts -- ``kv`` then holds the dv latent values of every row ([B,S_kv,1,dv] or paged blocks)
+    and ``kv_rope`` the D - dv rope values with the same leading shape (the KV / K_pe tensors of the dense MLA decode
+    kernels, used in place); D = 576, dv = 512, topk <= 8192 only."""
+    if kv_rope is not None:
+        return _fwd_two_part(q, kv, kv_rope, indices, sm_scale=sm_scale, q_start=q_start, causal=causal, dv=dv, return_lse=return_lse,
+                             q_start_b=q_start_b, kv_len_b=kv_len_b, q_len_b=q_len_b, block_table=block_table, block_size=block_size,
+                             nsplit=nsplit)
     opt = [t for t in (q_start_b, kv_len_b, q_len_b, block_table) if t is not None]
     dev = check_inputs([q, kv, indices] + opt, [None, q.dtype, torch.int32] + [torch.int32] * len(opt),
                        ["q", "kv", "indices"] + ["int32 side input"] * len(opt))
@@ -102,6 +110,42 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
                 ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
                 1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
                 int(max_blocks), int(impl), current_stream(dev)))
+    return out, lse
+
+
+def _fwd_two_part(q, kv, kv_rope, indices, *, sm_scale, q_start, causal, dv, return_lse, q_start_b, kv_len_b, q_len_b, block_table,
+                  block_size, nsplit):
+    opt = [t for t in (q_start_b, kv_len_b, q_len_b, block_table) if t is not None]
+    dev = check_inputs([q, kv, kv_rope, indices] + opt, [None, q.dtype, q.dtype, torch.int32] + [torch.int32] * len(opt),
+                       ["q", "kv", "kv_rope", "indices"] + ["int32 side input"] * len(opt))
+    code = dtype_code(q.dtype)
+    B, S, H, D = q.shape
+    if D != 576 or dv != 512 or kv.dim() != 4 or kv_rope.dim() != 4 or kv.shape[2:] != (1, dv) or kv_rope.shape[2:] != (1, D - dv) \
+            or kv.shape[:2] != kv_rope.shape[:2] or indices.shape[:3] != (B, S, 1):
+        raise ValueError(f"key rows in two parts need D = 576, dv = 512, kv [...,1,512] and kv_rope [...,1,64] of equal leading shape "
+                         f"(got q {tuple(q.shape)}, kv {tuple(kv.shape)}, kv_rope {tuple(kv_rope.shape)})")
+    if block_table is None:
+        if kv.shape[0] != B:
+            raise ValueError("kv batch size differs from q")
+        S_kv, max_blocks = kv.shape[1], 0
+    else:
+        block_size = int(block_size) if block_size else kv.shape[1]
+        max_blocks = block_table.shape[1]
+        S_kv = max_blocks * block_size
+    topk = indices.shape[3]
+    if topk > 8192:
+        raise ValueError("key rows in two parts need topk <= 8192")
+    out = torch.empty((B, S, H, dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, S, H), dtype=torch.float32, device=dev) if return_lse else None
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        nsplit = int(lib.dsa_sparse_mla_fwd_splitkv_nsplit(B, S, H, topk)) if nsplit is None else int(nsplit)
+        nbytes = int(lib.dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, dv, nsplit)) if nsplit > 1 else 0
+        workspace = _split_workspace(dev, nbytes) if nsplit > 1 else None
+        _lib.check(lib.dsa_sparse_mla_fwd_two_part(
+            ptr(q), ptr(kv), ptr(kv_rope), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
+            1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size), int(max_blocks),
+            nsplit, ptr(workspace), nbytes, current_stream(dev)))
     return out, lse
 
 
