@@ -265,7 +265,11 @@ def sparse_attn_tilelang(query, key, value, sparse_indices, scale_value, sparse_
     if squeeze:
         query, query_rope, sparse_indices = query.unsqueeze(0), query_rope.unsqueeze(0), sparse_indices.unsqueeze(0)
     q = torch.cat((query, query_rope), dim=-1).contiguous()
-    kv = torch.cat((key, key_rope), dim=-1).contiguous()
+    # the key cache and its rope part are read in place as the two parts of a key row where the kernel can do that
+    # (512 + 64 values, lists of at most 8192 keys); otherwise they are concatenated into rows of D values first
+    two_part = (key.shape[-1] == 512 and key_rope.shape[-1] == 64 and sparse_indices.shape[-1] <= 8192 and key.is_contiguous()
+                and key_rope.is_contiguous())
+    kv = key if two_part else torch.cat((key, key_rope), dim=-1).contiguous()
     dev = q.device
     B, S = q.shape[0], q.shape[1]
     act_q = torch.as_tensor(actual_seq_lengths_query, dtype=torch.int32).to(dev).contiguous()
@@ -279,7 +283,7 @@ def sparse_attn_tilelang(query, key, value, sparse_indices, scale_value, sparse_
     out, lse = sparse_mla_fwd_raw(q, kv, sparse_indices.to(torch.int32).contiguous(), sm_scale=float(scale_value), q_start=0,
                                   causal=(sparse_mode == 3), dv=query.shape[-1], return_lse=return_softmax_lse,
                                   q_start_b=q_start_b, kv_len_b=act_kv, q_len_b=act_q, block_table=bt,
-                                  block_size=kv.shape[1] if bt is not None else 0)
+                                  block_size=kv.shape[1] if bt is not None else 0, kv_rope=key_rope if two_part else None)
     if squeeze:
         out = out.squeeze(0)
         lse = lse.squeeze(0) if lse is not None else None
