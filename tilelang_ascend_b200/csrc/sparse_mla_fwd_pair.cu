@@ -428,7 +428,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     // list (it decides how many tiles every role of the pair walks); each gathers its own 32 keys of a tile.
     const int pw = warp - kFirstGatherWarp;  // keys [8 pw, 8 pw + 8) of the CTA's 32
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
-    const uint8_t* rope_bytes = reinterpret_cast<const uint8_t*>(p.kv_rope);   // null unless the key rows come in two parts
+    // key rows in one piece (kRowBytes each) or in two parts (latent rows of 1024 bytes in kv, rope rows of 128 bytes in kv_rope):
+    // the first eight chunks come from kv at the row stride, the rope chunk from its own base and stride
+    const size_t row_stride = (kRope && p.kv_rope) ? static_cast<size_t>(kDV * 2) : static_cast<size_t>(kRowBytes);
+    const uint8_t* last_base = (kRope && p.kv_rope) ? reinterpret_cast<const uint8_t*>(p.kv_rope) : kv_bytes + 8 * 128;
+    const size_t last_stride = (kRope && p.kv_rope) ? static_cast<size_t>((kD - kDV) * 2) : static_cast<size_t>(kRowBytes);
     int g = 0, qslots = 0;  // tiles so far; ring slots so far that carried Q rows instead of a tile (two per non-empty item)
     for (int k = 0; run_all; ++k) {
       const int unit = item_of(k);
@@ -548,15 +552,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           const int row = __shfl_sync(0xffffffffu, my_row, kl);
           const uint32_t dst = stage + sw128_offset(pw * 8 + kl, lane & 7);
           const uint32_t nbytes = row < 0 ? 0u : 16u;
-          if (kRope && rope_bytes) {   // rows in two parts: 1024 bytes of latent values here, 128 bytes of rope values there
-            const uint8_t* src = kv_bytes + static_cast<size_t>(row < 0 ? 0 : row) * (kDV * 2) + (lane & 7) * 16;
+          {
+            const size_t r0 = static_cast<size_t>(row < 0 ? 0 : row);
+            const uint8_t* src = kv_bytes + r0 * row_stride + (lane & 7) * 16;
 #pragma unroll
             for (int c = 0; c < 8; ++c) cp_async16(dst + c * kChunk, src + c * 128, nbytes);
-            cp_async16(dst + 8 * kChunk, rope_bytes + static_cast<size_t>(row < 0 ? 0 : row) * ((kD - kDV) * 2) + (lane & 7) * 16, nbytes);
-          } else {
-            const uint8_t* src = kv_bytes + static_cast<size_t>(row < 0 ? 0 : row) * kRowBytes + (lane & 7) * 16;
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) cp_async16(dst + c * kChunk, src + c * 128, nbytes);
+            if (kRope) cp_async16(dst + 8 * kChunk, last_base + r0 * last_stride + (lane & 7) * 16, nbytes);
           }
         }
         cp_async_arrive_noinc(bar(kBarKvFull + s));
