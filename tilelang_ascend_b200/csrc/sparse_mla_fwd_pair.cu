@@ -245,20 +245,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarSFree + sb));  // the Q K^T of tile g+2 may overwrite the buffer
-        const bool full = mask == 0xffffu;
         float mx;
-        if (full) {
+        {
+          // scores of keys that do not take part count as -inf from here on: their exponentials are exact zeros.  (One code
+          // path for full and partly filled tiles: a separate fast path for full tiles made the loop longer and the kernel slower.)
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sc[j] = ((mask >> j) & 1u) ? sc[j] : 0xff800000u;
           float m4[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) m4[j] = fmaxf(__uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1]));
 #pragma unroll
           for (int j = 4; j < 8; ++j) m4[j & 3] = fmax3(m4[j & 3], __uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1]));
           mx = fmaxf(fmax3(m4[0], m4[1], m4[2]), m4[3]);
-        } else {
-          mx = -INFINITY;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if ((mask >> j) & 1u) mx = fmaxf(mx, __uint_as_float(sc[j]));
         }
         float* slot = rowmax + (g & 1) * 256;
         slot[part * 64 + m] = mx;
@@ -273,10 +271,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         for (int j = 0; j < 8; ++j) {
           const float2 x = ffma2(make_float2(__uint_as_float(sc[2 * j]), __uint_as_float(sc[2 * j + 1])), scale2, neg2);
           float2 e = make_float2(exp2f(x.x), exp2f(x.y));
-          if (!full) {
-            e.x = ((mask >> (2 * j)) & 1u) ? e.x : 0.f;
-            e.y = ((mask >> (2 * j + 1)) & 1u) ? e.y : 0.f;
-          }
           pe[2 * j] = e.x; pe[2 * j + 1] = e.y;
           sum2 = fadd2(sum2, e);
         }
