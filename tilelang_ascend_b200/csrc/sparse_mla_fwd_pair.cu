@@ -67,9 +67,12 @@ static_assert(kQPieceOff + 3 * kQPiece <= kStageBytes, "a ring slot holds half o
 constexpr int kSoftmaxWarps = 8;                       // warp w: lanes 32 (w & 3) .. +31, score columns 16 (w >> 2) .. +15
 constexpr int kFirstGatherWarp = 8;
 constexpr int kFirstExchangeWarp = 12;                 // 12..15: (w & 3) is also the lane quarter of their tensor-memory stores
+// The four issuing warps sit on the four sub-partitions of the SM (warp % 4); the two Q K^T issuers, which issue nine times
+// as many instructions as the P V issuers, share theirs with softmax warps of DIFFERENT 32-head blocks (warp % 2), so that
+// neither block of softmax warps is the slower one.
 constexpr int kQkWarp = 16;                            // even CTA: Q K^T issuer of the even tiles; odd CTA: forwards kv_full
-constexpr int kPvWarp = 17;                            // even CTA: first P V issuer; odd CTA: forwards v_full
-constexpr int kQkWarpB = 18;                           // even CTA: Q K^T issuer of the odd tiles; odd CTA: forwards s_free
+constexpr int kQkWarpB = 17;                           // even CTA: Q K^T issuer of the odd tiles; odd CTA: forwards s_free
+constexpr int kPvWarp = 18;                            // even CTA: first P V issuer; odd CTA: forwards v_full
 constexpr int kRelayWarp = 19;                         // even CTA: second P V issuer; odd CTA: forwards p_ready
 constexpr int kThreads = 640;
 constexpr uint32_t kTmemCols = 512;
@@ -746,7 +749,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       }
     } else if (lane == 0) {
       // ---- odd CTA: tell the even CTA when this CTA's rows of a tile have landed (warp 16) / when this CTA's softmax and
-      // exchange warps are past a score buffer (warp 18) ----
+      // exchange warps are past a score buffer (warp 17) ----
       const uint32_t target = map_to_cta(sBars, 0);
       int g = 0, ne = 0;
       for (int k = 0; run_all && ok; ++k) {
@@ -822,7 +825,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         __syncwarp();
       }
     } else if (lane == 0) {
-      // ---- odd CTA: tell the even CTA when the even CTA's half of the swap has landed here (warp 17) / when this CTA's
+      // ---- odd CTA: tell the even CTA when the even CTA's half of the swap has landed here (warp 18) / when this CTA's
       // softmax warps have written P (warp 19) ----
       const bool fwd_v = warp == kPvWarp;
       const uint32_t target = map_to_cta(sBars, 0);
