@@ -166,6 +166,17 @@ int dsa_sparse_mla_fwd(const void* q, const void* kv, const int32_t* indices, vo
  * value for the current device (1 = do not split).  Queries that do not exist (q_len_b) get out = 0, lse = -inf.
  * Replaces the same reference kernels as dsa_sparse_mla_fwd (their decode shape:
  * bench_sfa/sparse_flash_attn_pa_no_cv_pipeline.py:384-419, T = 1). */
+/* The forward with only the FIRST split_queries of the B * S queries (memory order) split into nsplit shares each, the
+ * others handled whole: for launches whose last round of work units fills the SM pairs only partly (e.g. one GPU's block
+ * of a sharded prefill: a persistent kernel reaches the first queries last) -- the split queries' shares then fill that
+ * round.  workspace: dsa_sparse_mla_fwd_splitkv_workspace_bytes(1, split_queries, H, DV, nsplit) bytes.  Results of the
+ * split queries are combined from fp32 partial results (same tolerance as dsa_sparse_mla_fwd_splitkv, not bit-equal to the
+ * unsplit kernel); all other rows are bit-equal to dsa_sparse_mla_fwd. */
+int dsa_sparse_mla_fwd_split_tail(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B, int32_t S,
+                                  int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start,
+                                  int32_t causal, int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                                  const int32_t* block_table, int32_t block_size, int32_t max_blocks, int32_t split_queries, int32_t nsplit,
+                                  void* workspace, size_t workspace_bytes, void* stream);
 /* The same forward with the key rows in TWO tensors addressed by the same row numbers: kv_latent [B, S_kv, 1, DV] (or paged
  * blocks) and kv_rope [B, S_kv, 1, D - DV] -- the KV and K_pe arguments of the reference's dense MLA decode kernels
  * (examples_experiment/deepseek_mla/example_mla_decode/example_mla_decode.py:46-249, example_mla_decode_paged.py:41-53),

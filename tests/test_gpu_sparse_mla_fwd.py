@@ -338,3 +338,25 @@ def test_debug_check_flags_repeated_indices(monkeypatch):
     with pytest.raises(ValueError, match="more than once"):
         dsa.sparse_mla_fwd_raw(q.cuda(), kv.cuda(), idx.cuda(), sm_scale=576 ** -0.5, q_start=252, causal=True, dv=512)
     check_status()
+
+
+@pytest.mark.parametrize("S,m,n", [(200, 30, 2), (160, 12, 4), (75, 1, 3), (90, 89, 2)])
+def test_split_tail_rows_are_combined_and_all_other_rows_stay_bit_equal(S, m, n):
+    """Only the first m queries of a launch split into n shares (the tail that a persistent kernel reaches last): those rows
+    agree with the unsplit call and the oracle within the usual tolerance, every other row is bit-equal to the unsplit call."""
+    import tilelang_ascend_b200 as dsa
+    q, kv, idx = orc.make_sparse_mla_inputs(1, S, 600, 128, 320, seed=S + m)
+    whole_o, whole_l = _fwd(q, kv, idx, IMPL_TC, nsplit=1)
+    out, lse = dsa.sparse_mla_fwd_raw(q.cuda(), kv.cuda(), idx.cuda(), sm_scale=576 ** -0.5, q_start=600 - S, causal=True, dv=512,
+                                      nsplit=n, split_queries=m)
+    check_status()
+    out, lse = out.cpu(), lse.cpu()
+    assert torch.equal(out[:, m:], whole_o[:, m:]) and torch.equal(lse[:, m:], whole_l[:, m:])
+    assert_close_fp(out[:, :m], whole_o[:, :m], "split rows vs unsplit out")
+    assert_close_fp(lse[:, :m], whole_l[:, :m], "split rows vs unsplit lse")
+    ref_o, ref_l = orc.sparse_mla_fwd(q, kv, idx)
+    assert_close_fp(out, ref_o, "out vs oracle")
+    assert_close_fp(lse, ref_l, "lse vs oracle")
+    kernel = dsa.sparse_attention_fwd(128, 512, 64, 320, 1, return_softmax_lse=True)
+    k_o, k_l = kernel(q.cuda(), kv.cuda(), idx.cuda(), split_tail=(m, n))
+    assert torch.equal(k_o.cpu(), out) and torch.equal(k_l.cpu(), lse)

@@ -42,6 +42,9 @@ SIGNATURES = {
     "dsa_sparse_mla_fwd": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                      c_int32, c_int32, c_int32, c_float, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "dsa_sparse_mla_fwd_split_tail": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                                c_int32, c_int32, c_int32, c_float, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_size_t, c_void_p]),
     "dsa_sparse_mla_fwd_two_part": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                               c_int32, c_int32, c_int32, c_float, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int32, c_int32, c_int32, c_void_p, c_size_t, c_void_p]),

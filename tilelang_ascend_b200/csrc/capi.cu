@@ -109,7 +109,7 @@ int fill_fwd_params(dsa::FwdParams* p, const void* q, const void* kv, const int3
   p->q_start_b = q_start_b; p->kv_len_b = kv_len_b; p->q_len_b = q_len_b;
   p->block_table = block_table; p->block_size = block_size; p->max_blocks = max_blocks;
   p->scale_log2 = sm_scale * 1.4426950408889634f;
-  p->nsplit = 1; p->part_out = nullptr; p->part_lse = nullptr; p->kv_rope = nullptr;
+  p->nsplit = 1; p->part_out = nullptr; p->part_lse = nullptr; p->kv_rope = nullptr; p->split_queries = 0;
 #ifdef DSA_TRACE
   p->trace = g_trace;
 #endif
@@ -346,6 +346,29 @@ int dsa_sparse_mla_fwd_splitkv(const void* q, const void* kv, const int32_t* ind
   }
   int err = dsa::launch_sparse_mla_fwd_tc(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
   return err ? fail_cuda("sparse_mla_fwd_splitkv launch", err) : 0;
+}
+
+int dsa_sparse_mla_fwd_split_tail(const void* q, const void* kv, const int32_t* indices, void* out, float* lse, int32_t B, int32_t S,
+                                  int32_t S_kv, int32_t H, int32_t D, int32_t DV, int32_t topk, float sm_scale, int32_t q_start,
+                                  int32_t causal, int32_t dtype, const int32_t* q_start_b, const int32_t* kv_len_b, const int32_t* q_len_b,
+                                  const int32_t* block_table, int32_t block_size, int32_t max_blocks, int32_t split_queries, int32_t nsplit,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  dsa::FwdParams p;
+  if (fill_fwd_params(&p, q, kv, indices, out, lse, B, S, S_kv, H, D, DV, topk, sm_scale, q_start, causal, dtype, q_start_b,
+                      kv_len_b, q_len_b, block_table, block_size, max_blocks))
+    return 1;
+  if (!dsa::sparse_mla_fwd_pair_supported(p)) return fail("a split tail needs D = 576 or 512, DV = 512 and topk <= 8192");
+  if (nsplit < 2 || nsplit > 64) return fail("nsplit must be in [2, 64]");
+  if (split_queries < 1 || static_cast<int64_t>(split_queries) >= static_cast<int64_t>(B) * S) return fail("split_queries must be in [1, B * S)");
+  const size_t need = dsa_sparse_mla_fwd_splitkv_workspace_bytes(1, split_queries, H, DV, nsplit);
+  if (!workspace || workspace_bytes < need) return fail("workspace too small (dsa_sparse_mla_fwd_splitkv_workspace_bytes(1, split_queries, H, DV, nsplit))");
+  if (reinterpret_cast<uintptr_t>(workspace) & 15u) return fail("workspace must be 16-byte aligned");
+  p.nsplit = nsplit;
+  p.split_queries = split_queries;
+  p.part_out = static_cast<float*>(workspace);
+  p.part_lse = p.part_out + static_cast<size_t>(nsplit) * split_queries * H * DV;
+  int err = dsa::launch_sparse_mla_fwd_pair_combined(p, dtype == DSA_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+  return err ? fail_cuda("sparse_mla_fwd_split_tail launch", err) : 0;
 }
 
 int dsa_sparse_mla_bwd(const void* q, const void* kv, const int32_t* indices, const void* out, const float* lse, const void* d_out,

@@ -32,6 +32,9 @@ struct FwdParams {
   int nsplit;
   float* part_out;
   float* part_lse;
+  // With nsplit > 1 and 0 < split_queries < B * S only the FIRST split_queries of the B * S queries (in memory order: the
+  // ones a persistent kernel reaches last) are split; part_out / part_lse then hold nsplit x split_queries x H rows.  0 = all.
+  int split_queries;
   // Key rows in two parts (SM-pair kernel, D = 576 / DV = 512 only): when kv_rope is set, kv holds rows of DV values (the
   // latent part) and kv_rope rows of D - DV values (the rope part), both addressed by the same row number -- the layout of
   // the dense MLA decode kernels' KV / K_pe tensors, which are then used in place instead of being concatenated first.

@@ -768,7 +768,9 @@ bool sparse_mla_fwd_pair_supported(const FwdParams& p);
 int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, cudaStream_t stream);
 
 static int launch_combine(const FwdParams& p, bool bf16, cudaStream_t stream) {
-  const int64_t rows = static_cast<int64_t>(p.B) * p.S * p.H;
+  // the rows that were split: all queries, or the first split_queries of them
+  const int64_t all = static_cast<int64_t>(p.B) * p.S;
+  const int64_t rows = ((p.split_queries > 0 && p.split_queries < all) ? p.split_queries : all) * p.H;
   if (bf16)
     sparse_mla_fwd_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 128, 0, stream>>>(p.part_out, p.part_lse, reinterpret_cast<__nv_bfloat16*>(p.out),
                                                                                                 p.lse, rows, p.nsplit, p.DV);
@@ -789,7 +791,8 @@ int launch_sparse_mla_fwd_tc(const FwdParams& p, bool bf16, cudaStream_t stream)
   // The kernel of sparse_mla_fwd_pair.cu (cta_group::2 MMAs) is the default; DSA_FWD_KERNEL=split in the environment selects
   // the kernel below (each CTA all 128 heads and half of the dims), which the tests use as a cross-check.
   const char* which = getenv("DSA_FWD_KERNEL");
-  if (!(which && which[0] == 's') && sparse_mla_fwd_pair_supported(p)) {
+  const bool tail_only = p.nsplit > 1 && p.split_queries > 0 && p.split_queries < static_cast<long long>(p.B) * p.S;  // pair kernel only
+  if ((!(which && which[0] == 's') || tail_only) && sparse_mla_fwd_pair_supported(p)) {
     int rc = launch_sparse_mla_fwd_pair(p, bf16, stream);
     if (rc != 0 || p.nsplit <= 1) return rc;
     return launch_combine(p, bf16, stream);

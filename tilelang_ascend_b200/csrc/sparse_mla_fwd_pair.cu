@@ -154,11 +154,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   const int num_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
   const int head_blocks = (p.H + kM - 1) / kM;
   const int nsplit = p.nsplit > 1 ? p.nsplit : 1;
-  const int num_items = p.B * p.S * head_blocks * nsplit;  // work units: (query, head block, share of the key tiles)
+  // Work units: a (query, head block) item, or one of the nsplit shares of its key tiles.  The first split_rows queries are
+  // split (all of them unless the caller names fewer: the tail of a launch, which the clusters reach last and which fills
+  // their last round only partly), the others are one unit each.  Units are numbered with the split items first.
+  const int split_rows = nsplit > 1 ? ((p.split_queries > 0 && p.split_queries < p.B * p.S) ? p.split_queries : p.B * p.S) : 0;
+  const int split_units = split_rows * head_blocks * nsplit;
+  const int num_items = split_units + (p.B * p.S - split_rows) * head_blocks;
   const int ntiles = (p.topk + kBK - 1) / kBK;
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
-  // k-th work unit of this cluster (late queries first), or negative; unit = (query, head block) * nsplit + share
+  // k-th work unit of this cluster (late queries first), or negative
   auto item_of = [&](int k) { return num_items - 1 - cluster_id - k * num_clusters; };
+  // unit -> (query, head block) item, its share and the number of shares of that item
+  auto item_and_share = [&](int u, int* share, int* shares) {
+    if (u < split_units) {
+      const int it = u / nsplit;
+      *share = u - it * nsplit;
+      *shares = nsplit;
+      return it;
+    }
+    *share = 0;
+    *shares = 1;
+    return split_rows * head_blocks + (u - split_units);
+  };
 #ifdef DSA_TRACE
 #ifndef DSA_TRACE_MASK
 #define DSA_TRACE_MASK 0xffffffu   // which events are compiled in: every sample point slows its role, a build with few is closer to the product
@@ -177,7 +194,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
   auto q_rows_of = [&](int u, int* nrows) -> const uint8_t* {
     *nrows = 0;
     if (u < 0) return nullptr;
-    const int it_item = u / nsplit;
+    int sh_unused, ns_unused;
+    const int it_item = item_and_share(u, &sh_unused, &ns_unused);
     const int nbt = it_item / head_blocks, nh0 = (it_item - nbt * head_blocks) * kM + static_cast<int>(rank) * kHeads;
     if (nh0 >= p.H) return nullptr;
     *nrows = p.H - nh0 < kHeads ? p.H - nh0 : kHeads;
@@ -230,7 +248,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     for (int k = 0; run_all; ++k) {
       const int unit = item_of(k);
       if (unit < 0) break;
-      const int item = unit / nsplit, share = unit - item * nsplit;
+      int share, shares;
+      const int item = item_and_share(unit, &share, &shares);
       const int qp = k & 1;
       const int bt = item / head_blocks, h0 = (item - bt * head_blocks) * kM;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(kBarInfoFull + qp), (k >> 1) & 1, p.status));
@@ -337,13 +356,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
       const int dim0 = 256 * kh + 128 * ch;
       T* orow = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(bt) * p.H + h) * kDV + dim0;
       // split-KV: this unit's normalised partial result and its log-sum-exp go to the workspace instead
-      const int64_t prow_index = (static_cast<int64_t>(share) * p.B * p.S + bt) * p.H + h;
-      float* part_row = nsplit > 1 ? p.part_out + prow_index * kDV + dim0 : nullptr;
+      const int64_t prow_index = (static_cast<int64_t>(share) * split_rows + bt) * p.H + h;
+      float* part_row = shares > 1 ? p.part_out + prow_index * kDV + dim0 : nullptr;
       const bool lse_writer = kh == 0 && ch == 0;
       // scratch of this warp for the output transposition: inside the P rows of its own block of 32 heads (both P buffers), so
       // that only warps of the same block -- which meet at a named barrier when they are done -- can write P over it
       const uint32_t out_scratch = sBase + kOffP + (part < 2 ? 0u : kPBytes) + (q4 & 1) * 4096u + (part & 1) * 2048u;
-      if (nsplit > 1 && nvt == 0) {
+      if (shares > 1 && nvt == 0) {
         if (h < p.H) {  // nothing to add from this share (also for queries that do not exist: the combine step writes zeros)
           for (int j = 0; j < 32; ++j) reinterpret_cast<float4*>(part_row)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (lse_writer) p.part_lse[prow_index] = -INFINITY;
@@ -363,7 +382,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         for (int cc = 0; cc < 4; ++cc) {
           tmem_ld32(tO + lane_base + (4 * ch + cc) * 32, v);
           tmem_wait_ld();
-          if (nsplit > 1) {
+          if (shares > 1) {
             // fp32 partial rows: the same detour through the warp's scratch as below, 16 columns (64 bytes per row) at a time
 #pragma unroll
             for (int hq = 0; hq < 2; ++hq) {
@@ -406,7 +425,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
         }
         if (ok && lse_writer && h < p.H) {
           const float lse_v = m_used * 0.6931471805599453f + logf(l);
-          if (nsplit > 1) p.part_lse[prow_index] = lse_v;
+          if (shares > 1) p.part_lse[prow_index] = lse_v;
           else if (p.lse) p.lse[static_cast<int64_t>(bt) * p.H + h] = lse_v;
         }
       }
@@ -434,7 +453,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
     for (int k = 0; run_all; ++k) {
       const int unit = item_of(k);
       if (unit < 0) break;
-      const int item = unit / nsplit, share = unit - item * nsplit;
+      int share, shares;
+      const int item = item_and_share(unit, &share, &shares);
       const int qp = k & 1;
       const int bt = item / head_blocks;
       const RowCtx ctx = make_row_ctx(p, bt);
@@ -468,10 +488,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pr::kThreads, 1) spa
           if (nonempty) tile_list[qp * kMaxTiles + n + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(tile);
           n += __popc(bal);
         }
-        if (nsplit > 1) {
+        if (shares > 1) {
           // this unit's share of the list: entries [lo, hi) move to the front (in chunks of 32, reading before writing)
-          const int lo = static_cast<int>(static_cast<long long>(n) * share / nsplit);
-          const int hi = static_cast<int>(static_cast<long long>(n) * (share + 1) / nsplit);
+          const int lo = static_cast<int>(static_cast<long long>(n) * share / shares);
+          const int hi = static_cast<int>(static_cast<long long>(n) * (share + 1) / shares);
           __syncwarp();
           for (int base = 0; base < hi - lo; base += 32) {
             const int i = base + lane;
@@ -886,7 +906,9 @@ int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, cudaStream_t strea
   // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
   const long long items = static_cast<long long>(p.B) * p.S * ((p.H + pr::kM - 1) / pr::kM);
   long long clusters = sms / 2 > 0 ? sms / 2 : 1;
-  const long long units = items * (p.nsplit > 1 ? p.nsplit : 1);
+  const long long hb = (p.H + pr::kM - 1) / pr::kM, rows = static_cast<long long>(p.B) * p.S;
+  const long long split_rows = p.nsplit > 1 ? ((p.split_queries > 0 && p.split_queries < rows) ? p.split_queries : rows) : 0;
+  const long long units = split_rows * hb * (p.nsplit > 1 ? p.nsplit : 1) + (rows - split_rows) * hb;
   if (clusters > units) clusters = units;
   kern<<<dim3(static_cast<unsigned>(2 * clusters)), pr::kThreads, pr::kSmemBytes, stream>>>(p);
   return static_cast<int>(cudaGetLastError());

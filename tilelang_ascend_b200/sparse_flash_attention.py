@@ -51,7 +51,7 @@ def _next_pow2(x: int) -> int:
 
 def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal: bool, dv: int, out=None,
                        return_lse: bool = True, q_start_b=None, kv_len_b=None, q_len_b=None, block_table=None,
-                       block_size: int = 0, impl: int = _lib.IMPL_AUTO, nsplit=None, kv_rope=None):
+                       block_size: int = 0, impl: int = _lib.IMPL_AUTO, nsplit=None, kv_rope=None, split_queries: int = 0):
     """One launch of the forward through the C ABI.  q [B,S,H,D], kv [B,S_kv,1,D] (or paged blocks),
     indices [B,S,1,topk] int32.  Returns (out, lse-or-None).
 
@@ -59,6 +59,11 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
     D=576 / dv=512 calls with fewer queries than SM pairs, e.g. decode of a few sequences); 1 = never; n > 1 = n shares.
     The fp32 workspace of a split call is owned here (one per device and stream, reused between calls), as the reference's
     adapter owns its kernels' workspaces (tilelang/jit/adapter/cython/cython_wrapper.pyx:98-137).
+
+    ``split_queries`` = m with ``nsplit`` = n > 1: only the first m of the B * S queries (memory order) are split; a persistent
+    kernel reaches them last, and their shares fill its last round of work units when the other queries leave it partly
+    empty (one GPU's block of a sharded prefill).  Their results are combined from fp32 partial results; all other rows are
+    bit-equal to an unsplit call.
 
     ``kv_rope``: key rows in two parts -- ``kv`` then holds the dv latent values of every row ([B,S_kv,1,dv] or paged blocks)
     and ``kv_rope`` the D - dv rope values with the same leading shape (the KV / K_pe tensors of the dense MLA decode
@@ -96,7 +101,16 @@ def sparse_mla_fwd_raw(q, kv, indices, *, sm_scale: float, q_start: int, causal:
         if nsplit is None:
             nsplit = int(lib.dsa_sparse_mla_fwd_splitkv_nsplit(B, S, H, topk)) if tc_shape else 1
         nsplit = int(nsplit)
-        if nsplit > 1:
+        if nsplit > 1 and 0 < int(split_queries) < B * S:
+            if not tc_shape:
+                raise ValueError("a split tail needs D = 576 or 512, dv = 512, topk <= 8192 and the tensor-core kernel")
+            nbytes = int(lib.dsa_sparse_mla_fwd_splitkv_workspace_bytes(1, int(split_queries), H, dv, nsplit))
+            workspace = _split_workspace(dev, nbytes)
+            _lib.check(lib.dsa_sparse_mla_fwd_split_tail(
+                ptr(q), ptr(kv), ptr(indices), ptr(out), ptr(lse), B, S, S_kv, H, D, dv, topk, float(sm_scale), int(q_start),
+                1 if causal else 0, code, ptr(q_start_b), ptr(kv_len_b), ptr(q_len_b), ptr(block_table), int(block_size),
+                int(max_blocks), int(split_queries), nsplit, ptr(workspace), nbytes, current_stream(dev)))
+        elif nsplit > 1:
             if not tc_shape:
                 raise ValueError("nsplit > 1 needs D = 576, dv = 512, topk <= 8192 and the tensor-core kernel")
             nbytes = int(lib.dsa_sparse_mla_fwd_splitkv_workspace_bytes(B, S, H, dv, nsplit))
@@ -201,7 +215,9 @@ class SparseAttentionFwdKernel:
         self.heads, self.dim, self.tail_dim, self.topk = heads, dim, tail_dim, topk
         self.sm_scale, self.dtype, self.return_softmax_lse, self.impl = sm_scale, dtype, return_softmax_lse, impl
 
-    def __call__(self, q, kv, indices, q_start_index_s: Optional[int] = None):
+    def __call__(self, q, kv, indices, q_start_index_s: Optional[int] = None, split_tail: Optional[tuple] = None):
+        """``split_tail=(m, n)`` (not in the reference): the first m queries are split into n shares of their keys each, so that
+        they fill the launch's last, partly filled round of work units (see :func:`sparse_mla_fwd_raw`)."""
         if q.dtype != self.dtype:
             raise ValueError(f"Input tensor q has dtype {q.dtype}, expected {self.dtype}")
         if q.dim() != 4 or q.shape[2] != self.heads or q.shape[3] != self.dim + self.tail_dim:
@@ -210,8 +226,9 @@ class SparseAttentionFwdKernel:
             raise ValueError(f"indices must be [B, S, 1, {self.topk}], got {tuple(indices.shape)}")
         S, S_kv = q.shape[1], kv.shape[1]
         q_start = S_kv - S if q_start_index_s is None else int(q_start_index_s)
+        extra = {} if not split_tail or split_tail[0] <= 0 or split_tail[1] <= 1 else {"split_queries": int(split_tail[0]), "nsplit": int(split_tail[1])}
         out, lse = sparse_mla_fwd_raw(q, kv, indices, sm_scale=self.sm_scale, q_start=q_start, causal=True, dv=self.dim,
-                                      return_lse=self.return_softmax_lse, impl=self.impl)
+                                      return_lse=self.return_softmax_lse, impl=self.impl, **extra)
         return (out, lse) if self.return_softmax_lse else out
 
 
