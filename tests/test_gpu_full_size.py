@@ -220,3 +220,14 @@ def test_cost_balanced_query_shards_reassemble_bit_exactly(world):
         if not pairs:
             assert max(loads) <= 1.01 * sum(loads) / world
         assert torch.equal(torch.cat(outs, 1), out) and torch.equal(torch.cat(lses, 1), lse)
+    # the partition with split last rounds: rows of a block's split tail within tolerance, all others bit-equal
+    spans = dsa.shard_ranges_by_rounds(costs, world, 74, tail_split=True)
+    for s, e in spans:
+        m, n, _ = dsa.tail_split_plan(costs, s, e, 74)
+        o, l = kernel(q[:, s:e].contiguous(), kv, idx[:, s:e].contiguous(), q_start_index_s=s, split_tail=(m, n))
+        check_status()
+        cut = m if n > 1 else 0
+        assert torch.equal(o[:, cut:], out[:, s + cut:e]) and torch.equal(l[:, cut:], lse[:, s + cut:e])
+        if cut:
+            assert (o[:, :cut].float() - out[:, s:s + cut].float()).abs().max().item() <= 2e-2
+            assert (l[:, :cut] - lse[:, s:s + cut]).abs().max().item() <= 1e-3

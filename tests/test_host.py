@@ -113,3 +113,22 @@ def test_partition_by_rounds_beats_the_cost_sum_partition_and_covers_everything(
         max(dsa.block_time_in_rounds(costs, *dsa.shard_range_balanced(costs, r, 4), 74) for r in range(4))
     assert dsa.shard_ranges_by_rounds([], 2, 74) == [(0, 0), (0, 0)]
     assert dsa.shard_ranges_by_rounds([5, 5, 5], 5, 2) [:2] == [(0, 2), (2, 3)] or sum(e - s for s, e in dsa.shard_ranges_by_rounds([5, 5, 5], 5, 2)) == 3
+
+
+def test_partition_with_split_tails_reaches_half_rounds():
+    """With the queries of a partly filled last round split into shares, the 8-GPU partition of the prefill shape gets blocks
+    of 5.5 rounds of long queries instead of 6 (model time 195 against 210; 190.75 would be perfect)."""
+    import tilelang_ascend_b200 as dsa
+    costs = dsa.causal_query_costs(4096, 4096, 2048)
+    plain = dsa.shard_ranges_by_rounds(costs, 8, 74)
+    split = dsa.shard_ranges_by_rounds(costs, 8, 74, tail_split=True)
+    assert split[0][0] == 0 and split[-1][1] == 4096 and all(a[1] == b[0] for a, b in zip(split, split[1:]))
+    t_plain = max(dsa.block_time_in_rounds(costs, s, e, 74) for s, e in plain)
+    t_split = max(dsa.block_time_in_rounds(costs, s, e, 74, True) for s, e in split)
+    assert t_split < t_plain and t_split <= 1.03 * dsa.block_time_in_rounds(costs, 0, 4096, 74) / 8
+    for s, e in split:
+        m, n, t = dsa.tail_split_plan(costs, s, e, 74)
+        assert (m == 0 and n == 1) or (m == (e - s) % 74 and 2 <= n <= 4 and m * n <= 74)
+    assert dsa.tail_split_plan(costs, 0, 74, 74) == (0, 1, 0)                 # whole rounds: nothing to split
+    assert dsa.tail_split_plan(costs, 0, 30, 74)[:2] == (0, 1)                # one-tile queries: splitting cannot pay
+    assert dsa.tail_split_plan(costs, 4096 - 74 - 20, 4096, 74)[:2] == (20, 3)  # 20 long queries fill the round as 3 shares each

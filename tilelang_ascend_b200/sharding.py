@@ -51,24 +51,56 @@ def shard_range_balanced(costs, rank: int, world: int) -> Tuple[int, int]:
     return bounds[rank], bounds[rank + 1]
 
 
-def block_time_in_rounds(costs, start: int, end: int, units_per_round: int) -> int:
+MAX_TAIL_SHARES = 4          # into how many shares the queries of a partly filled last round are split at most
+SPLIT_EXTRA_TILES = 1        # what a split query costs beside its tiles: fp32 partial results written and combined
+
+
+def tail_split_plan(costs, start: int, end: int, units_per_round: int):
+    """(m, n, time) for the LAST round of a block -- its first m = (end - start) % units_per_round items, the ones a persistent
+    kernel reaches last: split into n shares each so that they fill the round (m * n <= units_per_round), if that is faster
+    than leaving them whole; (0, 1, time) otherwise.  ``costs`` are tiles + FIXED_TILES_PER_QUERY; only the tiles shrink."""
+    import numpy as np
+    m = (end - start) % units_per_round
+    if m == 0:
+        return 0, 1, 0
+    worst = int(np.asarray(costs)[start:start + m].max())
+    best = (0, 1, worst)
+    for n in range(2, MAX_TAIL_SHARES + 1):
+        if m * n > units_per_round:
+            break
+        tiles = max(worst - FIXED_TILES_PER_QUERY, 0)
+        t = -(-tiles // n) + FIXED_TILES_PER_QUERY + SPLIT_EXTRA_TILES
+        if t < best[2]:
+            best = (m, n, t)
+    return best
+
+
+def block_time_in_rounds(costs, start: int, end: int, units_per_round: int, tail_split: bool = False) -> int:
     """Time (in the unit of ``costs``) a persistent kernel needs for items [start, end) when it walks them from the last
     item backwards in rounds of ``units_per_round`` (one item per SM pair and round; every round lasts as long as its most
-    expensive item): the sum over rounds of the largest cost in the round."""
+    expensive item): the sum over rounds of the largest cost in the round.  ``tail_split``: the last, partly filled round
+    may be run with its items split into shares (:func:`tail_split_plan`)."""
     import numpy as np
     c = np.asarray(costs)
     t = 0
-    for hi in range(end, start, -units_per_round):
-        t += int(c[max(start, hi - units_per_round):hi].max())
+    full = (end - start) // units_per_round
+    for r in range(full):
+        hi = end - r * units_per_round
+        t += int(c[hi - units_per_round:hi].max())
+    m = (end - start) - full * units_per_round
+    if m > 0:
+        t += tail_split_plan(c, start, end, units_per_round)[2] if tail_split else int(c[start:start + m].max())
     return t
 
 
-def shard_ranges_by_rounds(costs, world: int, units_per_round: int):
+def shard_ranges_by_rounds(costs, world: int, units_per_round: int, tail_split: bool = False):
     """Contiguous [start, end) blocks of ``len(costs)`` items for all ``world`` ranks that minimise the slowest rank's
     :func:`block_time_in_rounds`.  Cutting by the plain sum of costs ignores that a GPU works in rounds of
     ``units_per_round`` items: a block of 5.4 rounds takes as long as one of 6, which at 8 GPUs (about 400 long queries per
     rank on 74 SM pairs) is a tenth of the step.  Found by bisection on the time limit, each rank taking as many items as
-    fit (the time of a block is non-decreasing in its end)."""
+    fit (the time of a block is non-decreasing in its end).  ``tail_split``: blocks may end in a round whose queries are split
+    into shares (:func:`tail_split_plan`; the caller then launches its block with that plan), which makes half and third
+    rounds available to the partition."""
     import numpy as np
     c = np.asarray(costs, dtype=np.int64)
     n = int(c.shape[0])
@@ -82,12 +114,12 @@ def shard_ranges_by_rounds(costs, world: int, units_per_round: int):
         for _ in range(world):
             # largest e with time(s, e) <= limit: grow in whole rounds first, then item by item
             e = s
-            while e < n and block_time_in_rounds(c, s, min(n, e + units_per_round), units_per_round) <= limit:
+            while e < n and block_time_in_rounds(c, s, min(n, e + units_per_round), units_per_round, tail_split) <= limit:
                 e = min(n, e + units_per_round)
             lo, hi = e, min(n, e + units_per_round)
             while lo < hi:  # binary search inside the last partial round
                 mid = (lo + hi + 1) // 2
-                if block_time_in_rounds(c, s, mid, units_per_round) <= limit:
+                if block_time_in_rounds(c, s, mid, units_per_round, tail_split) <= limit:
                     lo = mid
                 else:
                     hi = mid - 1
@@ -95,7 +127,7 @@ def shard_ranges_by_rounds(costs, world: int, units_per_round: int):
             s = lo
         return spans if s == n else None
 
-    lo_t, hi_t = 1, block_time_in_rounds(c, 0, n, units_per_round)
+    lo_t, hi_t = 1, block_time_in_rounds(c, 0, n, units_per_round, tail_split)
     while lo_t < hi_t:
         mid = (lo_t + hi_t) // 2
         if cut(mid) is not None:
