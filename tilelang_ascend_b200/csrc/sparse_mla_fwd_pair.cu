@@ -904,7 +904,6 @@ int launch_sparse_mla_fwd_pair(const FwdParams& p, bool bf16, cudaStream_t strea
                    : (bf16 ? sparse_mla_fwd_pair_kernel<true, false> : sparse_mla_fwd_pair_kernel<false, false>);
   if ((e = ensure_dynamic_smem(kern, dev, static_cast<int>(pr::kSmemBytes))) != cudaSuccess) return static_cast<int>(e);
   // persistent: one 2-CTA cluster per SM pair, each walking its share of the (query, head block) items
-  const long long items = static_cast<long long>(p.B) * p.S * ((p.H + pr::kM - 1) / pr::kM);
   long long clusters = sms / 2 > 0 ? sms / 2 : 1;
   const long long hb = (p.H + pr::kM - 1) / pr::kM, rows = static_cast<long long>(p.B) * p.S;
   const long long split_rows = p.nsplit > 1 ? ((p.split_queries > 0 && p.split_queries < rows) ? p.split_queries : rows) : 0;
