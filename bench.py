@@ -8,10 +8,13 @@
 
 One step = one pass of the sparse MLA forward over the DeepSeek-V3.2 prefill workload
 (B=1, S_q=S_kv=4096, H=128, D=576, dv=512, topk=2048, bf16, causal index lists, synthetic N(0,1)).
-With N GPUs the 4096 queries of that ONE workload are cut into N contiguous blocks of equal cost (strong scaling: total
-work fixed; the latent KV is replicated; no collective in the timed region), `value` is 4096 tokens divided by the slowest
-rank's device time, and after the timing an NCCL all-gather reassembles out / lse, which rank 0 compares bit for bit with
-its own unsharded run.  Rank 0 prints ONE JSON line.
+With N GPUs the 4096 queries of that ONE workload are cut into N contiguous blocks that take equal time in rounds of one
+query per SM pair (strong scaling: total work fixed; the latent KV is replicated; no collective in the timed region; a
+block may end in a round whose queries are split into shares of their keys), `value` is 4096 tokens divided by the slowest
+rank's device time -- a step is one replay of a CUDA graph holding the step's launches -- and after the timing an NCCL
+all-gather reassembles out / lse, which rank 0 compares with its own unsharded run: bit for bit, except the rows of split
+last rounds, which are sums of fp32 partial results and are compared within the tolerance of the parity tests.
+Rank 0 prints ONE JSON line on standard output (everything else, also what libraries print from C, goes to standard error).
 """
 from __future__ import annotations
 
